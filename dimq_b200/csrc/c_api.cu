@@ -1,0 +1,105 @@
+// Argument validation and kernel selection of the weight-only entry points, plus
+// the small utility entry points of the C ABI.
+#include "common.cuh"
+
+namespace dimq {
+int check_wq_weight(const dimq_wq_weight* w, int64_t out_rows);
+int launch_linear_wq_generic(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
+                             const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K,
+                             int epilogue, cudaStream_t st);
+int launch_conv2d_direct(bool a4, const void* x, int x_dtype, const dimq_wq_weight* w, float scale, int zp,
+                         const void* bias, int bias_dtype, const void* residual, void* y, int y_dtype,
+                         const dimq_conv_geom* g, int epilogue, cudaStream_t st);
+bool stream_supported(const dimq_wq_weight* w, int64_t M, int64_t N, int64_t K);
+int launch_linear_wq_stream(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
+                            const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K,
+                            int epilogue, cudaStream_t st);
+bool tc_supported(const void* x, int x_dtype, const dimq_wq_weight* w, int64_t M, int64_t N, int64_t K);
+int launch_linear_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
+                        const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K, int epilogue,
+                        int w_fmt, cudaStream_t st);
+int read_device_status(uint32_t* status);
+}  // namespace dimq
+
+using namespace dimq;
+
+extern "C" int dimq_version(void) { return 100; }
+
+extern "C" const char* dimq_status_string(int status) {
+  switch (status) {
+    case DIMQ_OK: return "ok";
+    case DIMQ_ERR_NULL_POINTER: return "a required pointer is null";
+    case DIMQ_ERR_BAD_SIZE: return "a size or count is out of range";
+    case DIMQ_ERR_BAD_DTYPE: return "unsupported element type";
+    case DIMQ_ERR_BAD_BITS: return "unsupported index bit width (or more codebook entries than 2^bits)";
+    case DIMQ_ERR_BAD_QPARAMS: return "act_scale must be positive and act_zero_point in [0, 15]";
+    case DIMQ_ERR_BAD_SHAPE: return "tensor shapes / convolution geometry do not fit together";
+    case DIMQ_ERR_UNSUPPORTED: return "the requested algorithm does not support these arguments";
+    case DIMQ_ERR_ALIGNMENT: return "a pointer is not aligned as the kernel requires";
+    case DIMQ_ERR_DRIVER: return "tensor-map encoding through the CUDA driver failed";
+    case DIMQ_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel expired";
+    case DIMQ_ERR_TOO_LARGE: return "problem too large for this kernel's grid";
+    default: break;
+  }
+  if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));
+  return "unknown dimq status";
+}
+
+extern "C" int dimq_last_device_status(uint32_t* status) {
+  if (status == nullptr) return DIMQ_ERR_NULL_POINTER;
+  return read_device_status(status);
+}
+
+extern "C" int dimq_linear_wq(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias,
+                              int bias_dtype, const void* residual, void* y, int y_dtype, int64_t M, int64_t N,
+                              int64_t K, int epilogue, int algo, void* stream) {
+  if (M < 0 || N <= 0 || K <= 0) return DIMQ_ERR_BAD_SIZE;
+  if (!valid_dtype(x_dtype) || !valid_dtype(y_dtype)) return DIMQ_ERR_BAD_DTYPE;
+  if (bias != nullptr && !valid_dtype(bias_dtype)) return DIMQ_ERR_BAD_DTYPE;
+  if (epilogue < DIMQ_EPI_NONE || epilogue > DIMQ_EPI_GELU) return DIMQ_ERR_UNSUPPORTED;
+  const int rc = check_wq_weight(w, N);
+  if (rc != DIMQ_OK) return rc;
+  if (M == 0) return DIMQ_OK;
+  if (x == nullptr || y == nullptr) return DIMQ_ERR_NULL_POINTER;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // operand format of the dequantised weight on the tensor cores: fp16 keeps 11
+  // significand bits of the codeword (bf16 would keep 8)
+  const int w_fmt = 0;
+  if (algo == DIMQ_ALGO_AUTO) {
+    if (stream_supported(w, M, N, K)) algo = DIMQ_ALGO_STREAM;
+    else if (M > 8 && tc_supported(x, x_dtype, w, M, N, K)) algo = DIMQ_ALGO_TCGEN05;
+    else algo = DIMQ_ALGO_GENERIC;
+  }
+  switch (algo) {
+    case DIMQ_ALGO_GENERIC:
+      return launch_linear_wq_generic(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, st);
+    case DIMQ_ALGO_STREAM:
+      return launch_linear_wq_stream(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, st);
+    case DIMQ_ALGO_TCGEN05:
+      return launch_linear_wq_tc(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, w_fmt, st);
+    case DIMQ_ALGO_TCGEN05 + 100:  // tcgen05 with the weight operand rounded to bf16 (measurement only)
+      return launch_linear_wq_tc(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, 1, st);
+    default:
+      return DIMQ_ERR_UNSUPPORTED;
+  }
+}
+
+extern "C" int dimq_conv2d_wq(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias,
+                              int bias_dtype, const void* residual, void* y, int y_dtype,
+                              const dimq_conv_geom* geom, int epilogue, int algo, void* stream) {
+  if (geom == nullptr) return DIMQ_ERR_NULL_POINTER;
+  dimq_conv_geom g = *geom;
+  int rc = dimq_conv_out_size(&g);
+  if (rc != DIMQ_OK) return rc;
+  if (g.out_h != geom->out_h || g.out_w != geom->out_w) return DIMQ_ERR_BAD_SHAPE;
+  if (!valid_dtype(x_dtype) || !valid_dtype(y_dtype)) return DIMQ_ERR_BAD_DTYPE;
+  if (bias != nullptr && !valid_dtype(bias_dtype)) return DIMQ_ERR_BAD_DTYPE;
+  if (epilogue < DIMQ_EPI_NONE || epilogue > DIMQ_EPI_GELU) return DIMQ_ERR_UNSUPPORTED;
+  rc = check_wq_weight(w, g.out_channels);
+  if (rc != DIMQ_OK) return rc;
+  if (static_cast<int64_t>(g.batch) * g.out_channels * g.out_h * g.out_w == 0) return DIMQ_OK;
+  if (x == nullptr || y == nullptr) return DIMQ_ERR_NULL_POINTER;
+  if (algo != DIMQ_ALGO_AUTO && algo != DIMQ_ALGO_GENERIC) return DIMQ_ERR_UNSUPPORTED;
+  return launch_conv2d_direct(false, x, x_dtype, w, 1.0f, 0, bias, bias_dtype, residual, y, y_dtype, &g, epilogue,
+                              static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,173 @@
+/*
+ * dimq_b200 — C ABI of the B200 (sm_100a) backend for DIMQ packed-index inference.
+ *
+ * Every entry point takes raw device pointers, explicit sizes and a CUDA stream
+ * (a cudaStream_t passed as void*; NULL is the legacy default stream).  Nothing
+ * here allocates device memory, synchronises the stream or takes ownership of a
+ * buffer: the caller provides inputs, outputs and (where stated) scratch.
+ * Launches go to the device that is current on the calling thread.
+ *
+ * Return value: 0 on success; a negative DIMQ_ERR_* code for a rejected
+ * argument (nothing was launched); a positive value is a cudaError_t reported by
+ * the launch.  dimq_status_string() turns either into text.
+ *
+ * "Replaces" names the function of the DIMQ reference (paths inside that
+ * project) whose role the entry point takes over.
+ */
+#ifndef DIMQ_B200_H_
+#define DIMQ_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define DIMQ_API __attribute__((visibility("default")))
+#else
+#define DIMQ_API
+#endif
+
+#define DIMQ_OK 0
+#define DIMQ_ERR_NULL_POINTER (-1)
+#define DIMQ_ERR_BAD_SIZE (-2)
+#define DIMQ_ERR_BAD_DTYPE (-3)
+#define DIMQ_ERR_BAD_BITS (-4)
+#define DIMQ_ERR_BAD_QPARAMS (-5)   /* act_scale <= 0 or act_zp outside [0, 15] */
+#define DIMQ_ERR_BAD_SHAPE (-6)     /* channel / group / kernel geometry does not fit */
+#define DIMQ_ERR_UNSUPPORTED (-7)   /* the requested algorithm cannot take these arguments */
+#define DIMQ_ERR_ALIGNMENT (-8)
+#define DIMQ_ERR_DRIVER (-9)        /* a driver entry point (tensor-map encode) is unavailable or failed */
+#define DIMQ_ERR_DEVICE_TIMEOUT (-10) /* a bounded wait inside a kernel expired (see dimq_last_device_status) */
+#define DIMQ_ERR_TOO_LARGE (-11)
+
+/* element types of floating tensors */
+#define DIMQ_F32 0
+#define DIMQ_F16 1
+#define DIMQ_BF16 2
+
+/* kernel selection for the weight-only ops */
+#define DIMQ_ALGO_AUTO 0
+#define DIMQ_ALGO_GENERIC 1   /* exact fp32 SIMT kernel, any shape */
+#define DIMQ_ALGO_STREAM 2    /* small-M index-streaming kernel (HBM-bound regime) */
+#define DIMQ_ALGO_TCGEN05 3   /* TMA + in-pipeline dequantisation + tcgen05 MMA (tensor-core regime) */
+
+/* fused epilogues of the weight-only ops */
+#define DIMQ_EPI_NONE 0
+#define DIMQ_EPI_RELU 1
+#define DIMQ_EPI_GELU 2       /* exact (erf) GELU */
+
+DIMQ_API int dimq_version(void);
+DIMQ_API const char* dimq_status_string(int status);
+
+/* ---- index bit-packing ------------------------------------------------- */
+
+/* packed[j] = idx[2j] & 15 | (idx[2j+1] & 15) << 4; an odd tail leaves the high
+ * nibble zero.  `packed` holds (numel + 1) / 2 bytes.
+ * Replaces pack_u4_cuda, dimq_cuda_backend/csrc/dimq_pack.cu:52-67. */
+DIMQ_API int dimq_pack_u4(const uint8_t* indices, int64_t numel, uint8_t* packed, void* stream);
+
+/* indices[i] = nibble i of `packed` (even i -> low nibble).
+ * Replaces unpack_u4_cuda, dimq_cuda_backend/csrc/dimq_pack.cu:69-85. */
+DIMQ_API int dimq_unpack_u4(const uint8_t* packed, int64_t numel, uint8_t* indices, void* stream);
+
+/* bits in {1, 2, 3, 4, 8}: index j occupies bits [j*bits, (j+1)*bits) of a
+ * little-endian bit stream of (numel*bits + 7) / 8 bytes, tail bits zero.
+ * bits == 4 is dimq_pack_u4.  Generalises dimq_pack.cu:11-35 (the reference is
+ * 4-bit only). */
+DIMQ_API int dimq_pack_bits(const uint8_t* indices, int64_t numel, int bits, uint8_t* packed, void* stream);
+DIMQ_API int dimq_unpack_bits(const uint8_t* packed, int64_t numel, int bits, uint8_t* indices, void* stream);
+
+/* ---- W4A4 pieces --------------------------------------------------------- */
+
+/* out[i] = clamp(rint(float(x[i]) / act_scale) + act_zp, 0, 15), IEEE divide,
+ * round-half-even.  Replaces quantize_activation_u4_cuda, dimq_pack.cu:87-109. */
+DIMQ_API int dimq_quantize_activation_u4(const void* x, int x_dtype, int64_t numel, float act_scale, int act_zp,
+                                uint8_t* out, void* stream);
+
+/* table[g][w][a] = float(codebook[g][w]) * (act_scale * float(a - act_zp)), fp32,
+ * a in [0, 16).  groups == 1, entries == 16 is the reference op.
+ * Replaces build_product_table_cuda, dimq_cuda_backend/csrc/dimq_product_table.cu:29-46. */
+DIMQ_API int dimq_build_product_table(const void* codebook, int cb_dtype, int64_t groups, int entries,
+                             float act_scale, int act_zp, float* table, void* stream);
+
+/* y[m][n] = sum_k P[widx(n,k)][q(x[m][k])] + bias[n], fp32 out; the product
+ * table is built inside the kernel (no temporary).  x is [M, K] row-major,
+ * packed_w the u4 stream of the [N, K] index matrix (rows not padded), codebook
+ * has 16 entries.  bias may be NULL.
+ * Replaces linear_lut_cuda, dimq_cuda_backend/csrc/dimq_gemm_lut.cu:58-117. */
+DIMQ_API int dimq_linear_lut(const void* x, int x_dtype, const uint8_t* packed_w, const void* codebook, int cb_dtype,
+                    float act_scale, int act_zp, const void* bias, int bias_dtype, float* y, int64_t M,
+                    int64_t N, int64_t K, void* stream);
+
+/* Geometry of a 2-D convolution.  Strides are in ELEMENTS and describe where
+ * element (b, c, h, w) of the logical NCHW tensor lives, so both contiguous
+ * NCHW and channels_last (NHWC) storage are addressed without a copy. */
+typedef struct dimq_conv_geom {
+  int32_t batch, in_channels, in_h, in_w;
+  int32_t out_channels, in_channels_per_group, kernel_h, kernel_w;
+  int32_t stride_h, stride_w, pad_h, pad_w, dilation_h, dilation_w, groups;
+  int32_t out_h, out_w;               /* filled by dimq_conv_out_size */
+  int64_t x_stride[4];                /* b, c, h, w */
+  int64_t y_stride[4];                /* b, oc, oh, ow */
+} dimq_conv_geom;
+
+/* out = (in + 2*pad - dilation*(kernel-1) - 1) / stride + 1 for both axes
+ * (dimq_cuda_backend/csrc/dimq_conv2d_lut.cu:129-130).  Validates the geometry. */
+DIMQ_API int dimq_conv_out_size(dimq_conv_geom* geom);
+
+/* Direct W4A4 convolution over the product table, taps outside the image skipped.
+ * Replaces conv2d_lut_cuda, dimq_cuda_backend/csrc/dimq_conv2d_lut.cu:90-186. */
+DIMQ_API int dimq_conv2d_lut(const void* x, int x_dtype, const uint8_t* packed_w, const void* codebook, int cb_dtype,
+                    float act_scale, int act_zp, const void* bias, int bias_dtype, float* y,
+                    const dimq_conv_geom* geom, void* stream);
+
+/* ---- export: nearest-codeword assignment (+ packing) -------------------- */
+
+/* idx = argmin_k (float(w) - codebook[g][k])^2 in fp32, first minimum wins, a
+ * NaN distance beats every number; row r of the [rows, cols] weight uses
+ * codebook g = r / group_rows.  Writes unpacked uint8 indices (may be NULL)
+ * and/or the `bits`-wide packed stream of the flattened index matrix (may be
+ * NULL; entries <= 2^bits required).
+ * Replaces hard_quantize_weight, quant/dimq.py:197-221, and
+ * assign_weight_indices + pack_u4_indices, dimq_backend/export.py:24-55. */
+DIMQ_API int dimq_hard_quantize(const void* w, int w_dtype, int64_t rows, int64_t cols, const float* codebooks,
+                       int entries, int64_t group_rows, uint8_t* indices, uint8_t* packed, int bits,
+                       void* stream);
+
+/* ---- weight-only LUT GEMM / conv ---------------------------------------- */
+
+typedef struct dimq_wq_weight {
+  const uint8_t* packed;     /* `bits`-wide stream of the [N, K] (or [OC, ICg, KH, KW]) index tensor */
+  int32_t bits;              /* 2, 3, 4 or 8 */
+  const void* codebooks;     /* [groups, entries] */
+  int32_t cb_dtype;          /* DIMQ_F32 / DIMQ_F16 / DIMQ_BF16 */
+  int32_t entries;           /* <= 2^bits */
+  int64_t groups;
+  int64_t group_rows;        /* output rows (channels) per codebook */
+} dimq_wq_weight;
+
+/* y[m][n] = sum_k x[m][k] * codebooks[n / group_rows][idx(n, k)] + bias[n], then
+ * the epilogue, then + residual[m][n] (may be NULL).  fp32 accumulation.  The
+ * reference computes this as dequantize_packed_weight + F.linear
+ * (dimq_backend/reference.py:47-56, quant/dimq_wrapper.py:237-240). */
+DIMQ_API int dimq_linear_wq(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
+                   const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K, int epilogue,
+                   int algo, void* stream);
+
+/* Weight-only convolution; same contract as dimq_conv2d_lut without the
+ * activation quantiser (dimq_backend/reference.py:113-144 with x left in float,
+ * quant/dimq_wrapper.py:189-197).  y has y_dtype elements at geom->y_stride. */
+DIMQ_API int dimq_conv2d_wq(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
+                   const void* residual, void* y, int y_dtype, const dimq_conv_geom* geom, int epilogue,
+                   int algo, void* stream);
+
+/* Status word written by the last tcgen05 kernel on this thread's device that
+ * gave up a bounded wait (0 = none).  Reading it synchronises the device. */
+DIMQ_API int dimq_last_device_status(uint32_t* status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DIMQ_B200_H_ */

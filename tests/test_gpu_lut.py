@@ -1,0 +1,294 @@
+"""GPU parity of the LUT GEMM / conv kernels against the CPU oracle, through the C ABI.
+
+Tolerances: the W4A4 (product-table) ops are checked at the reference's own
+1e-5; the weight-only ops at max-abs 1e-2 and relative L2 1e-3 against the
+dequantise-then-fp32-linear/conv oracle on the same (bf16/fp16-rounded) inputs.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import c_oracle
+from oracle import dimq_oracle as o
+from tests._cases import bf16_round, make_weight
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS = 1e-2
+REL_L2 = 1e-3
+
+
+@pytest.fixture(scope="module")
+def ops(cuda_device):
+    from dimq_b200 import ops as _ops
+
+    _ops.require_extension()
+    return _ops
+
+
+def _cuda(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+def _assert_close(y: torch.Tensor, y_ref: np.ndarray, what: str = ""):
+    assert tuple(y.shape) == tuple(y_ref.shape), (y.shape, y_ref.shape)
+    max_abs, rel = o.parity_metrics(y.float().cpu().numpy(), y_ref)
+    assert max_abs <= MAX_ABS and rel <= REL_L2, f"{what}: max_abs={max_abs:.3e} rel_l2={rel:.3e}"
+
+
+# ---- W4A4 product-table ops (the reference's own CUDA tests) ---------------------
+
+def test_linear_lut_reference_case(ops, golden):
+    # dimq_cuda_backend/tests/test_cuda_ops.py:51-64
+    y = ops.dimq_linear_lut(_cuda(golden["lin_x"]), _cuda(golden["lin_packed"]), _cuda(golden["lin_cb"]), 0.2, 7,
+                            _cuda(golden["lin_bias"]), 6, 11)
+    assert y.dtype == torch.float32
+    np.testing.assert_allclose(y.cpu().numpy(), golden["lin_y_lut"], rtol=1e-5, atol=1e-5)
+    y = ops.dimq_linear_lut(_cuda(golden["lin_x"]), _cuda(golden["lin_packed"]), _cuda(golden["lin_cb"]), 0.2, 7,
+                            None, 6, 11)
+    np.testing.assert_allclose(y.cpu().numpy(), golden["lin_y_nobias"], rtol=1e-5, atol=1e-5)
+    y = ops.dimq_linear_lut(_cuda(golden["linb_x"]), _cuda(golden["linb_packed"]), _cuda(golden["linb_cb"]), 0.3, 8,
+                            None, 24, 64)
+    assert y.shape == (2, 5, 24)
+    np.testing.assert_allclose(y.cpu().numpy(), golden["linb_y_lut"], rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 1, 1), (5, 33, 17), (70, 129, 45), (256, 768, 96)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_linear_lut_matches_c_oracle(ops, m, k, n, dtype):
+    rng = np.random.default_rng(m * 31 + k)
+    x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(dtype)
+    widx = rng.integers(0, 16, size=(n, k), dtype=np.uint8)
+    packed = o.pack_u4(widx)
+    cb = np.sort(rng.standard_normal(16).astype(np.float32) * 0.1)
+    bias = rng.standard_normal(n).astype(np.float32)
+    want = c_oracle.linear_lut_a4(x.float().numpy(), packed, cb, 0.25, 6, n, k, bias)
+    got = ops.dimq_linear_lut(x.cuda(), _cuda(packed), _cuda(cb), 0.25, 6, _cuda(bias, torch.float16), n, k)
+    want_h = c_oracle.linear_lut_a4(x.float().numpy(), packed, cb, 0.25, 6, n, k, bias.astype(np.float16).astype(np.float32))
+    np.testing.assert_allclose(got.cpu().numpy(), want_h, rtol=1e-5, atol=2e-5)
+    del want
+
+
+def test_linear_lut_argument_checks(ops, golden):
+    x, pw, cb = _cuda(golden["lin_x"]), _cuda(golden["lin_packed"]), _cuda(golden["lin_cb"])
+    with pytest.raises(RuntimeError):
+        ops.dimq_linear_lut(x, pw, cb, 0.0, 7, None, 6, 11)
+    with pytest.raises(RuntimeError):
+        ops.dimq_linear_lut(x, pw, cb, 0.2, 16, None, 6, 11)
+    with pytest.raises(RuntimeError):
+        ops.dimq_linear_lut(x, pw, cb[:8], 0.2, 7, None, 6, 11)
+    with pytest.raises(RuntimeError):
+        ops.dimq_linear_lut(x, pw, cb, 0.2, 7, None, 60, 11)  # packed too small
+    with pytest.raises(RuntimeError):
+        ops.dimq_linear_lut(x, pw, cb, 0.2, 7, None, 6, 12)   # last dim mismatch
+    with pytest.raises(RuntimeError):
+        ops.dimq_linear_lut(x, pw.to(torch.int32), cb, 0.2, 7, None, 6, 11)
+    with pytest.raises(NotImplementedError):
+        torch.ops.dimq.linear_lut(x.cpu(), pw.cpu(), cb.cpu(), 0.2, 7, None, 6, 11)
+
+
+def test_conv2d_lut_reference_case(ops, golden):
+    # dimq_cuda_backend/tests/test_cuda_ops.py:67-93
+    y = ops.dimq_conv2d_lut(_cuda(golden["conv_x"]), _cuda(golden["conv_packed"]), _cuda(golden["conv_cb"]), 0.25, 7,
+                            _cuda(golden["conv_bias"]), (5, 3, 3, 3), (2, 1), (1, 1), (1, 1), 1)
+    assert y.dtype == torch.float32
+    np.testing.assert_allclose(y.cpu().numpy(), golden["conv_y_deq"], rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(y.cpu().numpy(), golden["conv_y_lut"], rtol=1e-5, atol=1e-5)
+    y = ops.dimq_conv2d_lut(_cuda(golden["convg_x"]), _cuda(golden["convg_packed"]), _cuda(golden["conv_cb"]), 0.25,
+                            7, None, (6, 2, 3, 2), (1, 2), (2, 1), (2, 1), 2)
+    np.testing.assert_allclose(y.cpu().numpy(), golden["convg_y_deq"], rtol=1e-5, atol=1e-5)
+    # channels_last storage is read in place and the result comes back channels_last
+    x_cl = _cuda(golden["conv_x"]).contiguous(memory_format=torch.channels_last)
+    y_cl = ops.dimq_conv2d_lut(x_cl, _cuda(golden["conv_packed"]), _cuda(golden["conv_cb"]), 0.25, 7,
+                               _cuda(golden["conv_bias"]), (5, 3, 3, 3), (2, 1), (1, 1), (1, 1), 1)
+    assert y_cl.is_contiguous(memory_format=torch.channels_last)
+    np.testing.assert_allclose(y_cl.cpu().numpy(), golden["conv_y_deq"], rtol=1e-5, atol=1e-5)
+    with pytest.raises(RuntimeError):
+        ops.dimq_conv2d_lut(_cuda(golden["conv_x"]), _cuda(golden["conv_packed"]), _cuda(golden["conv_cb"]), 0.25, 7,
+                            None, (5, 4, 3, 3), (2, 1), (1, 1), (1, 1), 1)
+    empty = ops.dimq_conv2d_lut(_cuda(golden["conv_x"])[:0], _cuda(golden["conv_packed"]), _cuda(golden["conv_cb"]),
+                                0.25, 7, None, (5, 3, 3, 3), (2, 1), (1, 1), (1, 1), 1)
+    assert empty.shape == (0, 5, 3, 7)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_conv2d_lut_matches_c_oracle(ops, dtype):
+    rng = np.random.default_rng(21)
+    x = torch.from_numpy(rng.standard_normal((3, 8, 13, 11)).astype(np.float32)).to(dtype)
+    widx = rng.integers(0, 16, size=(12, 4, 3, 5), dtype=np.uint8)
+    packed = o.pack_u4(widx)
+    cb = np.sort(rng.standard_normal(16).astype(np.float32) * 0.2)
+    bias = rng.standard_normal(12).astype(np.float32)
+    kw = dict(stride=(2, 1), padding=(1, 2), dilation=(1, 2), groups=2)
+    want = c_oracle.conv2d_lut_a4(x.float().numpy(), packed, cb, 0.3, 5, widx.shape, bias, **kw)
+    got = ops.dimq_conv2d_lut(x.cuda(), _cuda(packed), _cuda(cb), 0.3, 5, _cuda(bias), widx.shape, kw["stride"],
+                              kw["padding"], kw["dilation"], kw["groups"])
+    np.testing.assert_allclose(got.cpu().numpy(), want, rtol=1e-5, atol=2e-5)
+
+
+# ---- weight-only GEMM --------------------------------------------------------------
+
+def test_linear_wq_golden(ops, golden):
+    for algo in ("generic", None):
+        y = ops.dimq_linear_wq(_cuda(golden["wq_lin_x"]), _cuda(golden["wq_lin_packed"]), _cuda(golden["wq_lin_cb"]),
+                               _cuda(golden["wq_lin_bias"]), 48, 96, bits=4, algo=algo)
+        np.testing.assert_allclose(y.cpu().numpy(), golden["wq_lin_y"], rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4, 8])
+@pytest.mark.parametrize("m,k,n,grp", [(3, 37, 29, None), (40, 100, 70, 16), (1, 64, 8, 1)])
+def test_linear_wq_generic_odd_shapes(ops, bits, m, k, n, grp):
+    case = make_weight(n, k, bits, seed=bits * 100 + m, group_rows=grp, cb_dtype=np.float32)
+    rng = np.random.default_rng(m)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    want = o.linear_wq(x, case["packed"], case["codebooks"], bits, n, k, bias, case["group_rows"])
+    got = ops.dimq_linear_wq(_cuda(x), _cuda(case["packed"]), _cuda(case["codebooks"]), _cuda(bias), n, k, bits=bits,
+                             group_rows=case["group_rows"], algo="generic")
+    np.testing.assert_allclose(got.cpu().numpy(), want, rtol=1e-5, atol=1e-5)
+
+
+def test_linear_wq_config1_fp32(ops):
+    """Single DIMQ Linear 768 -> 3072, fp32 activations [8*197, 768], 4-bit per-layer quantile codebook."""
+    case = make_weight(3072, 768, 4, seed=0, cb_dtype=np.float32)
+    x = np.random.default_rng(0).standard_normal((8 * 197, 768)).astype(np.float32)
+    want = o.linear_wq(x, case["packed"], case["codebooks"], 4, 3072, 768)
+    got = ops.dimq_linear_wq(_cuda(x).view(8, 197, 768), _cuda(case["packed"]), _cuda(case["codebooks"]), None, 3072,
+                             768, bits=4)
+    assert got.shape == (8, 197, 3072)
+    _assert_close(got.view(-1, 3072), want, "config 1")
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4, 8])
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 7, 8])
+def test_linear_wq_stream_small_m(ops, bits, m):
+    n, k = 520, 1024
+    case = make_weight(n, k, bits, seed=bits + 10 * m, group_rows=128)
+    x = bf16_round(np.random.default_rng(m).standard_normal((m, k)).astype(np.float32))
+    bias = np.random.default_rng(m + 1).standard_normal(n).astype(np.float32)
+    want = o.linear_wq(x, case["packed"], case["codebooks"], bits, n, k, bias, 128)
+    got = ops.dimq_linear_wq(_cuda(x, torch.bfloat16), _cuda(case["packed"]), _cuda(case["codebooks"], torch.float16),
+                             _cuda(bias), n, k, bits=bits, group_rows=128, algo="stream")
+    _assert_close(got, want, f"stream bits={bits} m={m}")
+    np.testing.assert_allclose(got.cpu().numpy(), want, rtol=2e-4, atol=2e-4)
+    # K = 768: a row is 24 units, fewer than one per lane
+    case = make_weight(n, 768, bits, seed=bits, group_rows=None)
+    x = bf16_round(np.random.default_rng(m).standard_normal((m, 768)).astype(np.float32))
+    want = o.linear_wq(x, case["packed"], case["codebooks"], bits, n, 768)
+    got = ops.dimq_linear_wq(_cuda(x, torch.bfloat16), _cuda(case["packed"]), _cuda(case["codebooks"]), None, n, 768,
+                             bits=bits, algo="stream")
+    np.testing.assert_allclose(got.cpu().numpy(), want, rtol=2e-4, atol=2e-4)
+
+
+TC_SHAPES = [(192, 64, 128), (200, 128, 130), (577, 768, 384), (64, 1024, 256), (16, 256, 128)]
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4, 8])
+@pytest.mark.parametrize("m,k,n", TC_SHAPES)
+def test_linear_wq_tcgen05(ops, bits, m, k, n):
+    grp = None if bits == 8 else 128
+    case = make_weight(n, k, bits, seed=bits * 13 + m, group_rows=grp)
+    rng = np.random.default_rng(m + k)
+    x = bf16_round(rng.standard_normal((m, k)).astype(np.float32))
+    bias = rng.standard_normal(n).astype(np.float32)
+    want = o.linear_wq(x, case["packed"], case["codebooks"], bits, n, k, bias, case["group_rows"])
+    got = ops.dimq_linear_wq(_cuda(x, torch.bfloat16), _cuda(case["packed"]), _cuda(case["codebooks"], torch.float16),
+                             _cuda(bias), n, k, bits=bits, group_rows=grp, algo="tcgen05")
+    assert ops.last_device_status() == 0
+    _assert_close(got, want, f"tcgen05 bits={bits} {m}x{k}x{n}")
+
+
+@pytest.mark.parametrize("x_dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("y_dtype", [torch.float32, torch.bfloat16])
+def test_linear_wq_tcgen05_dtypes_epilogues(ops, x_dtype, y_dtype):
+    m, k, n = 300, 256, 200
+    case = make_weight(n, k, 4, seed=3)
+    rng = np.random.default_rng(8)
+    x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(x_dtype)
+    bias = rng.standard_normal(n).astype(np.float32)
+    res = torch.from_numpy(rng.standard_normal((m, n)).astype(np.float32)).to(y_dtype)
+    lin = o.linear_wq(x.float().numpy(), case["packed"], case["codebooks"], 4, n, k, bias)
+    for epi, fn in (("relu", lambda v: np.maximum(v, 0)), ("gelu", None), (None, lambda v: v)):
+        if fn is None:
+            want = torch.nn.functional.gelu(torch.from_numpy(lin)).numpy()
+        else:
+            want = fn(lin)
+        want = want + res.float().numpy()
+        got = ops.dimq_linear_wq(x.cuda(), _cuda(case["packed"]), _cuda(case["codebooks"], torch.float16), _cuda(bias),
+                                 n, k, bits=4, out_dtype=y_dtype, epilogue=epi, residual=res.cuda(), algo="tcgen05")
+        assert got.dtype == y_dtype
+        tol = 2e-2 if y_dtype == torch.bfloat16 else 1e-2
+        max_abs, rel = o.parity_metrics(got.float().cpu().numpy(), want)
+        assert max_abs <= tol * 3 and rel <= (5e-3 if y_dtype == torch.bfloat16 else REL_L2), (epi, max_abs, rel)
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4])
+@pytest.mark.parametrize("k,n", [(1024, 4096), (4096, 1024)])
+@pytest.mark.parametrize("m", [1, 4, 16, 64, 256, 4096])
+def test_linear_wq_m_sweep_auto_dispatch(ops, bits, k, n, m):
+    """The M-sweep of the regime dispatch on ViT-L shapes, bf16 activations, per-layer codebooks."""
+    case = _sweep_case(bits, k, n)
+    x = bf16_round(np.random.default_rng(m).standard_normal((m, k)).astype(np.float32))
+    want = o.linear_wq(x, case["packed"], case["codebooks"], bits, n, k)
+    got = ops.dimq_linear_wq(_cuda(x, torch.bfloat16), case["packed_cuda"], case["cb_cuda"], None, n, k, bits=bits)
+    assert ops.last_device_status() == 0
+    _assert_close(got, want, f"sweep bits={bits} m={m} {k}->{n}")
+
+
+_SWEEP_CACHE: dict = {}
+
+
+def _sweep_case(bits, k, n):
+    key = (bits, k, n)
+    if key not in _SWEEP_CACHE:
+        case = make_weight(n, k, bits, seed=bits)
+        case["packed_cuda"] = _cuda(case["packed"])
+        case["cb_cuda"] = _cuda(case["codebooks"], torch.float16)
+        _SWEEP_CACHE[key] = case
+    return _SWEEP_CACHE[key]
+
+
+def test_linear_wq_linearity_at_full_size(ops):
+    """Size-independent property at M = 4096: y(a*x1 + x2) = a*y(x1) + y(x2) up to rounding."""
+    case = _sweep_case(4, 1024, 4096)
+    rng = np.random.default_rng(77)
+    x1 = torch.from_numpy(rng.standard_normal((4096, 1024)).astype(np.float32)).cuda()
+    x2 = torch.from_numpy(rng.standard_normal((4096, 1024)).astype(np.float32)).cuda()
+    f = lambda t: ops.dimq_linear_wq(t.to(torch.float16), case["packed_cuda"], case["cb_cuda"], None, 4096, 1024, bits=4)
+    y1, y2, y12 = f(x1), f(x2), f(2.0 * x1 + x2)
+    max_abs, rel = o.parity_metrics(y12.cpu().numpy(), (2.0 * y1 + y2).cpu().numpy())
+    assert rel <= 2e-3, (max_abs, rel)
+
+
+# ---- weight-only conv ------------------------------------------------------------------
+
+def test_conv2d_wq_golden(ops, golden):
+    x = _cuda(golden["wq_conv_x"])
+    for stride, key in (((1, 1), "wq_conv_y"), ((2, 2), "wq_conv_y_s2")):
+        y = ops.dimq_conv2d_wq(x, _cuda(golden["wq_conv_packed"]), _cuda(golden["wq_conv_cb"]), None, (8, 4, 3, 3),
+                               stride, (1, 1), (1, 1), 1, bits=4)
+        np.testing.assert_allclose(y.cpu().numpy(), golden[key], rtol=1e-5, atol=1e-5)
+        y = ops.dimq_conv2d_wq(x.contiguous(memory_format=torch.channels_last), _cuda(golden["wq_conv_packed"]),
+                               _cuda(golden["wq_conv_cb"]), None, (8, 4, 3, 3), stride, (1, 1), (1, 1), 1, bits=4)
+        assert y.is_contiguous(memory_format=torch.channels_last)
+        np.testing.assert_allclose(y.cpu().numpy(), golden[key], rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4, 8])
+def test_conv2d_wq_generic_per_channel_codebooks(ops, bits):
+    rng = np.random.default_rng(bits)
+    oc, icg, kh, kw = 16, 6, 3, 3
+    case = make_weight(oc, icg * kh * kw, bits, seed=bits, group_rows=1, std=(2.0 / (icg * 9)) ** 0.5,
+                       cb_dtype=np.float32)
+    x = np.maximum(rng.standard_normal((2, 12, 9, 10)).astype(np.float32), 0)
+    bias = rng.standard_normal(oc).astype(np.float32)
+    kwargs = dict(stride=(1, 2), padding=(1, 0), dilation=(1, 1), groups=2)
+    want = o.conv2d_wq(x, case["packed"], case["codebooks"], bits, (oc, icg, kh, kw), bias, group_rows=1, **kwargs)
+    got = ops.dimq_conv2d_wq(_cuda(x), _cuda(case["packed"]), _cuda(case["codebooks"]), _cuda(bias),
+                             (oc, icg, kh, kw), kwargs["stride"], kwargs["padding"], kwargs["dilation"], 2, bits=bits,
+                             group_rows=1, epilogue="relu")
+    np.testing.assert_allclose(got.cpu().numpy(), np.maximum(want, 0), rtol=1e-4, atol=1e-4)
