@@ -17,7 +17,7 @@ int launch_linear_wq_stream(const void* x, int x_dtype, const dimq_wq_weight* w,
 bool tc_supported(const void* x, int x_dtype, const dimq_wq_weight* w, int64_t M, int64_t N, int64_t K);
 int launch_linear_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
                         const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K, int epilogue,
-                        int w_fmt, cudaStream_t st);
+                        int precision, cudaStream_t st);
 int read_device_status(uint32_t* status);
 }  // namespace dimq
 
@@ -62,9 +62,6 @@ extern "C" int dimq_linear_wq(const void* x, int x_dtype, const dimq_wq_weight* 
   if (M == 0) return DIMQ_OK;
   if (x == nullptr || y == nullptr) return DIMQ_ERR_NULL_POINTER;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // operand format of the dequantised weight on the tensor cores: fp16 keeps 11
-  // significand bits of the codeword (bf16 would keep 8)
-  const int w_fmt = 0;
   if (algo == DIMQ_ALGO_AUTO) {
     if (stream_supported(w, M, N, K)) algo = DIMQ_ALGO_STREAM;
     else if (M > 8 && tc_supported(x, x_dtype, w, M, N, K)) algo = DIMQ_ALGO_TCGEN05;
@@ -76,8 +73,8 @@ extern "C" int dimq_linear_wq(const void* x, int x_dtype, const dimq_wq_weight* 
     case DIMQ_ALGO_STREAM:
       return launch_linear_wq_stream(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, st);
     case DIMQ_ALGO_TCGEN05:
-      return launch_linear_wq_tc(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, w_fmt, st);
-    case DIMQ_ALGO_TCGEN05 + 100:  // tcgen05 with the weight operand rounded to bf16 (measurement only)
+      return launch_linear_wq_tc(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, 0, st);
+    case DIMQ_ALGO_TCGEN05 + 100:  // codewords rounded to the activations' 16-bit format, never split (measurement only)
       return launch_linear_wq_tc(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, 1, st);
     default:
       return DIMQ_ERR_UNSUPPORTED;

@@ -30,7 +30,7 @@ constexpr int kTileW = 128;      // weight rows per tile (UMMA M)
 constexpr int kTileX = 192;      // activation rows per tile (UMMA N)
 constexpr int kBlockK = 64;      // k per stage: 128 bytes of 16-bit elements
 constexpr int kXStages = 6;      // shared-memory stages of the activation tile
-constexpr int kWStages = 4;      // tensor-memory stages of the dequantised weight tile
+constexpr int kWStages = 4;      // tensor-memory stages of the dequantised weight tile (2 in split mode)
 constexpr int kAccStages = 2;    // accumulator buffers
 constexpr int kTmemCols = 512;
 constexpr int kAccCol = 0;                         // accumulators: columns [0, 2*kTileX)
@@ -40,7 +40,7 @@ constexpr int kXStageBytes = kTileX * kBlockK * 2;  // 24 KB
 constexpr int kNumDequantWarps = 8;
 constexpr int kNumEpilogueWarps = 4;
 constexpr int kThreads = (2 + kNumEpilogueWarps + kNumDequantWarps) * 32;
-constexpr int kMaxTableBytes = 64 * 1024;
+constexpr int kMaxTableBytes = 40 * 1024;
 
 struct TcParams {
   const uint8_t* packed;      // [N][K] indices, `bits` wide, rows contiguous
@@ -54,7 +54,10 @@ struct TcParams {
   int y_dtype;
   int64_t M, N, K;
   int epilogue;
-  int w_fmt;                  // operand format of the dequantised weight: 0 fp16, 1 bf16
+  int w_fmt;                  // operand format of the dequantised weight: 0 fp16, 1 bf16.  In split
+                              // mode (bf16 only) every codeword c is carried as hi = bf16(c) and
+                              // lo = bf16(c - hi) and each k-step issues two MMAs, so the product is
+                              // exact to ~2^-17 although the operands are bf16.
   uint32_t idesc;
   int m_tiles, n_tiles;
 };
@@ -100,9 +103,97 @@ __device__ __forceinline__ uint32_t to_operand16(float v, int w_fmt) {
   return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(v)));
 }
 
-// PAIR: the table holds, per group, 4^BITS words, entry v = {C[v & mask], C[v >> BITS]} as two
-// 16-bit operands.  Otherwise it holds 2^BITS 16-bit operands per group.
-template <int BITS, bool PAIR>
+
+// Epilogue of one 32-column chunk: thread = output feature n, r[j] = accumulator of activation row
+// (m_first + j).  yp / rp point at element [m_first][n]; a warp store covers 32 consecutive n.
+template <typename T, bool RES>
+__device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], T* __restrict__ yp, const T* __restrict__ rp,
+                                            int64_t ld, int rows, float bias, int epilogue) {
+  if (rows >= 32) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      float v = apply_epilogue(__uint_as_float(r[j]) + bias, epilogue);
+      if (RES) v += to_float<T>(rp[j * ld]);
+      yp[j * ld] = from_float<T>(v);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (j < rows) {
+        float v = apply_epilogue(__uint_as_float(r[j]) + bias, epilogue);
+        if (RES) v += to_float<T>(rp[j * ld]);
+        yp[j * ld] = from_float<T>(v);
+      }
+    }
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void store_chunk_t(const uint32_t (&r)[32], void* y, const void* res, int64_t off,
+                                              int64_t ld, int rows, float bias, int epilogue) {
+  if (res != nullptr)
+    store_chunk<T, true>(r, static_cast<T*>(y) + off, static_cast<const T*>(res) + off, ld, rows, bias, epilogue);
+  else
+    store_chunk<T, false>(r, static_cast<T*>(y) + off, nullptr, ld, rows, bias, epilogue);
+}
+
+__device__ __forceinline__ void cp_async(uint32_t dst, const void* src, int bytes) {
+  if (bytes == 16)
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+  else if (bytes == 8)
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+  else
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Prefetch ring of packed-index units: one slot per dequantisation thread and stage in flight.
+constexpr int kIdxPrefetch = 4;
+template <int BITS>
+struct IdxSlot { static constexpr int kBytes = BITS == 8 ? 32 : 16; };
+
+template <int BITS>
+__device__ __forceinline__ void issue_unit(uint32_t dst, const uint8_t* src) {
+  if constexpr (BITS == 4) { cp_async(dst, src, 16); }
+  else if constexpr (BITS == 2) { cp_async(dst, src, 8); }
+  else if constexpr (BITS == 8) { cp_async(dst, src, 16); cp_async(dst + 16, src + 16, 16); }
+  else {
+#pragma unroll
+    for (int i = 0; i < BITS; ++i) cp_async(dst + 4 * i, src + 4 * i, 4);
+  }
+}
+
+template <int BITS>
+__device__ __forceinline__ void read_unit(const unsigned char* slot, uint32_t (&w)[BITS]) {
+  if constexpr (BITS == 8) {
+    const uint4 q0 = *reinterpret_cast<const uint4*>(slot);
+    const uint4 q1 = *reinterpret_cast<const uint4*>(slot + 16);
+    w[0] = q0.x; w[1] = q0.y; w[2] = q0.z; w[3] = q0.w; w[4] = q1.x; w[5] = q1.y; w[6] = q1.z; w[7] = q1.w;
+  } else {
+    const uint4 q = *reinterpret_cast<const uint4*>(slot);
+    const uint32_t v[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < BITS; ++i) w[i] = v[i];
+  }
+}
+
+// 32-bit words of lookup table per codebook group.
+//   PAIR : entry v (two adjacent indices, 2*BITS bits) -> {C[v & mask], C[v >> BITS]} as two 16-bit
+//          operands in one word; in split mode two words {hi pair, lo pair}.
+//   !PAIR: entry e -> one 16-bit operand (two per word); in split mode one word {hi | lo << 16}.
+__host__ __device__ constexpr int table_words(int bits, bool pair, bool split) {
+  return pair ? (1 << (2 * bits)) * (split ? 2 : 1) : (split ? (1 << bits) : (1 << bits) / 2);
+}
+
+__device__ __forceinline__ void split_bf16(float c, uint32_t& hi, uint32_t& lo) {
+  const __nv_bfloat16 h = __float2bfloat16_rn(c);
+  hi = __bfloat16_as_ushort(h);
+  lo = __bfloat16_as_ushort(__float2bfloat16_rn(c - __bfloat162float(h)));
+}
+
+template <int BITS, bool PAIR, bool SPLIT>
 __global__ void __launch_bounds__(kThreads, 1)
 linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -110,13 +201,17 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* x_stage = smem;
   SharedHeader* hdr = reinterpret_cast<SharedHeader*>(smem + kXStages * kXStageBytes);
-  uint32_t* table = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(hdr) + 256);
+  unsigned char* idx_ring = reinterpret_cast<unsigned char*>(hdr) + 256;  // [kIdxPrefetch][256 threads][slot]
+  constexpr int kRingBytes = kIdxPrefetch * kNumDequantWarps * 32 * IdxSlot<BITS>::kBytes;
+  uint32_t* table = reinterpret_cast<uint32_t*>(idx_ring + kRingBytes);
   static_assert(sizeof(SharedHeader) <= 256, "header");
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int num_tiles = p.m_tiles * p.n_tiles;
   const int k_blocks = static_cast<int>(p.K / kBlockK);
+  constexpr int kWStageCols = SPLIT ? kBlockK : kBlockK / 2;   // TMEM columns per weight stage
+  constexpr uint32_t kWStagesUsed = SPLIT ? kWStages / 2 : kWStages;
 
   // ---- one-time setup ---------------------------------------------------------
   if (tid == 0) {
@@ -133,21 +228,34 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
   }
   {
     constexpr uint32_t mask = (1u << BITS) - 1u;
-    constexpr int per_group = PAIR ? (1 << (2 * BITS)) : (1 << BITS) / 2;  // 32-bit words per group
-    const int total = static_cast<int>(p.groups) * per_group;
+    constexpr int n_entries = PAIR ? (1 << (2 * BITS)) : (1 << BITS);
+    const int total = static_cast<int>(p.groups) * n_entries;
+    auto cw = [&](int g, int e) -> float {
+      return e < p.entries ? load_as_float(p.codebooks, p.cb_dtype, static_cast<int64_t>(g) * p.entries + e) : 0.0f;
+    };
     for (int i = tid; i < total; i += kThreads) {
-      const int g = i / per_group, v = i % per_group;
-      uint32_t lo, hi;
+      const int g = i / n_entries, v = i % n_entries;
       if (PAIR) {
-        const int e0 = v & mask, e1 = v >> BITS;
-        lo = e0 < p.entries ? to_operand16(load_as_float(p.codebooks, p.cb_dtype, (int64_t)g * p.entries + e0), p.w_fmt) : 0u;
-        hi = e1 < p.entries ? to_operand16(load_as_float(p.codebooks, p.cb_dtype, (int64_t)g * p.entries + e1), p.w_fmt) : 0u;
+        const float c0 = cw(g, v & mask), c1 = cw(g, v >> BITS);
+        if (SPLIT) {
+          uint32_t h0, l0, h1, l1;
+          split_bf16(c0, h0, l0);
+          split_bf16(c1, h1, l1);
+          table[2 * i] = h0 | (h1 << 16);
+          table[2 * i + 1] = l0 | (l1 << 16);
+        } else {
+          table[i] = to_operand16(c0, p.w_fmt) | (to_operand16(c1, p.w_fmt) << 16);
+        }
       } else {
-        const int e0 = 2 * v, e1 = 2 * v + 1;
-        lo = e0 < p.entries ? to_operand16(load_as_float(p.codebooks, p.cb_dtype, (int64_t)g * p.entries + e0), p.w_fmt) : 0u;
-        hi = e1 < p.entries ? to_operand16(load_as_float(p.codebooks, p.cb_dtype, (int64_t)g * p.entries + e1), p.w_fmt) : 0u;
+        const float c = cw(g, v);
+        if (SPLIT) {
+          uint32_t h, l;
+          split_bf16(c, h, l);
+          table[i] = h | (l << 16);
+        } else {
+          reinterpret_cast<uint16_t*>(table)[i] = static_cast<uint16_t>(to_operand16(c, p.w_fmt));
+        }
       }
-      table[i] = lo | (hi << 16);
     }
   }
   tc_fence_before();
@@ -199,17 +307,19 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
           if (!mbar_wait(smem_u32(&hdr->w_full[ws]), wph, abort_flag, 0x400u | ws)) { ok = false; break; }
           tc_fence_after();
           const uint64_t b_desc = make_smem_desc_sw128(smem_u32(x_stage + xs * kXStageBytes));
-          const uint32_t a_tmem = tmem_base + kWCol + ws * (kBlockK / 2);
+          const uint32_t a_tmem = tmem_base + kWCol + ws * kWStageCols;
 #pragma unroll
           for (int j = 0; j < kBlockK / 16; ++j) {
             // advance 16 k: 32 bytes inside the swizzled row (encoded >> 4), 8 TMEM columns
             mma_f16_ts(d_tmem, a_tmem + j * 8, b_desc + static_cast<uint64_t>(j * 2), p.idesc,
                        (kb > 0 || j > 0) ? 1u : 0u);
+            if (SPLIT)
+              mma_f16_ts(d_tmem, a_tmem + kBlockK / 2 + j * 8, b_desc + static_cast<uint64_t>(j * 2), p.idesc, 1u);
           }
           mma_commit(smem_u32(&hdr->x_empty[xs]));
           mma_commit(smem_u32(&hdr->w_empty[ws]));
           if (++xs == kXStages) { xs = 0; xph ^= 1u; }
-          if (++ws == kWStages) { ws = 0; wph ^= 1u; }
+          if (++ws == kWStagesUsed) { ws = 0; wph ^= 1u; }
         }
         if (!ok) break;
         mma_commit(smem_u32(&hdr->d_full[as]));
@@ -242,17 +352,14 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
           tc_fence_before();
           mbar_arrive(smem_u32(&hdr->d_empty[as]));
         }
-        if (n_ok) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int64_t m = m0 + c * 32 + j;
-            if (m < p.M) {
-              float v = apply_epilogue(__uint_as_float(r[j]) + bias, p.epilogue);
-              const int64_t o = m * p.N + n;
-              if (p.residual != nullptr) v += load_as_float(p.residual, p.y_dtype, o);
-              store_from_float(p.y, p.y_dtype, o, v);
-            }
-          }
+        const int64_t m_first = m0 + c * 32;
+        const int64_t rows64 = p.M - m_first;
+        const int rows = rows64 >= 32 ? 32 : static_cast<int>(rows64);
+        if (n_ok && rows > 0) {
+          const int64_t off = m_first * p.N + n;
+          if (p.y_dtype == DIMQ_BF16) store_chunk_t<__nv_bfloat16>(r, p.y, p.residual, off, p.N, rows, bias, p.epilogue);
+          else if (p.y_dtype == DIMQ_F16) store_chunk_t<__half>(r, p.y, p.residual, off, p.N, rows, bias, p.epilogue);
+          else store_chunk_t<float>(r, p.y, p.residual, off, p.N, rows, bias, p.epilogue);
         }
       }
       if (++as == kAccStages) { as = 0; aph ^= 1u; }
@@ -264,7 +371,7 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
     const int half = dw >> 2;                       // which 32 of the stage's 64 k
     const int row_in_tile = quarter * 32 + lane;
     const int64_t row_bytes = p.K * BITS / 8;
-    constexpr int per_group = PAIR ? (1 << (2 * BITS)) : (1 << BITS) / 2;
+    constexpr int per_group = table_words(BITS, PAIR, SPLIT);
     const int64_t total_iters = static_cast<int64_t>((num_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x) * k_blocks;
     auto unit_ptr = [&](int64_t it) -> const uint8_t* {
       const int t = blockIdx.x + static_cast<int>(it / k_blocks) * gridDim.x;
@@ -274,21 +381,52 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
       return p.packed + row * row_bytes + static_cast<int64_t>(kb) * (8 * BITS) + half * (4 * BITS);
     };
     uint32_t ws = 0, wph = 0;
-    uint32_t nxt[BITS];
-    if (total_iters > 0) load_unit<BITS>(unit_ptr(0), nxt);
-    for (int64_t it = 0; it < total_iters; ++it) {
-      uint32_t cur[BITS];
+    const int dq_tid = tid - (2 + kNumEpilogueWarps) * 32;  // 0..255
+    constexpr int kSlot = IdxSlot<BITS>::kBytes;
+    unsigned char* my_ring = idx_ring + dq_tid * kSlot;           // slot s at my_ring + s * 256 * kSlot
+    constexpr int kRingStride = kNumDequantWarps * 32 * kSlot;
+    // the packed indices of stage `it` are fetched kIdxPrefetch - 1 stages ahead (cp.async, own slot)
 #pragma unroll
-      for (int i = 0; i < BITS; ++i) cur[i] = nxt[i];
-      if (it + 1 < total_iters) load_unit<BITS>(unit_ptr(it + 1), nxt);
+    for (int s0 = 0; s0 < kIdxPrefetch - 1; ++s0) {
+      if (s0 < total_iters) issue_unit<BITS>(smem_u32(my_ring + s0 * kRingStride), unit_ptr(s0));
+      cp_async_commit();
+    }
+    for (int64_t it = 0; it < total_iters; ++it) {
+      {
+        const int64_t ahead = it + kIdxPrefetch - 1;
+        if (ahead < total_iters)
+          issue_unit<BITS>(smem_u32(my_ring + static_cast<int>(ahead % kIdxPrefetch) * kRingStride), unit_ptr(ahead));
+        cp_async_commit();
+      }
+      cp_async_wait<kIdxPrefetch - 1>();
+      uint32_t cur[BITS];
+      read_unit<BITS>(my_ring + static_cast<int>(it % kIdxPrefetch) * kRingStride, cur);
       const int t = blockIdx.x + static_cast<int>(it / k_blocks) * gridDim.x;
       int64_t row = static_cast<int64_t>(t / p.m_tiles) * kTileW + row_in_tile;
       if (row >= p.N) row = p.N - 1;
       const uint32_t* tbl = table + (row / p.group_rows) * per_group;
       uint32_t out[16];
+      uint32_t out_lo[SPLIT ? 16 : 1];
       if (PAIR) {
 #pragma unroll
-        for (int q = 0; q < 16; ++q) out[q] = tbl[get_field<BITS, 2 * BITS>(cur, q)];
+        for (int q = 0; q < 16; ++q) {
+          const uint32_t v = get_field<BITS, 2 * BITS>(cur, q);
+          if (SPLIT) {
+            const uint2 e = reinterpret_cast<const uint2*>(tbl)[v];
+            out[q] = e.x;
+            out_lo[q] = e.y;
+          } else {
+            out[q] = tbl[v];
+          }
+        }
+      } else if (SPLIT) {
+#pragma unroll
+        for (int q = 0; q < 16; ++q) {
+          const uint32_t a = tbl[get_field<BITS, BITS>(cur, 2 * q)];
+          const uint32_t b = tbl[get_field<BITS, BITS>(cur, 2 * q + 1)];
+          out[q] = (a & 0xFFFFu) | (b << 16);
+          out_lo[q] = (a >> 16) | (b & 0xFFFF0000u);
+        }
       } else {
         const uint16_t* tbl16 = reinterpret_cast<const uint16_t*>(tbl);
 #pragma unroll
@@ -301,11 +439,18 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
       // tcgen05.st is warp-collective: the whole warp proceeds or the whole warp gives up
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->w_empty[ws]), wph ^ 1u, abort_flag, 0x600u | ws))) break;
       tc_fence_after();
-      tmem_st16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kWCol + ws * (kBlockK / 2) + half * 16, out);
+      const uint32_t w_tmem = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kWCol + ws * kWStageCols + half * 16;
+      tmem_st16(w_tmem, out);
+      if (SPLIT) {
+        uint32_t lo16[16];
+#pragma unroll
+        for (int q = 0; q < 16; ++q) lo16[q] = out_lo[SPLIT ? q : 0];
+        tmem_st16(w_tmem + kBlockK / 2, lo16);
+      }
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(smem_u32(&hdr->w_full[ws]));
-      if (++ws == kWStages) { ws = 0; wph ^= 1u; }
+      if (++ws == kWStagesUsed) { ws = 0; wph ^= 1u; }
     }
   }
 
@@ -336,18 +481,17 @@ EncodeTiledFn get_encode_tiled() {
   return fn;
 }
 
-template <int BITS, bool PAIR>
+template <int BITS, bool PAIR, bool SPLIT>
 int launch_tc(const CUtensorMap& tmap, const TcParams& p, size_t smem, int grid, cudaStream_t st) {
-  auto kern = linear_wq_tc_kernel<BITS, PAIR>;
+  auto kern = linear_wq_tc_kernel<BITS, PAIR, SPLIT>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return static_cast<int>(e);
   kern<<<grid, kThreads, smem, st>>>(tmap, p);
   return launch_status();
 }
 
-size_t table_bytes(int bits, int64_t groups, bool pair) {
-  const size_t per_group = pair ? (size_t(1) << (2 * bits)) : (size_t(1) << bits) / 2;
-  return groups * per_group * 4;
+size_t table_bytes(int bits, int64_t groups, bool pair, bool split) {
+  return static_cast<size_t>(groups) * table_words(bits, pair, split) * 4;
 }
 
 }  // namespace
@@ -357,14 +501,14 @@ bool tc_supported(const void* x, int x_dtype, const dimq_wq_weight* w, int64_t M
   if (M < 1 || N < 1 || K < kBlockK || K % kBlockK != 0) return false;
   if (!aligned(x, 16) || !aligned(w->packed, 16)) return false;
   if (M > 0x7FFFFFFF / 2 || N > 0x7FFFFFFF / 2) return false;
-  if (table_bytes(w->bits, w->groups, false) > (size_t)kMaxTableBytes) return false;
+  if (table_bytes(w->bits, w->groups, false, true) > (size_t)kMaxTableBytes) return false;
   const int64_t tiles = ((M + kTileX - 1) / kTileX) * ((N + kTileW - 1) / kTileW);
   return tiles < 0x7FFFFFFF;
 }
 
 int launch_linear_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
                         const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K, int epilogue,
-                        int w_fmt, cudaStream_t st) {
+                        int precision, cudaStream_t st) {
   if (!tc_supported(x, x_dtype, w, M, N, K)) return DIMQ_ERR_UNSUPPORTED;
   EncodeTiledFn encode = get_encode_tiled();
   if (encode == nullptr) return DIMQ_ERR_DRIVER;
@@ -395,22 +539,36 @@ int launch_linear_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, con
   p.N = N;
   p.K = K;
   p.epilogue = epilogue;
+  // Both MMA operands must have the same 16-bit format (a bf16 x fp16 mix is rejected by the
+  // hardware as an illegal instruction).  fp16 activations: fp16 codewords.  bf16 activations:
+  // bf16 codewords, exact when the codebook is stored in bf16, otherwise the hi + lo split.
+  const int w_fmt = x_dtype == DIMQ_BF16 ? 1 : 0;
+  const bool split = w_fmt == 1 && precision != 1 && w->cb_dtype != DIMQ_BF16;
   p.w_fmt = w_fmt;
-  p.idesc = tc::make_idesc_f16(w_fmt, x_dtype == DIMQ_BF16 ? 1 : 0, kTileW, kTileX);
+  p.idesc = tc::make_idesc_f16(w_fmt, w_fmt, kTileW, kTileX);
   p.m_tiles = static_cast<int>((M + kTileX - 1) / kTileX);
   p.n_tiles = static_cast<int>((N + kTileW - 1) / kTileW);
   const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
   const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
 
-  const bool pair = w->bits != 8 && table_bytes(w->bits, w->groups, true) <= (size_t)kMaxTableBytes;
-  const size_t smem = 1024 + static_cast<size_t>(kXStages) * kXStageBytes + 256 + table_bytes(w->bits, w->groups, pair);
+  const bool pair = w->bits != 8 && table_bytes(w->bits, w->groups, true, split) <= (size_t)kMaxTableBytes;
+  const size_t ring = static_cast<size_t>(kIdxPrefetch) * kNumDequantWarps * 32 * (w->bits == 8 ? 32 : 16);
+  const size_t smem = 1024 + static_cast<size_t>(kXStages) * kXStageBytes + 256 + ring +
+                      table_bytes(w->bits, w->groups, pair, split);
+#define DIMQ_TC_CASE(B)                                                                            \
+  case B:                                                                                          \
+    if (B != 8 && pair) return split ? launch_tc<B, B != 8, true>(tmap, p, smem, grid, st)         \
+                                     : launch_tc<B, B != 8, false>(tmap, p, smem, grid, st);       \
+    return split ? launch_tc<B, false, true>(tmap, p, smem, grid, st)                              \
+                 : launch_tc<B, false, false>(tmap, p, smem, grid, st);
   switch (w->bits) {
-    case 2: return pair ? launch_tc<2, true>(tmap, p, smem, grid, st) : launch_tc<2, false>(tmap, p, smem, grid, st);
-    case 3: return pair ? launch_tc<3, true>(tmap, p, smem, grid, st) : launch_tc<3, false>(tmap, p, smem, grid, st);
-    case 4: return pair ? launch_tc<4, true>(tmap, p, smem, grid, st) : launch_tc<4, false>(tmap, p, smem, grid, st);
-    case 8: return launch_tc<8, false>(tmap, p, smem, grid, st);
+    DIMQ_TC_CASE(2)
+    DIMQ_TC_CASE(3)
+    DIMQ_TC_CASE(4)
+    DIMQ_TC_CASE(8)
     default: return DIMQ_ERR_BAD_BITS;
   }
+#undef DIMQ_TC_CASE
 }
 
 int read_device_status(uint32_t* status) {

@@ -13,7 +13,7 @@ namespace tc {
 // Every spin on an mbarrier gives up after this many polls (each poll is a
 // try_wait that itself blocks for a hardware-defined slice), sets the CTA's
 // abort flag and records a status word; the kernel then drains and returns.
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr uint32_t kSpinLimit = 1u << 20;
 
 // Status word of the last tcgen05 kernel that gave up a wait (0 = none).
 __device__ uint32_t g_device_status;

@@ -12,8 +12,8 @@ def make_weight(n_out: int, k_in: int, bits: int, seed: int, *, group_rows: int 
                 cb_dtype=np.float16):
     """N(0, std) weight -> quantile codebooks (per layer or per `group_rows` rows) -> indices -> packed stream.
 
-    The codebook is rounded to `cb_dtype` first (the packed export stores fp16) and the SAME rounded
-    codebook is what both the oracle and the kernel see.
+    The codebook is rounded to `cb_dtype` first (a numpy dtype, or "bf16"; the packed export stores
+    fp16) and the SAME rounded codebook is what both the oracle and the kernel see.
     """
     rng = np.random.default_rng(seed)
     w = (rng.standard_normal((n_out, k_in)) * std).astype(np.float32)
@@ -24,7 +24,7 @@ def make_weight(n_out: int, k_in: int, bits: int, seed: int, *, group_rows: int 
     else:
         grp = group_rows
         cbs = np.stack([o.quantile_codebook(w[g0 : g0 + grp], entries) for g0 in range(0, n_out, grp)])
-    cbs = cbs.astype(cb_dtype).astype(np.float32)
+    cbs = bf16_round(cbs) if cb_dtype == "bf16" else cbs.astype(cb_dtype).astype(np.float32)
     idx = c_oracle.hard_quantize(w, cbs, grp)
     packed = c_oracle.pack_bits(idx, bits)
     return {"w": w, "codebooks": cbs, "idx": idx, "packed": packed, "group_rows": grp, "bits": bits}

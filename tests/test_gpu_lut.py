@@ -187,19 +187,42 @@ def test_linear_wq_stream_small_m(ops, bits, m):
 TC_SHAPES = [(192, 64, 128), (200, 128, 130), (577, 768, 384), (64, 1024, 256), (16, 256, 128)]
 
 
+# operand precision modes of the tensor-core kernel: (activation dtype, codebook dtype)
+#   bf16 x, fp16 codebook -> bf16 operands, every codeword split into hi + lo (two MMAs per k-step)
+#   bf16 x, bf16 codebook -> bf16 operands, exact in one term
+#   fp16 x, fp16 codebook -> fp16 operands, exact in one term
+TC_MODES = [(torch.bfloat16, np.float16, torch.float16), (torch.bfloat16, "bf16", torch.bfloat16),
+            (torch.float16, np.float16, torch.float16)]
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
 @pytest.mark.parametrize("bits", [2, 3, 4, 8])
 @pytest.mark.parametrize("m,k,n", TC_SHAPES)
-def test_linear_wq_tcgen05(ops, bits, m, k, n):
+def test_linear_wq_tcgen05(ops, bits, m, k, n, mode):
+    x_dtype, cb_np, cb_torch = TC_MODES[mode]
     grp = None if bits == 8 else 128
-    case = make_weight(n, k, bits, seed=bits * 13 + m, group_rows=grp)
+    case = make_weight(n, k, bits, seed=bits * 13 + m, group_rows=grp, cb_dtype=cb_np)
     rng = np.random.default_rng(m + k)
-    x = bf16_round(rng.standard_normal((m, k)).astype(np.float32))
+    x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(x_dtype)
     bias = rng.standard_normal(n).astype(np.float32)
-    want = o.linear_wq(x, case["packed"], case["codebooks"], bits, n, k, bias, case["group_rows"])
-    got = ops.dimq_linear_wq(_cuda(x, torch.bfloat16), _cuda(case["packed"]), _cuda(case["codebooks"], torch.float16),
+    want = o.linear_wq(x.float().numpy(), case["packed"], case["codebooks"], bits, n, k, bias, case["group_rows"])
+    got = ops.dimq_linear_wq(x.cuda(), _cuda(case["packed"]), _cuda(case["codebooks"], cb_torch),
                              _cuda(bias), n, k, bits=bits, group_rows=grp, algo="tcgen05")
     assert ops.last_device_status() == 0
-    _assert_close(got, want, f"tcgen05 bits={bits} {m}x{k}x{n}")
+    _assert_close(got, want, f"tcgen05 bits={bits} {m}x{k}x{n} mode={mode}")
+
+
+def test_linear_wq_tcgen05_per_channel_codebooks(ops):
+    """One codebook per output row: the lookup tables hold single codewords instead of pairs."""
+    m, k, n = 250, 576, 64
+    case = make_weight(n, k, 4, seed=9, group_rows=1, std=(2.0 / 576) ** 0.5)
+    x = torch.relu(torch.from_numpy(np.random.default_rng(2).standard_normal((m, k)).astype(np.float32))).to(torch.bfloat16)
+    want = o.linear_wq(x.float().numpy(), case["packed"], case["codebooks"], 4, n, k, None, 1)
+    for cb_torch in (torch.float16, torch.float32):
+        got = ops.dimq_linear_wq(x.cuda(), _cuda(case["packed"]), _cuda(case["codebooks"], cb_torch), None, n, k,
+                                 bits=4, group_rows=1, algo="tcgen05")
+        assert ops.last_device_status() == 0
+        _assert_close(got, want, "per-channel")
 
 
 @pytest.mark.parametrize("x_dtype", [torch.bfloat16, torch.float16])
