@@ -67,10 +67,16 @@ def is_available() -> bool:
     return True
 
 
+# number of kernels this process has launched through the C ABI (one per successful entry-point call)
+LAUNCH_COUNT = [0]
+
+
 def check(status: int, what: str) -> None:
     if status != 0:
         msg = lib().dimq_status_string(int(status)).decode()
         raise RuntimeError(f"dimq_b200.{what} failed: {msg} (status {status})")
+    if what != "last_device_status":
+        LAUNCH_COUNT[0] += 1
 
 
 def dtype_code(t: torch.Tensor, what: str) -> int:

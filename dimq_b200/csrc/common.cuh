@@ -62,9 +62,22 @@ __device__ __forceinline__ uint32_t get_index(const uint8_t* __restrict__ packed
   return (v >> sh) & ((1u << bits) - 1u);
 }
 
+// erf(x) by Abramowitz & Stegun 7.1.26 (|error| <= 1.5e-7): one reciprocal, one exp2, six FMAs.
+__device__ __forceinline__ float fast_erf(float x) {
+  const float z = fabsf(x);
+  const float t = __fdividef(1.0f, fmaf(0.3275911f, z, 1.0f));
+  float p = fmaf(t, 1.061405429f, -1.453152027f);
+  p = fmaf(t, p, 1.421413741f);
+  p = fmaf(t, p, -0.284496736f);
+  p = fmaf(t, p, 0.254829592f);
+  p *= t;
+  const float e = __expf(-z * z);
+  return copysignf(fmaf(-p, e, 1.0f), x);
+}
+
 __device__ __forceinline__ float apply_epilogue(float v, int epilogue) {
   if (epilogue == DIMQ_EPI_RELU) return fmaxf(v, 0.0f);
-  if (epilogue == DIMQ_EPI_GELU) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
+  if (epilogue == DIMQ_EPI_GELU) return 0.5f * v * (1.0f + fast_erf(v * 0.70710678118654752440f));
   return v;
 }
 

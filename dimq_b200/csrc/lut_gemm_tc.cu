@@ -372,39 +372,54 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
     const int row_in_tile = quarter * 32 + lane;
     const int64_t row_bytes = p.K * BITS / 8;
     constexpr int per_group = table_words(BITS, PAIR, SPLIT);
-    const int64_t total_iters = static_cast<int64_t>((num_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x) * k_blocks;
-    auto unit_ptr = [&](int64_t it) -> const uint8_t* {
-      const int t = blockIdx.x + static_cast<int>(it / k_blocks) * gridDim.x;
-      const int kb = static_cast<int>(it % k_blocks);
-      int64_t row = static_cast<int64_t>(t / p.m_tiles) * kTileW + row_in_tile;
-      if (row >= p.N) row = p.N - 1;
-      return p.packed + row * row_bytes + static_cast<int64_t>(kb) * (8 * BITS) + half * (4 * BITS);
+    const int my_tiles = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+    const int total_iters = my_tiles * k_blocks;
+    const int n_rows = static_cast<int>(p.N);
+    const int group_rows = static_cast<int>(p.group_rows);
+    // first packed byte of this thread's weight row (and k half) for a tile
+    auto row_ptr = [&](int t) -> const uint8_t* {
+      int row = (t / p.m_tiles) * kTileW + row_in_tile;
+      if (row >= n_rows) row = n_rows - 1;
+      return p.packed + static_cast<int64_t>(row) * row_bytes + half * (4 * BITS);
     };
     uint32_t ws = 0, wph = 0;
     const int dq_tid = tid - (2 + kNumEpilogueWarps) * 32;  // 0..255
     constexpr int kSlot = IdxSlot<BITS>::kBytes;
-    unsigned char* my_ring = idx_ring + dq_tid * kSlot;           // slot s at my_ring + s * 256 * kSlot
     constexpr int kRingStride = kNumDequantWarps * 32 * kSlot;
-    // the packed indices of stage `it` are fetched kIdxPrefetch - 1 stages ahead (cp.async, own slot)
-#pragma unroll
-    for (int s0 = 0; s0 < kIdxPrefetch - 1; ++s0) {
-      if (s0 < total_iters) issue_unit<BITS>(smem_u32(my_ring + s0 * kRingStride), unit_ptr(s0));
-      cp_async_commit();
-    }
-    for (int64_t it = 0; it < total_iters; ++it) {
-      {
-        const int64_t ahead = it + kIdxPrefetch - 1;
-        if (ahead < total_iters)
-          issue_unit<BITS>(smem_u32(my_ring + static_cast<int>(ahead % kIdxPrefetch) * kRingStride), unit_ptr(ahead));
-        cp_async_commit();
+    const uint32_t ring_u32 = smem_u32(idx_ring + dq_tid * kSlot);  // slot s at + s * kRingStride
+    const unsigned char* my_ring = idx_ring + dq_tid * kSlot;
+    // The packed indices of a stage are fetched kIdxPrefetch - 1 stages ahead (cp.async into this
+    // thread's own slot); the cursor walks (tile, k block) without divisions.
+    int pf_tile = blockIdx.x, pf_kb = 0, pf_slot = 0, pf_count = 0;
+    const uint8_t* pf_row = row_ptr(pf_tile);
+    auto prefetch_next = [&]() {
+      if (pf_count < total_iters) {
+        issue_unit<BITS>(ring_u32 + pf_slot * kRingStride, pf_row + pf_kb * (8 * BITS));
+        ++pf_count;
+        if (++pf_kb == k_blocks) {
+          pf_kb = 0;
+          pf_tile += gridDim.x;
+          if (pf_count < total_iters) pf_row = row_ptr(pf_tile);
+        }
       }
+      cp_async_commit();
+      if (++pf_slot == kIdxPrefetch) pf_slot = 0;
+    };
+#pragma unroll
+    for (int s0 = 0; s0 < kIdxPrefetch - 1; ++s0) prefetch_next();
+    int slot = 0;
+    bool alive = true;
+    for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+      int row = (t / p.m_tiles) * kTileW + row_in_tile;
+      if (row >= n_rows) row = n_rows - 1;
+      const uint32_t* tbl = table + (row / group_rows) * per_group;
+#pragma unroll 1
+      for (int kb = 0; kb < k_blocks; ++kb) {
+      prefetch_next();
       cp_async_wait<kIdxPrefetch - 1>();
       uint32_t cur[BITS];
-      read_unit<BITS>(my_ring + static_cast<int>(it % kIdxPrefetch) * kRingStride, cur);
-      const int t = blockIdx.x + static_cast<int>(it / k_blocks) * gridDim.x;
-      int64_t row = static_cast<int64_t>(t / p.m_tiles) * kTileW + row_in_tile;
-      if (row >= p.N) row = p.N - 1;
-      const uint32_t* tbl = table + (row / p.group_rows) * per_group;
+      read_unit<BITS>(my_ring + slot * kRingStride, cur);
+      if (++slot == kIdxPrefetch) slot = 0;
       uint32_t out[16];
       uint32_t out_lo[SPLIT ? 16 : 1];
       if (PAIR) {
@@ -437,7 +452,7 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
         }
       }
       // tcgen05.st is warp-collective: the whole warp proceeds or the whole warp gives up
-      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->w_empty[ws]), wph ^ 1u, abort_flag, 0x600u | ws))) break;
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->w_empty[ws]), wph ^ 1u, abort_flag, 0x600u | ws))) { alive = false; break; }
       tc_fence_after();
       const uint32_t w_tmem = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kWCol + ws * kWStageCols + half * 16;
       tmem_st16(w_tmem, out);
@@ -451,6 +466,7 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
       tc_fence_before();
       mbar_arrive(smem_u32(&hdr->w_full[ws]));
       if (++ws == kWStagesUsed) { ws = 0; wph ^= 1u; }
+      }
     }
   }
 

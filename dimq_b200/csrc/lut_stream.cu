@@ -59,18 +59,38 @@ linear_wq_stream_kernel(const void* __restrict__ x, int x_dtype, dimq_wq_weight 
   const int64_t Kp = (K + 1023) & ~static_cast<int64_t>(1023);
   const int tid = threadIdx.x;
   for (int i = tid; i < cb_total; i += kThreads) cb_s[i] = load_as_float(w.codebooks, w.cb_dtype, i);
-  // element k = ((it*32 + lane)*8 + q)*4 + e  ->  position ((it*8 + q)*32 + lane)*4 + e
-  const int64_t xk = static_cast<int64_t>(MT) * K;
-  for (int64_t i = tid; i < xk; i += kThreads) {
-    const int m = static_cast<int>(i / K);
-    const int64_t k = i % K;
-    const int e = static_cast<int>(k & 3);
-    const int q = static_cast<int>((k >> 2) & 7);
-    const int64_t unit = k >> 5;
-    const int lane = static_cast<int>(unit & 31);
-    const int64_t it = unit >> 5;
-    const float v = m < M ? load_as_float(x, x_dtype, static_cast<int64_t>(m) * K + k) : 0.0f;
-    x_s[m * Kp + ((it * 8 + q) * 32 + lane) * 4 + e] = v;
+  // element k = ((it*32 + lane)*8 + q)*4 + e  ->  position ((it*8 + q)*32 + lane)*4 + e:
+  // four consecutive k stay together, so x moves as float4 groups
+  const bool x_vec = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  for (int m = 0; m < MT; ++m) {
+    float* xm = x_s + m * Kp;
+    for (int64_t k4 = static_cast<int64_t>(tid) * 4; k4 < K; k4 += kThreads * 4) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (m < M) {
+        const int64_t src = static_cast<int64_t>(m) * K + k4;
+        if (x_dtype == DIMQ_F32) {
+          if (x_vec) v = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(x) + src));
+          else { const float* xp = static_cast<const float*>(x) + src; v = make_float4(xp[0], xp[1], xp[2], xp[3]); }
+        } else {
+          uint2 raw;
+          if (x_vec) raw = __ldg(reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(x) + src));
+          else { const uint16_t* xp = static_cast<const uint16_t*>(x) + src; raw = make_uint2(xp[0] | (uint32_t(xp[1]) << 16), xp[2] | (uint32_t(xp[3]) << 16)); }
+          if (x_dtype == DIMQ_BF16) {
+            v = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u),
+                            __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000u));
+          } else {
+            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+            const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+            v = make_float4(a.x, a.y, c.x, c.y);
+          }
+        }
+      }
+      const int q = static_cast<int>((k4 >> 2) & 7);
+      const int64_t unit = k4 >> 5;
+      const int ln = static_cast<int>(unit & 31);
+      const int64_t it = unit >> 5;
+      *reinterpret_cast<float4*>(xm + ((it * 8 + q) * 32 + ln) * 4) = v;
+    }
   }
   __syncthreads();
 

@@ -1,0 +1,163 @@
+"""Synthetic whole-model workloads built from packed DIMQ layers.
+
+``build_vit_b16_checkpoint`` creates a random-init ViT-B/16 (12 layers, hidden 768,
+12 heads, MLP 3072, 197 tokens, 1000 classes), quantises every qkv / proj / fc1 /
+fc2 / head Linear to ``bits``-bit indices with one quantile codebook per
+``group_rows`` output rows — the nearest-codeword assignment and the packing run in
+the CUDA library (the export path of dimq_backend/export.py:159-260) — and returns
+a ``dimq_packed_lut`` style dictionary.  ``DIMQViT`` runs it: the quantised Linears
+go through the weight-only LUT GEMM, attention / LayerNorm / patch embedding stay
+dense bf16 PyTorch ops.
+
+The codebooks are rounded to ``codebook_dtype`` *before* the indices are assigned, so
+the stored codebook is exactly what the kernels and any CPU check dequantise with.
+"""
+
+from __future__ import annotations
+
+from typing import Any
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import ops
+from .modules import DIMQLinear
+
+VIT_B16 = dict(layers=12, hidden=768, heads=12, mlp=3072, patch=16, image=224, classes=1000)
+
+
+def quantile_codebooks(w: torch.Tensor, entries: int, group_rows: int) -> torch.Tensor:
+    """One sorted ``entries``-entry quantile codebook per ``group_rows`` rows of ``w`` (fp32, on w's device).
+
+    Probabilities ``linspace(0, 1, entries + 2)[1:-1]`` and the post-processing of
+    quant/dimq.py:132-137,175-194 (strictly increasing, mean kept); every weight of the group
+    is used (no random subsample).
+    """
+    rows = w.shape[0]
+    flat = w.reshape(rows, -1).float()
+    q = torch.linspace(0.0, 1.0, entries + 2, device=w.device, dtype=torch.float32)[1:-1]
+    books = []
+    for g0 in range(0, rows, group_rows):
+        sample = flat[g0 : g0 + group_rows].reshape(-1)
+        centers = torch.quantile(sample, q).sort().values
+        span = (sample.max() - sample.min()).abs()
+        sigma = sample.std(unbiased=False).abs()
+        min_gap = torch.maximum(span, sigma).clamp_min(1e-6) * 1e-6
+        fixed = centers.clone()
+        for i in range(1, entries):
+            if fixed[i] <= fixed[i - 1]:
+                fixed[i] = fixed[i - 1] + min_gap
+        fixed = fixed - (fixed.mean() - centers.mean())
+        books.append(fixed.sort().values)
+    return torch.stack(books)
+
+
+def quantize_linear(weight: torch.Tensor, bias: torch.Tensor | None, bits: int, group_rows: int | None,
+                    codebook_dtype: torch.dtype, name: str) -> dict[str, Any]:
+    """Float weight on a CUDA device -> packed layer entry (indices assigned and packed on the GPU)."""
+    out_f, in_f = weight.shape
+    grp = out_f if group_rows is None else int(group_rows)
+    books = quantile_codebooks(weight, 1 << bits, grp).to(codebook_dtype)
+    _, packed = ops.hard_quantize(weight.float().contiguous(), books.float(), group_rows=grp, bits=bits,
+                                  return_indices=False)
+    return {
+        "name": name, "type": "linear", "bit_w": bits, "weight_shape": [out_f, in_f], "weight_numel": out_f * in_f,
+        "packed_weight": packed, "codebook": books, "group_rows": grp,
+        "codebook_granularity": "per_layer" if grp == out_f else "per_row_group",
+        "act_scale": None, "act_zero_point": None, "bias": bias, "layout": "linear_nk",
+        "out_features": out_f, "in_features": in_f,
+    }
+
+
+@torch.no_grad()
+def build_vit_b16_checkpoint(*, seed: int = 0, device="cuda", bits: int = 3, group_rows: int = 128,
+                             codebook_dtype: torch.dtype = torch.bfloat16, layers: int | None = None,
+                             dtype: torch.dtype = torch.bfloat16) -> dict[str, Any]:
+    cfg = dict(VIT_B16)
+    if layers is not None:
+        cfg["layers"] = int(layers)
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    dev = torch.device(device)
+
+    def randn(*shape, std=0.02):
+        return (torch.randn(*shape, generator=gen) * std).to(dev)
+
+    hid, mlp = cfg["hidden"], cfg["mlp"]
+    tokens = (cfg["image"] // cfg["patch"]) ** 2 + 1
+    qlayers: dict[str, dict[str, Any]] = {}
+    dense: dict[str, torch.Tensor] = {
+        "patch_embed.weight": randn(hid, 3, cfg["patch"], cfg["patch"]).to(dtype),
+        "patch_embed.bias": randn(hid).to(dtype),
+        "cls_token": randn(1, 1, hid).to(dtype),
+        "pos_embed": randn(1, tokens, hid).to(dtype),
+        "norm.weight": (1.0 + randn(hid, std=0.05)).to(dtype),
+        "norm.bias": randn(hid, std=0.05).to(dtype),
+    }
+    for i in range(cfg["layers"]):
+        for ln in ("norm1", "norm2"):
+            dense[f"blocks.{i}.{ln}.weight"] = (1.0 + randn(hid, std=0.05)).to(dtype)
+            dense[f"blocks.{i}.{ln}.bias"] = randn(hid, std=0.05).to(dtype)
+        for lname, (o, k) in (("attn.qkv", (3 * hid, hid)), ("attn.proj", (hid, hid)), ("mlp.fc1", (mlp, hid)),
+                              ("mlp.fc2", (hid, mlp))):
+            name = f"blocks.{i}.{lname}"
+            qlayers[name] = quantize_linear(randn(o, k), randn(o).to(dtype), bits, group_rows, codebook_dtype, name)
+    qlayers["head"] = quantize_linear(randn(cfg["classes"], hid), randn(cfg["classes"]).to(dtype), bits, group_rows,
+                                      codebook_dtype, "head")
+    return {"format": "dimq_packed_lut", "format_version": 2, "model_name": "vit_b16_synthetic", "config": cfg,
+            "weight_encoding": "packed_bitstream_indices", "activation_quantization": "none", "layers": qlayers,
+            "non_quantized_state_dict": dense}
+
+
+class DIMQViT(nn.Module):
+    """ViT-B/16 forward over packed DIMQ Linears (weight-only LUT GEMM), dense bf16 elsewhere."""
+
+    def __init__(self, checkpoint: dict[str, Any], *, act_dtype: torch.dtype = torch.bfloat16) -> None:
+        super().__init__()
+        self.cfg = dict(checkpoint["config"])
+        self.act_dtype = act_dtype
+        for key, value in checkpoint["non_quantized_state_dict"].items():
+            self.register_buffer(key.replace(".", "__"), value.to(act_dtype))
+        self.q = nn.ModuleDict()
+        for name, layer in checkpoint["layers"].items():
+            epi = "gelu" if name.endswith("mlp.fc1") else None
+            out_dtype = torch.float32 if name == "head" else act_dtype
+            self.q[name.replace(".", "__")] = DIMQLinear.from_export_layer(layer, out_dtype=out_dtype, epilogue=epi)
+
+    def _t(self, key: str) -> torch.Tensor:
+        return getattr(self, key.replace(".", "__"))
+
+    def _lin(self, name: str) -> DIMQLinear:
+        return self.q[name.replace(".", "__")]
+
+    def forward(self, images: torch.Tensor) -> torch.Tensor:
+        cfg = self.cfg
+        hid, heads = cfg["hidden"], cfg["heads"]
+        b = images.shape[0]
+        x = F.conv2d(images.to(self.act_dtype), self._t("patch_embed.weight"), self._t("patch_embed.bias"),
+                     stride=cfg["patch"])
+        x = x.flatten(2).transpose(1, 2)
+        x = torch.cat([self._t("cls_token").expand(b, -1, -1), x], dim=1) + self._t("pos_embed")
+        x = x.contiguous()
+        t = x.shape[1]
+        for i in range(cfg["layers"]):
+            pre = f"blocks.{i}."
+            h = F.layer_norm(x, (hid,), self._t(pre + "norm1.weight"), self._t(pre + "norm1.bias"), 1e-6)
+            qkv = self._lin(pre + "attn.qkv")(h).view(b, t, 3, heads, hid // heads).permute(2, 0, 3, 1, 4)
+            a = F.scaled_dot_product_attention(qkv[0], qkv[1], qkv[2])
+            a = a.transpose(1, 2).reshape(b, t, hid)
+            x = self._lin(pre + "attn.proj")(a, residual=x)
+            h = F.layer_norm(x, (hid,), self._t(pre + "norm2.weight"), self._t(pre + "norm2.bias"), 1e-6)
+            h = self._lin(pre + "mlp.fc1")(h)
+            x = self._lin(pre + "mlp.fc2")(h, residual=x)
+        cls = F.layer_norm(x[:, 0], (hid,), self._t("norm.weight"), self._t("norm.bias"), 1e-6)
+        return self._lin("head")(cls.contiguous())
+
+    def lut_gemm_flops(self, batch: int) -> float:
+        """Algorithmic flops (2*M*N*K) of the quantised Linears for one forward of ``batch`` images."""
+        t = (self.cfg["image"] // self.cfg["patch"]) ** 2 + 1
+        total = 0.0
+        for name, mod in self.q.items():
+            m = batch if name == "head" else batch * t
+            total += 2.0 * m * mod.out_features * mod.in_features
+        return total

@@ -1,0 +1,114 @@
+"""CPU restatement of the whole-model path: dequantise every packed layer, then run the
+float model with PyTorch CPU ops — what the DIMQ reference does in its QAT-wrapper eval
+forward (quant/dimq_wrapper.py:237-240: hard-quantised weight + ``F.linear``) and in
+``convert_to_dequantized_model`` (quant/export_dimq.py:15-29).
+
+TEST INFRASTRUCTURE ONLY: used by the parity tests, ``smoke()`` and the CPU-baseline /
+``--impl reference`` legs of ``bench.py``.  Parity status: pinned through the layer-level
+functions of ``dimq_oracle`` (checked against the reference's golden vectors); the model
+wiring itself (ViT-B/16 block structure) is the synthetic workload's own definition.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+from . import dimq_oracle as o
+
+
+def dequantize_layer(layer: dict) -> torch.Tensor:
+    """``codebook.float()[indices]`` for one packed layer (dimq_backend/reference.py:47-56)."""
+    shape = [int(v) for v in layer["weight_shape"]]
+    numel = int(np.prod(shape))
+    idx = o.unpack_bits(layer["packed_weight"].cpu().numpy(), numel, int(layer["bit_w"])).reshape(shape[0], -1)
+    books = layer["codebook"].float().cpu().numpy()
+    if books.ndim == 1:
+        books = books[None, :]
+    w = o.dequantize(idx, books, int(layer.get("group_rows") or shape[0]))
+    return torch.from_numpy(np.ascontiguousarray(w, dtype=np.float32)).reshape(shape)
+
+
+class ViTOracle:
+    """fp32 CPU ViT over the dequantised weights.  ``round_dtype`` (e.g. torch.bfloat16) rounds the
+    activations at the points where the GPU path stores them in that type."""
+
+    def __init__(self, checkpoint: dict, round_dtype: torch.dtype | None = None) -> None:
+        self.cfg = dict(checkpoint["config"])
+        self.round_dtype = round_dtype
+        self.dense = {k: v.float().cpu() for k, v in checkpoint["non_quantized_state_dict"].items()}
+        self.w = {}
+        self.b = {}
+        for name, layer in checkpoint["layers"].items():
+            self.w[name] = dequantize_layer(layer)
+            self.b[name] = None if layer.get("bias") is None else layer["bias"].float().cpu()
+
+    def _r(self, x: torch.Tensor) -> torch.Tensor:
+        return x if self.round_dtype is None else x.to(self.round_dtype).float()
+
+    @torch.no_grad()
+    def forward(self, images: torch.Tensor) -> torch.Tensor:
+        cfg, d = self.cfg, self.dense
+        hid, heads = cfg["hidden"], cfg["heads"]
+        x = self._r(F.conv2d(self._r(images.float().cpu()), d["patch_embed.weight"], d["patch_embed.bias"],
+                             stride=cfg["patch"]))
+        b = x.shape[0]
+        x = x.flatten(2).transpose(1, 2)
+        x = self._r(torch.cat([d["cls_token"].expand(b, -1, -1), x], dim=1) + d["pos_embed"])
+        t = x.shape[1]
+        for i in range(cfg["layers"]):
+            pre = f"blocks.{i}."
+            h = self._r(F.layer_norm(x, (hid,), d[pre + "norm1.weight"], d[pre + "norm1.bias"], 1e-6))
+            qkv = self._r(F.linear(h, self.w[pre + "attn.qkv"], self.b[pre + "attn.qkv"]))
+            qkv = qkv.view(b, t, 3, heads, hid // heads).permute(2, 0, 3, 1, 4)
+            a = self._r(F.scaled_dot_product_attention(qkv[0], qkv[1], qkv[2]))
+            a = a.transpose(1, 2).reshape(b, t, hid)
+            x = self._r(F.linear(a, self.w[pre + "attn.proj"], self.b[pre + "attn.proj"]) + x)
+            h = self._r(F.layer_norm(x, (hid,), d[pre + "norm2.weight"], d[pre + "norm2.bias"], 1e-6))
+            h = self._r(F.gelu(F.linear(h, self.w[pre + "mlp.fc1"], self.b[pre + "mlp.fc1"])))
+            x = self._r(F.linear(h, self.w[pre + "mlp.fc2"], self.b[pre + "mlp.fc2"]) + x)
+        cls = self._r(F.layer_norm(x[:, 0], (hid,), d["norm.weight"], d["norm.bias"], 1e-6))
+        return F.linear(cls, self.w["head"], self.b["head"])
+
+
+def build_vit_b16_checkpoint_cpu(*, seed: int = 0, bits: int = 3, group_rows: int = 128, layers: int = 12,
+                                 codebook_round=None) -> dict:
+    """A synthetic packed ViT-B/16 checkpoint made entirely on the CPU with the oracle's own
+    functions (quantile codebooks per ``group_rows`` rows, nearest-codeword indices, bit-stream
+    packing): N(0, 0.02) weights, the shapes of ViT-B/16.  Used by the CPU-only reference arm."""
+    from . import c_oracle
+
+    cfg = dict(layers=layers, hidden=768, heads=12, mlp=3072, patch=16, image=224, classes=1000)
+    rng = np.random.default_rng(seed)
+    hid, mlp = cfg["hidden"], cfg["mlp"]
+    tokens = (cfg["image"] // cfg["patch"]) ** 2 + 1
+
+    def randn(*shape, std=0.02):
+        return torch.from_numpy((rng.standard_normal(shape) * std).astype(np.float32))
+
+    def qlayer(name, out_f, in_f):
+        w = randn(out_f, in_f).numpy()
+        books = np.stack([o.quantile_codebook(w[g0 : g0 + group_rows], 1 << bits) for g0 in range(0, out_f, group_rows)])
+        if codebook_round is not None:
+            books = codebook_round(books)
+        idx = c_oracle.hard_quantize(w, books, group_rows)
+        return {"name": name, "type": "linear", "bit_w": bits, "weight_shape": [out_f, in_f],
+                "packed_weight": torch.from_numpy(c_oracle.pack_bits(idx, bits)), "codebook": torch.from_numpy(books),
+                "group_rows": group_rows, "bias": randn(out_f), "out_features": out_f, "in_features": in_f,
+                "act_scale": None, "act_zero_point": None}
+
+    dense = {"patch_embed.weight": randn(hid, 3, 16, 16), "patch_embed.bias": randn(hid),
+             "cls_token": randn(1, 1, hid), "pos_embed": randn(1, tokens, hid),
+             "norm.weight": 1.0 + randn(hid, std=0.05), "norm.bias": randn(hid, std=0.05)}
+    qlayers = {}
+    for i in range(layers):
+        for ln in ("norm1", "norm2"):
+            dense[f"blocks.{i}.{ln}.weight"] = 1.0 + randn(hid, std=0.05)
+            dense[f"blocks.{i}.{ln}.bias"] = randn(hid, std=0.05)
+        for lname, (of, k) in (("attn.qkv", (3 * hid, hid)), ("attn.proj", (hid, hid)), ("mlp.fc1", (mlp, hid)),
+                               ("mlp.fc2", (hid, mlp))):
+            qlayers[f"blocks.{i}.{lname}"] = qlayer(f"blocks.{i}.{lname}", of, k)
+    qlayers["head"] = qlayer("head", cfg["classes"], hid)
+    return {"format": "dimq_packed_lut", "format_version": 2, "config": cfg, "layers": qlayers,
+            "non_quantized_state_dict": dense}
