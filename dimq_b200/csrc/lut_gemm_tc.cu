@@ -19,6 +19,8 @@
 // Warp roles (448 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM
 // allocator, warps 2-5 epilogue, warps 6-13 dequantisation.  Persistent grid:
 // one CTA per SM walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...
+#include <cstdlib>
+
 #include "tc_common.cuh"
 
 namespace dimq {
@@ -60,6 +62,8 @@ struct TcParams {
                               // exact to ~2^-17 although the operands are bf16.
   uint32_t idesc;
   int m_tiles, n_tiles;
+  int dbg;                    // diagnostics: 1 skip epilogue work, 2 skip dequant work, 4 skip MMAs
+  unsigned long long* prof;   // optional per-CTA wait-cycle counters (diagnostics), else null
 };
 
 struct SharedHeader {
@@ -69,6 +73,15 @@ struct SharedHeader {
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
 };
+
+// Diagnostics: cycles spent inside one bounded wait, accumulated per role when p.prof is set.
+#define DIMQ_TIMED(acc, expr)                                   \
+  [&]() {                                                        \
+    const long long t0_ = p.prof ? clock64() : 0;                \
+    const bool ok_ = (expr);                                     \
+    if (p.prof) acc += static_cast<unsigned long long>(clock64() - t0_); \
+    return ok_;                                                  \
+  }()
 
 template <int BITS>
 __device__ __forceinline__ void load_unit(const uint8_t* p, uint32_t (&w)[BITS]) {
@@ -270,17 +283,24 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
       uint32_t stage = 0, phase = 0;
       uint32_t issued = 0;
       bool ok = true;
+      unsigned long long w_xe = 0;
+      const long long t_begin = clock64();
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         const int m_blk = t % p.m_tiles;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(smem_u32(&hdr->x_empty[stage]), phase ^ 1u, abort_flag, 0x100u | stage)) { ok = false; break; }
+          if (!DIMQ_TIMED(w_xe, mbar_wait(smem_u32(&hdr->x_empty[stage]), phase ^ 1u, abort_flag, 0x100u | stage))) { ok = false; break; }
           const uint32_t full = smem_u32(&hdr->x_full[stage]);
-          mbar_arrive_expect_tx(full, kXStageBytes);
-          tma_load_2d(smem_u32(x_stage + stage * kXStageBytes), &tmap_x, full, kb * kBlockK, m_blk * kTileX);
+          if (p.dbg & 8) {
+            mbar_arrive(full);
+          } else {
+            mbar_arrive_expect_tx(full, kXStageBytes);
+            tma_load_2d(smem_u32(x_stage + stage * kXStageBytes), &tmap_x, full, kb * kBlockK, m_blk * kTileX);
+          }
           ++issued;
           if (++stage == kXStages) { stage = 0; phase ^= 1u; }
         }
       }
+      if (p.prof) { p.prof[blockIdx.x * 16 + 0] = w_xe; p.prof[blockIdx.x * 16 + 1] = clock64() - t_begin; }
       if (!ok) {
         // Gave up: wait (bounded) for the copies still in flight so that no TMA write
         // lands in shared memory after this CTA has exited.
@@ -298,23 +318,30 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
     if (lane == 0) {
       uint32_t xs = 0, xph = 0, ws = 0, wph = 0, as = 0, aph = 0;
       bool ok = true;
+      unsigned long long w_de = 0, w_xf = 0, w_wf = 0;
+      const long long t_begin = clock64();
+      const uint64_t desc0 = make_smem_desc_sw128(smem_u32(x_stage));
+      const uint32_t a0 = tmem_base + kWCol;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        if (!mbar_wait(smem_u32(&hdr->d_empty[as]), aph ^ 1u, abort_flag, 0x200u | as)) { ok = false; break; }
+        if (!DIMQ_TIMED(w_de, mbar_wait(smem_u32(&hdr->d_empty[as]), aph ^ 1u, abort_flag, 0x200u | as))) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + kAccCol + as * kTileX;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(smem_u32(&hdr->x_full[xs]), xph, abort_flag, 0x300u | xs)) { ok = false; break; }
-          if (!mbar_wait(smem_u32(&hdr->w_full[ws]), wph, abort_flag, 0x400u | ws)) { ok = false; break; }
+          if (!DIMQ_TIMED(w_xf, mbar_wait(smem_u32(&hdr->x_full[xs]), xph, abort_flag, 0x300u | xs))) { ok = false; break; }
+          if (!DIMQ_TIMED(w_wf, mbar_wait(smem_u32(&hdr->w_full[ws]), wph, abort_flag, 0x400u | ws))) { ok = false; break; }
           tc_fence_after();
-          const uint64_t b_desc = make_smem_desc_sw128(smem_u32(x_stage + xs * kXStageBytes));
-          const uint32_t a_tmem = tmem_base + kWCol + ws * kWStageCols;
+          const uint64_t b_desc = desc0 + static_cast<uint64_t>(xs * (kXStageBytes >> 4));
+          const uint32_t a_tmem = a0 + ws * kWStageCols;
+          // advance 16 k: 32 bytes inside the swizzled row (encoded >> 4), 8 TMEM columns
+          if (!(p.dbg & 4)) {
+          if (kb == 0) mma_f16_ts(d_tmem, a_tmem, b_desc, p.idesc, 0u);
+          else mma_f16_ts_acc(d_tmem, a_tmem, b_desc, p.idesc);
+          if (SPLIT) mma_f16_ts_acc(d_tmem, a_tmem + kBlockK / 2, b_desc, p.idesc);
 #pragma unroll
-          for (int j = 0; j < kBlockK / 16; ++j) {
-            // advance 16 k: 32 bytes inside the swizzled row (encoded >> 4), 8 TMEM columns
-            mma_f16_ts(d_tmem, a_tmem + j * 8, b_desc + static_cast<uint64_t>(j * 2), p.idesc,
-                       (kb > 0 || j > 0) ? 1u : 0u);
-            if (SPLIT)
-              mma_f16_ts(d_tmem, a_tmem + kBlockK / 2 + j * 8, b_desc + static_cast<uint64_t>(j * 2), p.idesc, 1u);
+          for (int j = 1; j < kBlockK / 16; ++j) {
+            mma_f16_ts_acc(d_tmem, a_tmem + j * 8, b_desc + static_cast<uint64_t>(j * 2), p.idesc);
+            if (SPLIT) mma_f16_ts_acc(d_tmem, a_tmem + kBlockK / 2 + j * 8, b_desc + static_cast<uint64_t>(j * 2), p.idesc);
+          }
           }
           mma_commit(smem_u32(&hdr->x_empty[xs]));
           mma_commit(smem_u32(&hdr->w_empty[ws]));
@@ -325,12 +352,18 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
         mma_commit(smem_u32(&hdr->d_full[as]));
         if (++as == kAccStages) { as = 0; aph ^= 1u; }
       }
+      if (p.prof) {
+        p.prof[blockIdx.x * 16 + 2] = w_de; p.prof[blockIdx.x * 16 + 3] = w_xf; p.prof[blockIdx.x * 16 + 4] = w_wf;
+        p.prof[blockIdx.x * 16 + 5] = clock64() - t_begin;
+      }
     }
   } else if (warp < 2 + kNumEpilogueWarps) {
     // ===================== epilogue =====================
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32)
     uint32_t as = 0, aph = 0;
     bool ok = true;
+    unsigned long long w_df = 0;
+    const long long t_begin = clock64();
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       const int m_blk = t % p.m_tiles, n_blk = t / p.m_tiles;
       const int64_t n = static_cast<int64_t>(n_blk) * kTileW + quarter * 32 + lane;
@@ -338,10 +371,12 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
       const bool n_ok = n < p.N;
       const float bias = (p.bias != nullptr && n_ok) ? load_as_float(p.bias, p.bias_dtype, n) : 0.0f;
       // tcgen05.ld is warp-collective: the whole warp proceeds or the whole warp gives up
-      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->d_full[as]), aph, abort_flag, 0x500u | as))) { ok = false; break; }
+      if (!__all_sync(0xFFFFFFFFu, DIMQ_TIMED(w_df, mbar_wait(smem_u32(&hdr->d_full[as]), aph, abort_flag, 0x500u | as)))) { ok = false; break; }
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kAccCol + as * kTileX;
 #pragma unroll 1
+      if (p.dbg & 1) { tc_fence_before(); mbar_arrive(smem_u32(&hdr->d_empty[as])); }
+      else
       for (int c = 0; c < kTileX / 32; ++c) {
         uint32_t r[32];
         __syncwarp();
@@ -364,6 +399,7 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
       }
       if (++as == kAccStages) { as = 0; aph ^= 1u; }
     }
+    if (p.prof && warp == 2 && lane == 0) { p.prof[blockIdx.x * 16 + 6] = w_df; p.prof[blockIdx.x * 16 + 7] = clock64() - t_begin; }
   } else {
     // ===================== dequantisation =====================
     const int dw = warp - (2 + kNumEpilogueWarps);  // 0..7
@@ -409,6 +445,10 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
     for (int s0 = 0; s0 < kIdxPrefetch - 1; ++s0) prefetch_next();
     int slot = 0;
     bool alive = true;
+    unsigned long long w_we = 0, w_cp = 0;
+    const long long t_begin = clock64();
+    bool pending = false;       // a tcgen05.st whose completion has not been published yet
+    uint32_t pending_ws = 0;
     for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
       int row = (t / p.m_tiles) * kTileW + row_in_tile;
       if (row >= n_rows) row = n_rows - 1;
@@ -416,7 +456,7 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
 #pragma unroll 1
       for (int kb = 0; kb < k_blocks; ++kb) {
       prefetch_next();
-      cp_async_wait<kIdxPrefetch - 1>();
+      { const long long t0_ = p.prof ? clock64() : 0; cp_async_wait<kIdxPrefetch - 1>(); if (p.prof) w_cp += clock64() - t0_; }
       uint32_t cur[BITS];
       read_unit<BITS>(my_ring + slot * kRingStride, cur);
       if (++slot == kIdxPrefetch) slot = 0;
@@ -451,23 +491,35 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
           out[q] = lo | (hi << 16);
         }
       }
+      // The store of the previous stage has had this stage's lookups to complete: publish it now.
+      if (pending) {
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&hdr->w_full[pending_ws]));
+        pending = false;
+      }
       // tcgen05.st is warp-collective: the whole warp proceeds or the whole warp gives up
-      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->w_empty[ws]), wph ^ 1u, abort_flag, 0x600u | ws))) { alive = false; break; }
+      if (!__all_sync(0xFFFFFFFFu, DIMQ_TIMED(w_we, mbar_wait(smem_u32(&hdr->w_empty[ws]), wph ^ 1u, abort_flag, 0x600u | ws)))) { alive = false; break; }
       tc_fence_after();
       const uint32_t w_tmem = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kWCol + ws * kWStageCols + half * 16;
-      tmem_st16(w_tmem, out);
-      if (SPLIT) {
+      if (!(p.dbg & 2)) tmem_st16(w_tmem, out);
+      if (SPLIT && !(p.dbg & 2)) {
         uint32_t lo16[16];
 #pragma unroll
         for (int q = 0; q < 16; ++q) lo16[q] = out_lo[SPLIT ? q : 0];
         tmem_st16(w_tmem + kBlockK / 2, lo16);
       }
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(smem_u32(&hdr->w_full[ws]));
+      pending = true;
+      pending_ws = ws;
       if (++ws == kWStagesUsed) { ws = 0; wph ^= 1u; }
       }
     }
+    if (pending) {
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&hdr->w_full[pending_ws]));
+    }
+    if (p.prof && dq_tid == 0) { p.prof[blockIdx.x * 16 + 8] = w_we; p.prof[blockIdx.x * 16 + 9] = w_cp; p.prof[blockIdx.x * 16 + 10] = clock64() - t_begin; }
   }
 
   // ---- teardown -----------------------------------------------------------------
@@ -562,6 +614,10 @@ int launch_linear_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, con
   const bool split = w_fmt == 1 && precision != 1 && w->cb_dtype != DIMQ_BF16;
   p.w_fmt = w_fmt;
   p.idesc = tc::make_idesc_f16(w_fmt, w_fmt, kTileW, kTileX);
+  p.prof = nullptr;
+  p.dbg = 0;
+  if (const char* env = getenv("DIMQ_B200_TC_DEBUG")) p.dbg = atoi(env);
+  if (const char* env = getenv("DIMQ_B200_PROFILE_PTR")) p.prof = reinterpret_cast<unsigned long long*>(strtoull(env, nullptr, 0));
   p.m_tiles = static_cast<int>((M + kTileX - 1) / kTileX);
   p.n_tiles = static_cast<int>((N + kTileW - 1) / kTileW);
   const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;

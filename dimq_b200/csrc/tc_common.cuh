@@ -61,6 +61,33 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return false;
 }
 
+// Same bounded wait for roles that have slack: between polls the warp sleeps a few tens of
+// nanoseconds so that it does not take issue slots from the warp that feeds the tensor core.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                  uint32_t code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+    __nanosleep(40);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 255u && *abort_flag != 0u) return false;
+  }
+  *abort_flag = 1u;
+  atomicOr(&g_device_status, 0x80000000u | code);
+  return false;
+}
+
+// D (+)= A * B with the accumulate flag known at compile time (no predicate set-up per call).
+__device__ __forceinline__ void mma_f16_ts_acc(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.eq.b32 p, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc)
+      : "memory");
+}
+
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
