@@ -31,7 +31,7 @@ using namespace tc;
 constexpr int kTileW = 128;      // weight rows per tile (UMMA M)
 constexpr int kTileX = 192;      // activation rows per tile (UMMA N)
 constexpr int kBlockK = 64;      // k per stage: 128 bytes of 16-bit elements
-constexpr int kXStages = 6;      // shared-memory stages of the activation tile
+constexpr int kXStages = 8;      // upper bound of shared-memory stages of the activation tile (p.x_stages are used)
 constexpr int kWStages = 4;      // tensor-memory stages of the dequantised weight tile (2 in split mode)
 constexpr int kAccStages = 2;    // accumulator buffers
 constexpr int kTmemCols = 512;
@@ -39,7 +39,9 @@ constexpr int kAccCol = 0;                         // accumulators: columns [0, 
 constexpr int kWCol = kAccStages * kTileX;         // weight stages: 32 columns each
 static_assert(kWCol + kWStages * (kBlockK / 2) <= kTmemCols, "TMEM layout");
 constexpr int kXStageBytes = kTileX * kBlockK * 2;  // 24 KB
-constexpr int kNumDequantWarps = 8;
+constexpr int kNumDequantGroups = 3;   // each group of 4 warps (one per TMEM lane quarter) takes every 3rd stage
+constexpr int kNumDequantWarps = 4 * kNumDequantGroups;
+constexpr int kRepWords = 2048;          // replicated lookup table of one dequantisation group (8 KB)
 constexpr int kNumEpilogueWarps = 4;
 constexpr int kThreads = (2 + kNumEpilogueWarps + kNumDequantWarps) * 32;
 constexpr int kMaxTableBytes = 40 * 1024;
@@ -62,6 +64,8 @@ struct TcParams {
                               // exact to ~2^-17 although the operands are bf16.
   uint32_t idesc;
   int m_tiles, n_tiles;
+  int x_stages;               // activation stages that fit shared memory (3..kXStages)
+  int rep;                    // 1: every 128-row tile lies in one codebook group -> replicated tables
   int dbg;                    // diagnostics: 1 skip epilogue work, 2 skip dequant work, 4 skip MMAs
   unsigned long long* prof;   // optional per-CTA wait-cycle counters (diagnostics), else null
 };
@@ -163,33 +167,35 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // Prefetch ring of packed-index units: one slot per dequantisation thread and stage in flight.
-constexpr int kIdxPrefetch = 4;
+constexpr int kIdxPrefetch = 3;
 template <int BITS>
-struct IdxSlot { static constexpr int kBytes = BITS == 8 ? 32 : 16; };
+struct IdxSlot { static constexpr int kBytes = BITS == 8 ? 64 : 32; };  // 64 indices of one weight row
 
 template <int BITS>
 __device__ __forceinline__ void issue_unit(uint32_t dst, const uint8_t* src) {
-  if constexpr (BITS == 4) { cp_async(dst, src, 16); }
-  else if constexpr (BITS == 2) { cp_async(dst, src, 8); }
-  else if constexpr (BITS == 8) { cp_async(dst, src, 16); cp_async(dst + 16, src + 16, 16); }
-  else {
+  // 64 indices = 8 * BITS bytes
+  if constexpr (BITS == 4) { cp_async(dst, src, 16); cp_async(dst + 16, src + 16, 16); }
+  else if constexpr (BITS == 2) { cp_async(dst, src, 16); }
+  else if constexpr (BITS == 8) {
 #pragma unroll
-    for (int i = 0; i < BITS; ++i) cp_async(dst + 4 * i, src + 4 * i, 4);
+    for (int i = 0; i < 4; ++i) cp_async(dst + 16 * i, src + 16 * i, 16);
+  } else {
+#pragma unroll
+    for (int i = 0; i < BITS; ++i) cp_async(dst + 8 * i, src + 8 * i, 8);
   }
 }
 
 template <int BITS>
-__device__ __forceinline__ void read_unit(const unsigned char* slot, uint32_t (&w)[BITS]) {
-  if constexpr (BITS == 8) {
-    const uint4 q0 = *reinterpret_cast<const uint4*>(slot);
-    const uint4 q1 = *reinterpret_cast<const uint4*>(slot + 16);
-    w[0] = q0.x; w[1] = q0.y; w[2] = q0.z; w[3] = q0.w; w[4] = q1.x; w[5] = q1.y; w[6] = q1.z; w[7] = q1.w;
-  } else {
-    const uint4 q = *reinterpret_cast<const uint4*>(slot);
-    const uint32_t v[4] = {q.x, q.y, q.z, q.w};
+__device__ __forceinline__ void read_unit(const unsigned char* slot, uint32_t (&w)[2 * BITS]) {
+  constexpr int kVec = (2 * BITS * 4 + 15) / 16;
+  uint32_t v[kVec * 4];
 #pragma unroll
-    for (int i = 0; i < BITS; ++i) w[i] = v[i];
+  for (int i = 0; i < kVec; ++i) {
+    const uint4 q = *reinterpret_cast<const uint4*>(slot + 16 * i);
+    v[4 * i] = q.x; v[4 * i + 1] = q.y; v[4 * i + 2] = q.z; v[4 * i + 3] = q.w;
   }
+#pragma unroll
+  for (int i = 0; i < 2 * BITS; ++i) w[i] = v[i];
 }
 
 // 32-bit words of lookup table per codebook group.
@@ -213,10 +219,12 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
   // [x stages (1024-aligned)] [header] [tables]
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* x_stage = smem;
-  SharedHeader* hdr = reinterpret_cast<SharedHeader*>(smem + kXStages * kXStageBytes);
-  unsigned char* idx_ring = reinterpret_cast<unsigned char*>(hdr) + 256;  // [kIdxPrefetch][256 threads][slot]
+  const uint32_t n_xs = static_cast<uint32_t>(p.x_stages);
+  SharedHeader* hdr = reinterpret_cast<SharedHeader*>(smem + n_xs * kXStageBytes);
+  unsigned char* idx_ring = reinterpret_cast<unsigned char*>(hdr) + 256;  // [kIdxPrefetch][dequant threads][slot]
   constexpr int kRingBytes = kIdxPrefetch * kNumDequantWarps * 32 * IdxSlot<BITS>::kBytes;
-  uint32_t* table = reinterpret_cast<uint32_t*>(idx_ring + kRingBytes);
+  uint32_t* rep_tables = reinterpret_cast<uint32_t*>(idx_ring + kRingBytes);  // [groups of warps][kRepWords]
+  uint32_t* table = rep_tables + (p.rep ? kNumDequantGroups * kRepWords : 0);
   static_assert(sizeof(SharedHeader) <= 256, "header");
 
   const int tid = threadIdx.x;
@@ -229,8 +237,8 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
   // ---- one-time setup ---------------------------------------------------------
   if (tid == 0) {
     for (int s = 0; s < kXStages; ++s) { mbar_init(smem_u32(&hdr->x_full[s]), 1); mbar_init(smem_u32(&hdr->x_empty[s]), 1); }
-    for (int s = 0; s < kWStages; ++s) { mbar_init(smem_u32(&hdr->w_full[s]), kNumDequantWarps * 32); mbar_init(smem_u32(&hdr->w_empty[s]), 1); }
-    for (int s = 0; s < kAccStages; ++s) { mbar_init(smem_u32(&hdr->d_full[s]), 1); mbar_init(smem_u32(&hdr->d_empty[s]), kNumEpilogueWarps * 32); }
+    for (int s = 0; s < kWStages; ++s) { mbar_init(smem_u32(&hdr->w_full[s]), 4); mbar_init(smem_u32(&hdr->w_empty[s]), 1); }
+    for (int s = 0; s < kAccStages; ++s) { mbar_init(smem_u32(&hdr->d_full[s]), 1); mbar_init(smem_u32(&hdr->d_empty[s]), kNumEpilogueWarps); }
     hdr->abort_flag = 0u;
     fence_barrier_init();
     prefetch_tensormap(&tmap_x);
@@ -297,17 +305,17 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
             tma_load_2d(smem_u32(x_stage + stage * kXStageBytes), &tmap_x, full, kb * kBlockK, m_blk * kTileX);
           }
           ++issued;
-          if (++stage == kXStages) { stage = 0; phase ^= 1u; }
+          if (++stage == n_xs) { stage = 0; phase ^= 1u; }
         }
       }
       if (p.prof) { p.prof[blockIdx.x * 16 + 0] = w_xe; p.prof[blockIdx.x * 16 + 1] = clock64() - t_begin; }
       if (!ok) {
         // Gave up: wait (bounded) for the copies still in flight so that no TMA write
         // lands in shared memory after this CTA has exited.
-        const uint32_t n_back = issued < (uint32_t)kXStages ? issued : (uint32_t)kXStages;
+        const uint32_t n_back = issued < n_xs ? issued : n_xs;
         uint32_t s = stage, ph = phase;
         for (uint32_t i = 0; i < n_back; ++i) {
-          if (s == 0) { s = kXStages - 1; ph ^= 1u; } else { --s; }
+          if (s == 0) { s = n_xs - 1; ph ^= 1u; } else { --s; }
           for (uint32_t it = 0; it < kSpinLimit; ++it)
             if (mbar_try_wait(smem_u32(&hdr->x_full[s]), ph)) break;
         }
@@ -318,7 +326,7 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
     if (lane == 0) {
       uint32_t xs = 0, xph = 0, ws = 0, wph = 0, as = 0, aph = 0;
       bool ok = true;
-      unsigned long long w_de = 0, w_xf = 0, w_wf = 0;
+      unsigned long long w_de = 0, w_xf = 0, w_wf = 0, t_cm = 0, t_fe = 0, t_mm = 0;
       const long long t_begin = clock64();
       const uint64_t desc0 = make_smem_desc_sw128(smem_u32(x_stage));
       const uint32_t a0 = tmem_base + kWCol;
@@ -327,9 +335,10 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + kAccCol + as * kTileX;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!DIMQ_TIMED(w_xf, mbar_wait(smem_u32(&hdr->x_full[xs]), xph, abort_flag, 0x300u | xs))) { ok = false; break; }
-          if (!DIMQ_TIMED(w_wf, mbar_wait(smem_u32(&hdr->w_full[ws]), wph, abort_flag, 0x400u | ws))) { ok = false; break; }
+          if (!DIMQ_TIMED(w_xf, mbar_wait2(smem_u32(&hdr->x_full[xs]), xph, smem_u32(&hdr->w_full[ws]), wph, abort_flag, 0x300u | xs))) { ok = false; break; }
+          long long tq0 = p.prof ? clock64() : 0;
           tc_fence_after();
+          if (p.prof) { const long long tq1 = clock64(); t_fe += tq1 - tq0; tq0 = tq1; }
           const uint64_t b_desc = desc0 + static_cast<uint64_t>(xs * (kXStageBytes >> 4));
           const uint32_t a_tmem = a0 + ws * kWStageCols;
           // advance 16 k: 32 bytes inside the swizzled row (encoded >> 4), 8 TMEM columns
@@ -343,9 +352,12 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
             if (SPLIT) mma_f16_ts_acc(d_tmem, a_tmem + kBlockK / 2 + j * 8, b_desc + static_cast<uint64_t>(j * 2), p.idesc);
           }
           }
+          if (p.prof) { const long long tq1 = clock64(); t_mm += tq1 - tq0; tq0 = tq1; }
+          // one commit per k block: the producer (activation slot xs) and the dequantisation
+          // group that will reuse this weight slot both wait on it
           mma_commit(smem_u32(&hdr->x_empty[xs]));
-          mma_commit(smem_u32(&hdr->w_empty[ws]));
-          if (++xs == kXStages) { xs = 0; xph ^= 1u; }
+          if (p.prof) { const long long tq1 = clock64(); t_cm += tq1 - tq0; }
+          if (++xs == n_xs) { xs = 0; xph ^= 1u; }
           if (++ws == kWStagesUsed) { ws = 0; wph ^= 1u; }
         }
         if (!ok) break;
@@ -355,6 +367,7 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
       if (p.prof) {
         p.prof[blockIdx.x * 16 + 2] = w_de; p.prof[blockIdx.x * 16 + 3] = w_xf; p.prof[blockIdx.x * 16 + 4] = w_wf;
         p.prof[blockIdx.x * 16 + 5] = clock64() - t_begin;
+        p.prof[blockIdx.x * 16 + 11] = t_cm; p.prof[blockIdx.x * 16 + 12] = t_fe; p.prof[blockIdx.x * 16 + 13] = t_mm;
       }
     }
   } else if (warp < 2 + kNumEpilogueWarps) {
@@ -375,7 +388,7 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kAccCol + as * kTileX;
 #pragma unroll 1
-      if (p.dbg & 1) { tc_fence_before(); mbar_arrive(smem_u32(&hdr->d_empty[as])); }
+      if (p.dbg & 1) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(smem_u32(&hdr->d_empty[as])); }
       else
       for (int c = 0; c < kTileX / 32; ++c) {
         uint32_t r[32];
@@ -385,7 +398,8 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
         if (c == kTileX / 32 - 1) {
           // every column of this buffer is in registers: hand it back to the MMA warp
           tc_fence_before();
-          mbar_arrive(smem_u32(&hdr->d_empty[as]));
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&hdr->d_empty[as]));
         }
         const int64_t m_first = m0 + c * 32;
         const int64_t rows64 = p.M - m_first;
@@ -402,41 +416,58 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
     if (p.prof && warp == 2 && lane == 0) { p.prof[blockIdx.x * 16 + 6] = w_df; p.prof[blockIdx.x * 16 + 7] = clock64() - t_begin; }
   } else {
     // ===================== dequantisation =====================
-    const int dw = warp - (2 + kNumEpilogueWarps);  // 0..7
+    // 12 warps in 3 groups of 4 (one warp per TMEM lane quarter).  Group g dequantises stages
+    // g, g + 3, g + 6, ... completely (64 k of 128 weight rows: thread = weight row), so a warp has
+    // three stage periods for one stage's latency chain.
+    // A group may run at most one mbarrier phase ahead of the MMA warp, which holds when the number
+    // of active groups does not exceed the number of weight stages (2 in split mode): the third
+    // group idles there.
+    constexpr int kGroups = SPLIT ? 2 : kNumDequantGroups;
+    static_assert(kGroups <= (SPLIT ? kWStages / 2 : kWStages), "dequant groups vs weight stages");
+    const int dw = warp - (2 + kNumEpilogueWarps);  // 0..11
+    const int grp = dw >> 2;
     const int quarter = warp & 3;                   // TMEM lane quarter this warp may write
-    const int half = dw >> 2;                       // which 32 of the stage's 64 k
     const int row_in_tile = quarter * 32 + lane;
     const int64_t row_bytes = p.K * BITS / 8;
     constexpr int per_group = table_words(BITS, PAIR, SPLIT);
+    constexpr int kWpe = SPLIT ? 2 : 1;                       // words per pair-table entry
+    constexpr int kPairEntries = 1 << (2 * BITS);
+    constexpr int kRepRaw = kRepWords / (kPairEntries * kWpe);
+    constexpr int kRep = kRepRaw < 1 ? 1 : (kRepRaw > 32 / kWpe ? 32 / kWpe : kRepRaw);  // copies per entry
     const int my_tiles = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
     const int total_iters = my_tiles * k_blocks;
+    const int n_own = (grp < kGroups && total_iters > grp) ? (total_iters - grp + kGroups - 1) / kGroups : 0;
     const int n_rows = static_cast<int>(p.N);
     const int group_rows = static_cast<int>(p.group_rows);
-    // first packed byte of this thread's weight row (and k half) for a tile
-    auto row_ptr = [&](int t) -> const uint8_t* {
+    const bool rep = PAIR && p.rep != 0;
+    uint32_t* my_rep = rep_tables + grp * kRepWords;
+    const int gt = (dw & 3) * 32 + lane;            // thread index inside the group, 0..127
+    auto row_of = [&](int t) -> int {
       int row = (t / p.m_tiles) * kTileW + row_in_tile;
-      if (row >= n_rows) row = n_rows - 1;
-      return p.packed + static_cast<int64_t>(row) * row_bytes + half * (4 * BITS);
+      return row >= n_rows ? n_rows - 1 : row;
     };
-    uint32_t ws = 0, wph = 0;
-    const int dq_tid = tid - (2 + kNumEpilogueWarps) * 32;  // 0..255
+    auto advance = [&](int& t, int& kb, int steps) {
+      kb += steps;
+      while (kb >= k_blocks) { kb -= k_blocks; t += gridDim.x; }
+    };
+    const int dq_tid = tid - (2 + kNumEpilogueWarps) * 32;
     constexpr int kSlot = IdxSlot<BITS>::kBytes;
     constexpr int kRingStride = kNumDequantWarps * 32 * kSlot;
     const uint32_t ring_u32 = smem_u32(idx_ring + dq_tid * kSlot);  // slot s at + s * kRingStride
     const unsigned char* my_ring = idx_ring + dq_tid * kSlot;
-    // The packed indices of a stage are fetched kIdxPrefetch - 1 stages ahead (cp.async into this
-    // thread's own slot); the cursor walks (tile, k block) without divisions.
-    int pf_tile = blockIdx.x, pf_kb = 0, pf_slot = 0, pf_count = 0;
-    const uint8_t* pf_row = row_ptr(pf_tile);
+    // prefetch cursor: the packed indices of an own stage are fetched kIdxPrefetch - 1 own stages ahead
+    int pf_tile = blockIdx.x, pf_kb = 0, pf_slot = 0, pf_j = 0, pf_row_tile = -1;
+    advance(pf_tile, pf_kb, grp);
+    const uint8_t* pf_row = p.packed;
     auto prefetch_next = [&]() {
-      if (pf_count < total_iters) {
-        issue_unit<BITS>(ring_u32 + pf_slot * kRingStride, pf_row + pf_kb * (8 * BITS));
-        ++pf_count;
-        if (++pf_kb == k_blocks) {
-          pf_kb = 0;
-          pf_tile += gridDim.x;
-          if (pf_count < total_iters) pf_row = row_ptr(pf_tile);
+      if (pf_j < n_own) {
+        if (pf_tile != pf_row_tile) {
+          pf_row = p.packed + static_cast<int64_t>(row_of(pf_tile)) * row_bytes;
+          pf_row_tile = pf_tile;
         }
+        issue_unit<BITS>(ring_u32 + pf_slot * kRingStride, pf_row + pf_kb * (8 * BITS));
+        ++pf_j;
+        advance(pf_tile, pf_kb, kGroups);
       }
       cp_async_commit();
       if (++pf_slot == kIdxPrefetch) pf_slot = 0;
@@ -444,80 +475,110 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
 #pragma unroll
     for (int s0 = 0; s0 < kIdxPrefetch - 1; ++s0) prefetch_next();
     int slot = 0;
-    bool alive = true;
     unsigned long long w_we = 0, w_cp = 0;
     const long long t_begin = clock64();
-    bool pending = false;       // a tcgen05.st whose completion has not been published yet
-    uint32_t pending_ws = 0;
-    for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
-      int row = (t / p.m_tiles) * kTileW + row_in_tile;
-      if (row >= n_rows) row = n_rows - 1;
-      const uint32_t* tbl = table + (row / group_rows) * per_group;
+    // activation slot and parity of k block (it - kWStagesUsed) for this group's first waiting stage
+    uint32_t rel_slot, rel_par;
+    {
+      // first own stage that has to wait: the smallest it = grp + j * kGroups with it >= kWStagesUsed
+      int it0 = grp;
+      while (it0 < static_cast<int>(kWStagesUsed)) it0 += kGroups;
+      const uint32_t rel = static_cast<uint32_t>(it0) - kWStagesUsed;
+      rel_slot = rel % n_xs;
+      rel_par = (rel / n_xs) & 1u;
+    }
+    int t = blockIdx.x, kb = 0, cur_tile = -1, cur_group = -1;
+    advance(t, kb, grp);
+    const uint32_t* tbl = table;
 #pragma unroll 1
-      for (int kb = 0; kb < k_blocks; ++kb) {
+    for (int j = 0; j < n_own; ++j) {
+      const int it = grp + j * kGroups;
+      const uint32_t ws = static_cast<uint32_t>(it) % kWStagesUsed;
+      if (t != cur_tile) {
+        cur_tile = t;
+        const int g = row_of(t) / group_rows;
+        if (rep) {
+          // all 128 rows of the tile share codebook group g: (re)build this warp group's replicated
+          // table, entry e copied kRep times so that lane l reads copy (l mod kRep) in its own bank
+          const int g0 = ((t / p.m_tiles) * kTileW) / group_rows;
+          if (g0 != cur_group) {
+            bar_sync(1 + grp, 128);
+            const uint32_t* src = table + g0 * per_group;
+            for (int i = gt; i < kPairEntries * kRep; i += 128) {
+              const int e = i / kRep;
+              if (SPLIT) { my_rep[2 * i] = src[2 * e]; my_rep[2 * i + 1] = src[2 * e + 1]; }
+              else my_rep[i] = src[e];
+            }
+            bar_sync(1 + grp, 128);
+            cur_group = g0;
+          }
+          tbl = my_rep + (lane & (kRep - 1)) * kWpe;
+        } else {
+          tbl = table + g * per_group;
+        }
+      }
       prefetch_next();
       { const long long t0_ = p.prof ? clock64() : 0; cp_async_wait<kIdxPrefetch - 1>(); if (p.prof) w_cp += clock64() - t0_; }
-      uint32_t cur[BITS];
+      uint32_t cur[2 * BITS];
       read_unit<BITS>(my_ring + slot * kRingStride, cur);
       if (++slot == kIdxPrefetch) slot = 0;
-      uint32_t out[16];
-      uint32_t out_lo[SPLIT ? 16 : 1];
+      uint32_t out[32];
+      uint32_t out_lo[SPLIT ? 32 : 1];
       if (PAIR) {
+        const int stride = rep ? kRep * kWpe : kWpe;  // words between consecutive entries
 #pragma unroll
-        for (int q = 0; q < 16; ++q) {
-          const uint32_t v = get_field<BITS, 2 * BITS>(cur, q);
+        for (int q = 0; q < 32; ++q) {
+          const uint32_t v = get_field<2 * BITS, 2 * BITS>(cur, q);
           if (SPLIT) {
-            const uint2 e = reinterpret_cast<const uint2*>(tbl)[v];
+            const uint2 e = *reinterpret_cast<const uint2*>(tbl + v * stride);
             out[q] = e.x;
-            out_lo[q] = e.y;
+            out_lo[SPLIT ? q : 0] = e.y;
           } else {
-            out[q] = tbl[v];
+            out[q] = tbl[v * stride];
           }
         }
       } else if (SPLIT) {
 #pragma unroll
-        for (int q = 0; q < 16; ++q) {
-          const uint32_t a = tbl[get_field<BITS, BITS>(cur, 2 * q)];
-          const uint32_t b = tbl[get_field<BITS, BITS>(cur, 2 * q + 1)];
+        for (int q = 0; q < 32; ++q) {
+          const uint32_t a = tbl[get_field<2 * BITS, BITS>(cur, 2 * q)];
+          const uint32_t b = tbl[get_field<2 * BITS, BITS>(cur, 2 * q + 1)];
           out[q] = (a & 0xFFFFu) | (b << 16);
-          out_lo[q] = (a >> 16) | (b & 0xFFFF0000u);
+          out_lo[SPLIT ? q : 0] = (a >> 16) | (b & 0xFFFF0000u);
         }
       } else {
         const uint16_t* tbl16 = reinterpret_cast<const uint16_t*>(tbl);
 #pragma unroll
-        for (int q = 0; q < 16; ++q) {
-          const uint32_t lo = tbl16[get_field<BITS, BITS>(cur, 2 * q)];
-          const uint32_t hi = tbl16[get_field<BITS, BITS>(cur, 2 * q + 1)];
+        for (int q = 0; q < 32; ++q) {
+          const uint32_t lo = tbl16[get_field<2 * BITS, BITS>(cur, 2 * q)];
+          const uint32_t hi = tbl16[get_field<2 * BITS, BITS>(cur, 2 * q + 1)];
           out[q] = lo | (hi << 16);
         }
       }
-      // The store of the previous stage has had this stage's lookups to complete: publish it now.
-      if (pending) {
-        tmem_st_wait();
-        tc_fence_before();
-        mbar_arrive(smem_u32(&hdr->w_full[pending_ws]));
-        pending = false;
-      }
       // tcgen05.st is warp-collective: the whole warp proceeds or the whole warp gives up
-      if (!__all_sync(0xFFFFFFFFu, DIMQ_TIMED(w_we, mbar_wait(smem_u32(&hdr->w_empty[ws]), wph ^ 1u, abort_flag, 0x600u | ws)))) { alive = false; break; }
+      // weight slot ws was last read by k block (it - kWStagesUsed): wait for its commit, which was
+      // signalled on the activation slot of that k block
+      if (it >= static_cast<int>(kWStagesUsed)) {
+        if (!__all_sync(0xFFFFFFFFu, DIMQ_TIMED(w_we, mbar_wait(smem_u32(&hdr->x_empty[rel_slot]), rel_par, abort_flag, 0x600u | ws)))) break;
+        rel_slot += kGroups;
+        if (rel_slot >= n_xs) { rel_slot -= n_xs; rel_par ^= 1u; }
+      }
       tc_fence_after();
-      const uint32_t w_tmem = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kWCol + ws * kWStageCols + half * 16;
-      if (!(p.dbg & 2)) tmem_st16(w_tmem, out);
-      if (SPLIT && !(p.dbg & 2)) {
-        uint32_t lo16[16];
+      const uint32_t w_tmem = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kWCol + ws * kWStageCols;
+      if (!(p.dbg & 2)) {
+        tmem_st32(w_tmem, out);
+        if (SPLIT) {
+          uint32_t lo32[32];
 #pragma unroll
-        for (int q = 0; q < 16; ++q) lo16[q] = out_lo[SPLIT ? q : 0];
-        tmem_st16(w_tmem + kBlockK / 2, lo16);
+          for (int q = 0; q < 32; ++q) lo32[q] = out_lo[SPLIT ? q : 0];
+          tmem_st32(w_tmem + kBlockK / 2, lo32);
+        }
       }
-      pending = true;
-      pending_ws = ws;
-      if (++ws == kWStagesUsed) { ws = 0; wph ^= 1u; }
-      }
-    }
-    if (pending) {
+      // one arrival per warp: per-thread arrivals on one mbarrier serialise in shared memory
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(smem_u32(&hdr->w_full[pending_ws]));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&hdr->w_full[ws]));
+      advance(t, kb, kGroups);
     }
     if (p.prof && dq_tid == 0) { p.prof[blockIdx.x * 16 + 8] = w_we; p.prof[blockIdx.x * 16 + 9] = w_cp; p.prof[blockIdx.x * 16 + 10] = clock64() - t_begin; }
   }
@@ -624,9 +685,17 @@ int launch_linear_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, con
   const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
 
   const bool pair = w->bits != 8 && table_bytes(w->bits, w->groups, true, split) <= (size_t)kMaxTableBytes;
-  const size_t ring = static_cast<size_t>(kIdxPrefetch) * kNumDequantWarps * 32 * (w->bits == 8 ? 32 : 16);
-  const size_t smem = 1024 + static_cast<size_t>(kXStages) * kXStageBytes + 256 + ring +
-                      table_bytes(w->bits, w->groups, pair, split);
+  p.rep = 0;
+  if (const char* env = getenv("DIMQ_B200_TC_REP")) p.rep = (atoi(env) != 0 && (w->groups == 1 || w->group_rows % kTileW == 0)) ? 1 : 0;
+  const size_t fixed = 1024 + 256 + static_cast<size_t>(kIdxPrefetch) * kNumDequantWarps * 32 * (w->bits == 8 ? 64 : 32) +
+                       (p.rep ? static_cast<size_t>(kNumDequantGroups) * kRepWords * 4 : 0) +
+                       table_bytes(w->bits, w->groups, pair, split);
+  const size_t kSmemMax = 227 * 1024;
+  int x_stages = static_cast<int>((kSmemMax - fixed) / kXStageBytes);
+  if (x_stages > kXStages) x_stages = kXStages;
+  if (x_stages < 3) return DIMQ_ERR_UNSUPPORTED;
+  p.x_stages = x_stages;
+  const size_t smem = fixed + static_cast<size_t>(x_stages) * kXStageBytes;
 #define DIMQ_TC_CASE(B)                                                                            \
   case B:                                                                                          \
     if (B != 8 && pair) return split ? launch_tc<B, B != 8, true>(tmap, p, smem, grid, st)         \

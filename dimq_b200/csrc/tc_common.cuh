@@ -13,7 +13,10 @@ namespace tc {
 // Every spin on an mbarrier gives up after this many polls (each poll is a
 // try_wait that itself blocks for a hardware-defined slice), sets the CTA's
 // abort flag and records a status word; the kernel then drains and returns.
-constexpr uint32_t kSpinLimit = 1u << 20;
+constexpr uint32_t kSpinLimit = 1u << 17;
+// Upper bound (ns) the hardware may keep a waiting thread suspended inside one try_wait; the thread
+// is woken as soon as the phase completes, so a generous hint removes polling traffic, not latency.
+constexpr uint32_t kSuspendHintNs = 20000u;
 
 // Status word of the last tcgen05 kernel that gave up a wait (0 = none).
 __device__ uint32_t g_device_status;
@@ -39,11 +42,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t"
       "}\n"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return ok != 0;
 }
@@ -86,6 +89,21 @@ __device__ __forceinline__ void mma_f16_ts_acc(uint32_t d_tmem, uint32_t a_tmem,
       "}\n"
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc)
       : "memory");
+}
+
+// Bounded wait on two barriers at once: both polls are issued back to back so that their
+// latencies overlap (the MMA warp's critical path).
+__device__ __forceinline__ bool mbar_wait2(uint32_t bar_a, uint32_t par_a, uint32_t bar_b, uint32_t par_b,
+                                           volatile uint32_t* abort_flag, uint32_t code) {
+  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+    const bool a = mbar_try_wait(bar_a, par_a);
+    const bool b = mbar_try_wait(bar_b, par_b);
+    if (a && b) return true;
+    if ((it & 255u) == 255u && *abort_flag != 0u) return false;
+  }
+  *abort_flag = 1u;
+  atomicOr(&g_device_status, 0x80000000u | code);
+  return false;
 }
 
 __device__ __forceinline__ void fence_barrier_init() {
@@ -175,6 +193,21 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
         "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+// Named barrier among a subset of the CTA's warps (id 1..15; id 0 is __syncthreads).
+__device__ __forceinline__ void bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 

@@ -112,15 +112,20 @@ def build_vit_b16_checkpoint(*, seed: int = 0, device="cuda", bits: int = 3, gro
 class DIMQViT(nn.Module):
     """ViT-B/16 forward over packed DIMQ Linears (weight-only LUT GEMM), dense bf16 elsewhere."""
 
-    def __init__(self, checkpoint: dict[str, Any], *, act_dtype: torch.dtype = torch.bfloat16) -> None:
+    def __init__(self, checkpoint: dict[str, Any], *, act_dtype: torch.dtype = torch.bfloat16,
+                 fuse_epilogues: bool = False) -> None:
         super().__init__()
         self.cfg = dict(checkpoint["config"])
         self.act_dtype = act_dtype
+        # The LUT GEMM can apply GELU and add the residual in its epilogue.  On the ViT shapes the
+        # four epilogue warps are then the critical path (measured), so by default both run as
+        # separate memory-bound elementwise kernels.
+        self.fuse_epilogues = bool(fuse_epilogues)
         for key, value in checkpoint["non_quantized_state_dict"].items():
             self.register_buffer(key.replace(".", "__"), value.to(act_dtype))
         self.q = nn.ModuleDict()
         for name, layer in checkpoint["layers"].items():
-            epi = "gelu" if name.endswith("mlp.fc1") else None
+            epi = "gelu" if (name.endswith("mlp.fc1") and self.fuse_epilogues) else None
             out_dtype = torch.float32 if name == "head" else act_dtype
             self.q[name.replace(".", "__")] = DIMQLinear.from_export_layer(layer, out_dtype=out_dtype, epilogue=epi)
 
@@ -146,10 +151,16 @@ class DIMQViT(nn.Module):
             qkv = self._lin(pre + "attn.qkv")(h).view(b, t, 3, heads, hid // heads).permute(2, 0, 3, 1, 4)
             a = F.scaled_dot_product_attention(qkv[0], qkv[1], qkv[2])
             a = a.transpose(1, 2).reshape(b, t, hid)
-            x = self._lin(pre + "attn.proj")(a, residual=x)
+            if self.fuse_epilogues:
+                x = self._lin(pre + "attn.proj")(a, residual=x)
+            else:
+                x = x + self._lin(pre + "attn.proj")(a)
             h = F.layer_norm(x, (hid,), self._t(pre + "norm2.weight"), self._t(pre + "norm2.bias"), 1e-6)
             h = self._lin(pre + "mlp.fc1")(h)
-            x = self._lin(pre + "mlp.fc2")(h, residual=x)
+            if self.fuse_epilogues:
+                x = self._lin(pre + "mlp.fc2")(h, residual=x)
+            else:
+                x = x + self._lin(pre + "mlp.fc2")(F.gelu(h))
         cls = F.layer_norm(x[:, 0], (hid,), self._t("norm.weight"), self._t("norm.bias"), 1e-6)
         return self._lin("head")(cls.contiguous())
 
