@@ -176,6 +176,7 @@ def main() -> None:
     import torch.distributed as dist
 
     from dimq_b200 import _lib, ops
+    from dimq_b200.dist import gather_logits
     from dimq_b200.workloads import DIMQViT, build_vit_b16_checkpoint
 
     ops.require_extension()  # no CPU fallback: fail loudly when the CUDA library is missing
@@ -202,7 +203,6 @@ def main() -> None:
         # ---- CUDA graphs: one per resident input buffer, plus one reading a staging buffer (e2e) ----
         stream = torch.cuda.Stream(device=dev)
         staging = torch.empty_like(dev_images[0])
-        gathered = torch.empty(world * B, 1000, dtype=torch.float32, device=dev) if world > 1 else None
         host_logits = torch.empty(B, 1000, dtype=torch.float32).pin_memory()
         graphs, outs = [], []
         with torch.cuda.stream(stream):
@@ -226,13 +226,13 @@ def main() -> None:
         def step_resident(i: int) -> None:
             graphs[i % n_bufs].replay()
             if world > 1:
-                dist.all_gather_into_tensor(gathered, outs[i % n_bufs])
+                gather_logits(outs[i % n_bufs])
 
         def step_e2e(i: int) -> None:
             staging.copy_(host_images[i % n_bufs], non_blocking=True)
             graphs[n_bufs].replay()
             if world > 1:
-                dist.all_gather_into_tensor(gathered, outs[n_bufs])
+                gather_logits(outs[n_bufs])
             host_logits.copy_(outs[n_bufs], non_blocking=True)
 
         def timed(step_fn) -> float:

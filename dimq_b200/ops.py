@@ -512,6 +512,34 @@ def dimq_conv2d_wq(x: torch.Tensor, packed_weight: torch.Tensor, codebooks: torc
     return y
 
 
+def add_layer_norm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, bias: torch.Tensor,
+                   eps: float = 1e-6):
+    """``(x + delta, LayerNorm(x + delta))`` over the last dimension (``delta=None``: ``(x, LayerNorm(x))``).
+
+    bf16 / fp16 CUDA tensors with a last dimension that is a multiple of 8 and at most 1024.
+    """
+    require_extension()
+    _require_cuda(x, "add_layer_norm")
+    cols = x.shape[-1]
+    xc = x.contiguous()
+    dc = None if delta is None else delta.contiguous()
+    if dc is not None and (dc.shape != xc.shape or dc.dtype != xc.dtype):
+        raise RuntimeError("delta must match x in shape and dtype")
+    w = weight.to(xc.dtype).contiguous()
+    b = bias.to(xc.dtype).contiguous()
+    if w.numel() != cols or b.numel() != cols:
+        raise RuntimeError("weight / bias must have one element per column")
+    x_out = torch.empty_like(xc) if dc is not None else xc
+    h = torch.empty_like(xc)
+    with torch.cuda.device(xc.device):
+        st = _lib.lib().dimq_add_layer_norm(_lib.ptr(xc), _lib.ptr(dc), _lib.ptr(w), _lib.ptr(b),
+                                            _lib.ptr(x_out) if dc is not None else C.c_void_p(0), _lib.ptr(h),
+                                            C.c_int64(xc.numel() // cols), C.c_int64(cols), C.c_float(eps),
+                                            _lib.dtype_code(xc, "x"), _lib.stream_ptr(xc.device))
+    _lib.check(st, "add_layer_norm")
+    return x_out, h
+
+
 def last_device_status() -> int:
     """Status word left by a tensor-core kernel that gave up a bounded wait (0 = none); clears it."""
     require_extension()

@@ -37,20 +37,25 @@ def quantile_codebooks(w: torch.Tensor, entries: int, group_rows: int) -> torch.
     rows = w.shape[0]
     flat = w.reshape(rows, -1).float()
     q = torch.linspace(0.0, 1.0, entries + 2, device=w.device, dtype=torch.float32)[1:-1]
+    n_groups = (rows + group_rows - 1) // group_rows
+    if rows % group_rows == 0:
+        samples = [flat.reshape(n_groups, -1)]                      # all groups in one batched call
+    else:
+        full = (rows // group_rows) * group_rows
+        samples = ([flat[:full].reshape(rows // group_rows, -1)] if full else []) + [flat[full:].reshape(1, -1)]
     books = []
-    for g0 in range(0, rows, group_rows):
-        sample = flat[g0 : g0 + group_rows].reshape(-1)
-        centers = torch.quantile(sample, q).sort().values
-        span = (sample.max() - sample.min()).abs()
-        sigma = sample.std(unbiased=False).abs()
+    for sample in samples:
+        centers = torch.quantile(sample, q, dim=1).t().contiguous().sort(dim=1).values   # [g, entries]
+        span = (sample.max(dim=1).values - sample.min(dim=1).values).abs()
+        sigma = sample.std(dim=1, unbiased=False).abs()
         min_gap = torch.maximum(span, sigma).clamp_min(1e-6) * 1e-6
         fixed = centers.clone()
         for i in range(1, entries):
-            if fixed[i] <= fixed[i - 1]:
-                fixed[i] = fixed[i - 1] + min_gap
-        fixed = fixed - (fixed.mean() - centers.mean())
-        books.append(fixed.sort().values)
-    return torch.stack(books)
+            bump = fixed[:, i] <= fixed[:, i - 1]
+            fixed[:, i] = torch.where(bump, fixed[:, i - 1] + min_gap, fixed[:, i])
+        fixed = fixed - (fixed.mean(dim=1, keepdim=True) - centers.mean(dim=1, keepdim=True))
+        books.append(fixed.sort(dim=1).values)
+    return torch.cat(books, dim=0)
 
 
 def quantize_linear(weight: torch.Tensor, bias: torch.Tensor | None, bits: int, group_rows: int | None,
@@ -139,30 +144,43 @@ class DIMQViT(nn.Module):
         cfg = self.cfg
         hid, heads = cfg["hidden"], cfg["heads"]
         b = images.shape[0]
-        x = F.conv2d(images.to(self.act_dtype), self._t("patch_embed.weight"), self._t("patch_embed.bias"),
-                     stride=cfg["patch"])
-        x = x.flatten(2).transpose(1, 2)
-        x = torch.cat([self._t("cls_token").expand(b, -1, -1), x], dim=1) + self._t("pos_embed")
+        p = cfg["patch"]
+        g = cfg["image"] // p
+        # patch embedding (dense bf16): a stride-p conv is a GEMM over flattened (c, kh, kw) patches
+        patches = images.to(self.act_dtype).view(b, 3, g, p, g, p).permute(0, 2, 4, 1, 3, 5).reshape(b * g * g, 3 * p * p)
+        x = torch.addmm(self._t("patch_embed.bias"), patches, self._t("patch_embed.weight").view(hid, -1).t())
+        x = torch.cat([self._t("cls_token").expand(b, -1, -1), x.view(b, g * g, hid)], dim=1) + self._t("pos_embed")
         x = x.contiguous()
         t = x.shape[1]
+        if self.fuse_epilogues:
+            for i in range(cfg["layers"]):
+                pre = f"blocks.{i}."
+                h = F.layer_norm(x, (hid,), self._t(pre + "norm1.weight"), self._t(pre + "norm1.bias"), 1e-6)
+                a = self._attention(self._lin(pre + "attn.qkv")(h), b, t)
+                x = self._lin(pre + "attn.proj")(a, residual=x)
+                h = F.layer_norm(x, (hid,), self._t(pre + "norm2.weight"), self._t(pre + "norm2.bias"), 1e-6)
+                x = self._lin(pre + "mlp.fc2")(self._lin(pre + "mlp.fc1")(h), residual=x)
+            cls = F.layer_norm(x[:, 0], (hid,), self._t("norm.weight"), self._t("norm.bias"), 1e-6)
+            return self._lin("head")(cls.contiguous())
+        # default: each residual add is fused with the LayerNorm that follows it (one pass over the
+        # residual stream instead of two); GELU is a separate elementwise kernel
+        delta = None
         for i in range(cfg["layers"]):
             pre = f"blocks.{i}."
-            h = F.layer_norm(x, (hid,), self._t(pre + "norm1.weight"), self._t(pre + "norm1.bias"), 1e-6)
-            qkv = self._lin(pre + "attn.qkv")(h).view(b, t, 3, heads, hid // heads).permute(2, 0, 3, 1, 4)
-            a = F.scaled_dot_product_attention(qkv[0], qkv[1], qkv[2])
-            a = a.transpose(1, 2).reshape(b, t, hid)
-            if self.fuse_epilogues:
-                x = self._lin(pre + "attn.proj")(a, residual=x)
-            else:
-                x = x + self._lin(pre + "attn.proj")(a)
-            h = F.layer_norm(x, (hid,), self._t(pre + "norm2.weight"), self._t(pre + "norm2.bias"), 1e-6)
-            h = self._lin(pre + "mlp.fc1")(h)
-            if self.fuse_epilogues:
-                x = self._lin(pre + "mlp.fc2")(h, residual=x)
-            else:
-                x = x + self._lin(pre + "mlp.fc2")(F.gelu(h))
-        cls = F.layer_norm(x[:, 0], (hid,), self._t("norm.weight"), self._t("norm.bias"), 1e-6)
-        return self._lin("head")(cls.contiguous())
+            x, h = ops.add_layer_norm(x, delta, self._t(pre + "norm1.weight"), self._t(pre + "norm1.bias"), 1e-6)
+            a = self._attention(self._lin(pre + "attn.qkv")(h), b, t)
+            x, h = ops.add_layer_norm(x, self._lin(pre + "attn.proj")(a), self._t(pre + "norm2.weight"),
+                                      self._t(pre + "norm2.bias"), 1e-6)
+            delta = self._lin(pre + "mlp.fc2")(F.gelu(self._lin(pre + "mlp.fc1")(h)))
+        _, cls = ops.add_layer_norm(x[:, 0].contiguous(), delta[:, 0].contiguous(), self._t("norm.weight"),
+                                    self._t("norm.bias"), 1e-6)
+        return self._lin("head")(cls)
+
+    def _attention(self, qkv: torch.Tensor, b: int, t: int) -> torch.Tensor:
+        hid, heads = self.cfg["hidden"], self.cfg["heads"]
+        qkv = qkv.view(b, t, 3, heads, hid // heads).permute(2, 0, 3, 1, 4)
+        a = F.scaled_dot_product_attention(qkv[0], qkv[1], qkv[2])
+        return a.transpose(1, 2).reshape(b, t, hid)
 
     def lut_gemm_flops(self, batch: int) -> float:
         """Algorithmic flops (2*M*N*K) of the quantised Linears for one forward of ``batch`` images."""

@@ -163,6 +163,17 @@ DIMQ_API int dimq_conv2d_wq(const void* x, int x_dtype, const dimq_wq_weight* w,
                    const void* residual, void* y, int y_dtype, const dimq_conv_geom* geom, int epilogue,
                    int algo, void* stream);
 
+/* ---- dense helper of the whole-model harness --------------------------- */
+
+/* h_out = LayerNorm(x [+ delta]) * gamma + beta over rows of `cols` 16-bit elements (DIMQ_BF16 or
+ * DIMQ_F16), statistics in fp32; with delta != NULL the sum x + delta (rounded to the element type)
+ * is also written to x_out (the residual stream).  cols % 8 == 0, cols <= 1024, 16-byte aligned rows.
+ * No counterpart in the reference: its models use torch.nn.LayerNorm; this fuses the residual add of
+ * a transformer block with the normalisation that follows it. */
+DIMQ_API int dimq_add_layer_norm(const void* x, const void* delta, const void* gamma, const void* beta,
+                                 void* x_out, void* h_out, int64_t rows, int64_t cols, float eps, int dtype,
+                                 void* stream);
+
 /* Status word written by the last tcgen05 kernel on this thread's device that
  * gave up a bounded wait (0 = none).  Reading it synchronises the device. */
 DIMQ_API int dimq_last_device_status(uint32_t* status);

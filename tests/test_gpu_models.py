@@ -90,3 +90,28 @@ def test_vit_forward_matches_cpu_oracle(vit):
         got_fused = fused(images.cuda()).float().cpu().numpy()
     _, rel_fused = o.parity_metrics(got_fused, want_bf16)
     assert rel_fused <= 1.5e-2, rel_fused
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_add_layer_norm_matches_torch(cuda_device, dtype):
+    from dimq_b200 import ops
+
+    torch.manual_seed(1)
+    x = torch.randn(5, 197, 768, device="cuda").to(dtype)
+    d = torch.randn(5, 197, 768, device="cuda").to(dtype)
+    w = (1 + 0.1 * torch.randn(768, device="cuda")).to(dtype)
+    b = (0.1 * torch.randn(768, device="cuda")).to(dtype)
+    x_out, h = ops.add_layer_norm(x, d, w, b, 1e-6)
+    want_x = x + d
+    assert torch.equal(x_out, want_x)
+    want_h = torch.nn.functional.layer_norm(want_x.float(), (768,), w.float(), b.float(), 1e-6)
+    assert (h.float() - want_h).abs().max().item() <= (4e-2 if dtype == torch.bfloat16 else 6e-3)
+    same, h2 = ops.add_layer_norm(x, None, w, b, 1e-6)
+    assert same.data_ptr() == x.data_ptr()
+    want_h2 = torch.nn.functional.layer_norm(x.float(), (768,), w.float(), b.float(), 1e-6)
+    assert (h2.float() - want_h2).abs().max().item() <= (4e-2 if dtype == torch.bfloat16 else 6e-3)
+    _, h3 = ops.add_layer_norm(x[:, 0, :264].contiguous(), None, w[:264], b[:264], 1e-6)   # ragged: 33 vectors
+    want_h3 = torch.nn.functional.layer_norm(x[:, 0, :264].float(), (264,), w[:264].float(), b[:264].float(), 1e-6)
+    assert (h3.float() - want_h3).abs().max().item() <= (4e-2 if dtype == torch.bfloat16 else 6e-3)
+    with pytest.raises(RuntimeError):
+        ops.add_layer_norm(x[..., :100].contiguous(), None, w[:100], b[:100])
