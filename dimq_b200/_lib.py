@@ -17,7 +17,7 @@ LIB_PATH = PKG / "libdimq_b200.so"
 
 F32, F16, BF16 = 0, 1, 2
 ALGO_AUTO, ALGO_GENERIC, ALGO_STREAM, ALGO_TCGEN05 = 0, 1, 2, 3
-EPI_NONE, EPI_RELU, EPI_GELU = 0, 1, 2
+EPI_NONE, EPI_RELU, EPI_GELU, EPI_ADD_RELU = 0, 1, 2, 3
 
 _DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 
@@ -26,7 +26,7 @@ EXPORTED_SYMBOLS = (
     "dimq_version", "dimq_status_string", "dimq_pack_u4", "dimq_unpack_u4", "dimq_pack_bits",
     "dimq_unpack_bits", "dimq_quantize_activation_u4", "dimq_build_product_table", "dimq_linear_lut",
     "dimq_conv_out_size", "dimq_conv2d_lut", "dimq_hard_quantize", "dimq_linear_wq", "dimq_conv2d_wq",
-    "dimq_last_device_status", "dimq_add_layer_norm",
+    "dimq_last_device_status", "dimq_add_layer_norm", "dimq_conv_prepack",
 )
 
 
@@ -39,7 +39,7 @@ class ConvGeom(C.Structure):
 
 class WqWeight(C.Structure):
     _fields_ = [("packed", C.c_void_p), ("bits", C.c_int32), ("codebooks", C.c_void_p), ("cb_dtype", C.c_int32),
-                ("entries", C.c_int32), ("groups", C.c_int64), ("group_rows", C.c_int64)]
+                ("entries", C.c_int32), ("groups", C.c_int64), ("group_rows", C.c_int64), ("packed_khwc", C.c_void_p)]
 
 
 @lru_cache(maxsize=1)

@@ -18,6 +18,10 @@ bool tc_supported(const void* x, int x_dtype, const dimq_wq_weight* w, int64_t M
 int launch_linear_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
                         const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K, int epilogue,
                         int precision, cudaStream_t st);
+bool conv_tc_supported(const void* x, int x_dtype, const dimq_wq_weight* w, const dimq_conv_geom* g, int y_dtype);
+int launch_conv2d_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
+                        const void* residual, void* y, int y_dtype, const dimq_conv_geom* g, int epilogue,
+                        cudaStream_t st);
 int read_device_status(uint32_t* status);
 }  // namespace dimq
 
@@ -56,7 +60,7 @@ extern "C" int dimq_linear_wq(const void* x, int x_dtype, const dimq_wq_weight* 
   if (M < 0 || N <= 0 || K <= 0) return DIMQ_ERR_BAD_SIZE;
   if (!valid_dtype(x_dtype) || !valid_dtype(y_dtype)) return DIMQ_ERR_BAD_DTYPE;
   if (bias != nullptr && !valid_dtype(bias_dtype)) return DIMQ_ERR_BAD_DTYPE;
-  if (epilogue < DIMQ_EPI_NONE || epilogue > DIMQ_EPI_GELU) return DIMQ_ERR_UNSUPPORTED;
+  if (epilogue < DIMQ_EPI_NONE || epilogue > DIMQ_EPI_ADD_RELU) return DIMQ_ERR_UNSUPPORTED;
   const int rc = check_wq_weight(w, N);
   if (rc != DIMQ_OK) return rc;
   if (M == 0) return DIMQ_OK;
@@ -91,12 +95,16 @@ extern "C" int dimq_conv2d_wq(const void* x, int x_dtype, const dimq_wq_weight* 
   if (g.out_h != geom->out_h || g.out_w != geom->out_w) return DIMQ_ERR_BAD_SHAPE;
   if (!valid_dtype(x_dtype) || !valid_dtype(y_dtype)) return DIMQ_ERR_BAD_DTYPE;
   if (bias != nullptr && !valid_dtype(bias_dtype)) return DIMQ_ERR_BAD_DTYPE;
-  if (epilogue < DIMQ_EPI_NONE || epilogue > DIMQ_EPI_GELU) return DIMQ_ERR_UNSUPPORTED;
+  if (epilogue < DIMQ_EPI_NONE || epilogue > DIMQ_EPI_ADD_RELU) return DIMQ_ERR_UNSUPPORTED;
   rc = check_wq_weight(w, g.out_channels);
   if (rc != DIMQ_OK) return rc;
   if (static_cast<int64_t>(g.batch) * g.out_channels * g.out_h * g.out_w == 0) return DIMQ_OK;
   if (x == nullptr || y == nullptr) return DIMQ_ERR_NULL_POINTER;
-  if (algo != DIMQ_ALGO_AUTO && algo != DIMQ_ALGO_GENERIC) return DIMQ_ERR_UNSUPPORTED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (algo == DIMQ_ALGO_AUTO) algo = conv_tc_supported(x, x_dtype, w, &g, y_dtype) ? DIMQ_ALGO_TCGEN05 : DIMQ_ALGO_GENERIC;
+  if (algo == DIMQ_ALGO_TCGEN05)
+    return launch_conv2d_wq_tc(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, &g, epilogue, st);
+  if (algo != DIMQ_ALGO_GENERIC) return DIMQ_ERR_UNSUPPORTED;
   return launch_conv2d_direct(false, x, x_dtype, w, 1.0f, 0, bias, bias_dtype, residual, y, y_dtype, &g, epilogue,
                               static_cast<cudaStream_t>(stream));
 }

@@ -81,6 +81,14 @@ __device__ __forceinline__ float apply_epilogue(float v, int epilogue) {
   return v;
 }
 
+// accumulator (+bias) -> output value.  DIMQ_EPI_ADD_RELU adds the residual before the ReLU; the
+// other epilogues apply the activation first and add the residual after it.
+__device__ __forceinline__ float finish_value(float v, int epilogue, bool has_res, float res) {
+  if (epilogue == DIMQ_EPI_ADD_RELU) return fmaxf(has_res ? v + res : v, 0.0f);
+  v = apply_epilogue(v, epilogue);
+  return has_res ? v + res : v;
+}
+
 inline bool valid_dtype(int d) { return d == DIMQ_F32 || d == DIMQ_F16 || d == DIMQ_BF16; }
 inline int dtype_size(int d) { return d == DIMQ_F32 ? 4 : 2; }
 inline bool valid_bits(int b) { return b == 1 || b == 2 || b == 3 || b == 4 || b == 8; }

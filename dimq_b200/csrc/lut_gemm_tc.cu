@@ -20,6 +20,7 @@
 // allocator, warps 2-5 epilogue, warps 6-13 dequantisation.  Persistent grid:
 // one CTA per SM walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...
 #include <cstdlib>
+#include <cstring>
 
 #include "tc_common.cuh"
 
@@ -65,9 +66,21 @@ struct TcParams {
   uint32_t idesc;
   int m_tiles, n_tiles;
   int x_stages;               // activation stages that fit shared memory (3..kXStages)
+  int tx;                     // activation rows per tile (UMMA N): 192 for the GEMM, 16..192 for conv
+  uint32_t x_stage_bytes;     // tx * 128
+  // implicit-GEMM convolution (conv != 0): activation rows are output pixels, a tile is a
+  // tw x th x tb box of (ow, oh, batch); k runs over (kh, kw, ci) in blocks of 64 channels
+  int conv;
+  int tw, th, tb, tiles_w, tiles_h;
+  int OW, OH, Bn;
+  int stride, pad_h, pad_w, dil_h, dil_w, KW, c_blocks;
   int rep;                    // 1: every 128-row tile lies in one codebook group -> replicated tables
   int dbg;                    // diagnostics: 1 skip epilogue work, 2 skip dequant work, 4 skip MMAs
   unsigned long long* prof;   // optional per-CTA wait-cycle counters (diagnostics), else null
+};
+
+struct TmapSet {
+  CUtensorMap m[4];   // GEMM: m[0]; conv: one map per (row, column) parity of a stride-2 input
 };
 
 struct SharedHeader {
@@ -121,6 +134,19 @@ __device__ __forceinline__ uint32_t to_operand16(float v, int w_fmt) {
 }
 
 
+// accumulator + bias -> activation / residual.  DIMQ_EPI_ADD_RELU adds the residual before the ReLU
+// (a ResNet block); the other epilogues apply the activation first and add the residual after it.
+template <typename T, bool RES>
+__device__ __forceinline__ float finish(float v, int epilogue, const T* res) {
+  if (epilogue == DIMQ_EPI_ADD_RELU) {
+    if (RES) v += to_float<T>(*res);
+    return fmaxf(v, 0.0f);
+  }
+  v = apply_epilogue(v, epilogue);
+  if (RES) v += to_float<T>(*res);
+  return v;
+}
+
 // Epilogue of one 32-column chunk: thread = output feature n, r[j] = accumulator of activation row
 // (m_first + j).  yp / rp point at element [m_first][n]; a warp store covers 32 consecutive n.
 template <typename T, bool RES>
@@ -129,18 +155,12 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], T* __restri
   if (rows >= 32) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
-      float v = apply_epilogue(__uint_as_float(r[j]) + bias, epilogue);
-      if (RES) v += to_float<T>(rp[j * ld]);
-      yp[j * ld] = from_float<T>(v);
+      yp[j * ld] = from_float<T>(finish<T, RES>(__uint_as_float(r[j]) + bias, epilogue, RES ? rp + j * ld : nullptr));
     }
   } else {
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
-      if (j < rows) {
-        float v = apply_epilogue(__uint_as_float(r[j]) + bias, epilogue);
-        if (RES) v += to_float<T>(rp[j * ld]);
-        yp[j * ld] = from_float<T>(v);
-      }
+      if (j < rows) yp[j * ld] = from_float<T>(finish<T, RES>(__uint_as_float(r[j]) + bias, epilogue, RES ? rp + j * ld : nullptr));
     }
   }
 }
@@ -152,6 +172,28 @@ __device__ __forceinline__ void store_chunk_t(const uint32_t (&r)[32], void* y, 
     store_chunk<T, true>(r, static_cast<T*>(y) + off, static_cast<const T*>(res) + off, ld, rows, bias, epilogue);
   else
     store_chunk<T, false>(r, static_cast<T*>(y) + off, nullptr, ld, rows, bias, epilogue);
+}
+
+// Convolution epilogue of one chunk: column (p0 + j) of the tile is output pixel
+// (b0 + bb, oh0 + hh, ow0 + ww) with ww fastest; y and the residual are NHWC.
+template <typename T>
+__device__ __forceinline__ void store_chunk_conv(const uint32_t (&r)[32], const TcParams& p, int p0, int m_blk,
+                                                 int64_t n, float bias) {
+  const int ow0 = (m_blk % p.tiles_w) * p.tw;
+  const int oh0 = ((m_blk / p.tiles_w) % p.tiles_h) * p.th;
+  const int b0 = (m_blk / (p.tiles_w * p.tiles_h)) * p.tb;
+  int ww = p0 % p.tw, hh = (p0 / p.tw) % p.th, bb = p0 / (p.tw * p.th);
+  T* y = static_cast<T*>(p.y);
+  const T* res = static_cast<const T*>(p.residual);
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    if (p0 + j < p.tx && b0 + bb < p.Bn && oh0 + hh < p.OH && ow0 + ww < p.OW) {
+      const int64_t off = ((static_cast<int64_t>(b0 + bb) * p.OH + (oh0 + hh)) * p.OW + (ow0 + ww)) * p.N + n;
+      const float v = __uint_as_float(r[j]) + bias;
+      y[off] = from_float<T>(res != nullptr ? finish<T, true>(v, p.epilogue, res + off) : finish<T, false>(v, p.epilogue, nullptr));
+    }
+    if (++ww == p.tw) { ww = 0; if (++hh == p.th) { hh = 0; ++bb; } }
+  }
 }
 
 __device__ __forceinline__ void cp_async(uint32_t dst, const void* src, int bytes) {
@@ -214,13 +256,13 @@ __device__ __forceinline__ void split_bf16(float c, uint32_t& hi, uint32_t& lo) 
 
 template <int BITS, bool PAIR, bool SPLIT>
 __global__ void __launch_bounds__(kThreads, 1)
-linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
+linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // [x stages (1024-aligned)] [header] [tables]
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* x_stage = smem;
   const uint32_t n_xs = static_cast<uint32_t>(p.x_stages);
-  SharedHeader* hdr = reinterpret_cast<SharedHeader*>(smem + n_xs * kXStageBytes);
+  SharedHeader* hdr = reinterpret_cast<SharedHeader*>(smem + n_xs * p.x_stage_bytes);
   unsigned char* idx_ring = reinterpret_cast<unsigned char*>(hdr) + 256;  // [kIdxPrefetch][dequant threads][slot]
   constexpr int kRingBytes = kIdxPrefetch * kNumDequantWarps * 32 * IdxSlot<BITS>::kBytes;
   uint32_t* rep_tables = reinterpret_cast<uint32_t*>(idx_ring + kRingBytes);  // [groups of warps][kRepWords]
@@ -241,7 +283,7 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
     for (int s = 0; s < kAccStages; ++s) { mbar_init(smem_u32(&hdr->d_full[s]), 1); mbar_init(smem_u32(&hdr->d_empty[s]), kNumEpilogueWarps); }
     hdr->abort_flag = 0u;
     fence_barrier_init();
-    prefetch_tensormap(&tmap_x);
+    prefetch_tensormap(&tmaps.m[0]);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&hdr->tmem_base), kTmemCols);
@@ -295,14 +337,37 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
       const long long t_begin = clock64();
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         const int m_blk = t % p.m_tiles;
+        int ow0 = 0, oh0 = 0, b0 = 0, tap = 0, cb = 0;
+        if (p.conv) {
+          ow0 = (m_blk % p.tiles_w) * p.tw;
+          oh0 = ((m_blk / p.tiles_w) % p.tiles_h) * p.th;
+          b0 = (m_blk / (p.tiles_w * p.tiles_h)) * p.tb;
+        }
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!DIMQ_TIMED(w_xe, mbar_wait(smem_u32(&hdr->x_empty[stage]), phase ^ 1u, abort_flag, 0x100u | stage))) { ok = false; break; }
           const uint32_t full = smem_u32(&hdr->x_full[stage]);
+          const uint32_t dst = smem_u32(x_stage + stage * p.x_stage_bytes);
           if (p.dbg & 8) {
             mbar_arrive(full);
+          } else if (!p.conv) {
+            mbar_arrive_expect_tx(full, p.x_stage_bytes);
+            tma_load_2d(dst, &tmaps.m[0], full, kb * kBlockK, m_blk * p.tx);
           } else {
-            mbar_arrive_expect_tx(full, kXStageBytes);
-            tma_load_2d(smem_u32(x_stage + stage * kXStageBytes), &tmap_x, full, kb * kBlockK, m_blk * kTileX);
+            // tap (kh, kw), channels [64 cb, 64 cb + 64): input pixel = s * out + tap offset.  With
+            // stride 2 the input is addressed through one tensor map per (row, column) parity, so the
+            // box stays dense; taps that fall outside the image read the zero fill.
+            const int kh = tap / p.KW, kw = tap - kh * p.KW;
+            const int dy = kh * p.dil_h - p.pad_h, dx = kw * p.dil_w - p.pad_w;
+            int map = 0, hy = oh0 + dy, wx = ow0 + dx;
+            if (p.stride == 2) {
+              const int py = dy & 1, px = dx & 1;          // parity (two's complement: also right for negatives)
+              map = py * 2 + px;
+              hy = oh0 + ((dy - py) >> 1);
+              wx = ow0 + ((dx - px) >> 1);
+            }
+            mbar_arrive_expect_tx(full, p.x_stage_bytes);
+            tma_load_4d(dst, &tmaps.m[map], full, cb * kBlockK, wx, hy, b0);
+            if (++cb == p.c_blocks) { cb = 0; ++tap; }
           }
           ++issued;
           if (++stage == n_xs) { stage = 0; phase ^= 1u; }
@@ -339,7 +404,7 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
           long long tq0 = p.prof ? clock64() : 0;
           tc_fence_after();
           if (p.prof) { const long long tq1 = clock64(); t_fe += tq1 - tq0; tq0 = tq1; }
-          const uint64_t b_desc = desc0 + static_cast<uint64_t>(xs * (kXStageBytes >> 4));
+          const uint64_t b_desc = desc0 + static_cast<uint64_t>(xs * (p.x_stage_bytes >> 4));
           const uint32_t a_tmem = a0 + ws * kWStageCols;
           // advance 16 k: 32 bytes inside the swizzled row (encoded >> 4), 8 TMEM columns
           if (!(p.dbg & 4)) {
@@ -380,35 +445,42 @@ linear_wq_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       const int m_blk = t % p.m_tiles, n_blk = t / p.m_tiles;
       const int64_t n = static_cast<int64_t>(n_blk) * kTileW + quarter * 32 + lane;
-      const int64_t m0 = static_cast<int64_t>(m_blk) * kTileX;
+      const int64_t m0 = static_cast<int64_t>(m_blk) * p.tx;
       const bool n_ok = n < p.N;
       const float bias = (p.bias != nullptr && n_ok) ? load_as_float(p.bias, p.bias_dtype, n) : 0.0f;
       // tcgen05.ld is warp-collective: the whole warp proceeds or the whole warp gives up
       if (!__all_sync(0xFFFFFFFFu, DIMQ_TIMED(w_df, mbar_wait(smem_u32(&hdr->d_full[as]), aph, abort_flag, 0x500u | as)))) { ok = false; break; }
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kAccCol + as * kTileX;
+      const int n_chunks = (p.tx + 31) / 32;
 #pragma unroll 1
       if (p.dbg & 1) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(smem_u32(&hdr->d_empty[as])); }
       else
-      for (int c = 0; c < kTileX / 32; ++c) {
+      for (int c = 0; c < n_chunks; ++c) {
         uint32_t r[32];
         __syncwarp();
         tmem_ld32(d_tmem + c * 32, r);
         tmem_ld_wait();
-        if (c == kTileX / 32 - 1) {
+        if (c == n_chunks - 1) {
           // every column of this buffer is in registers: hand it back to the MMA warp
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&hdr->d_empty[as]));
         }
-        const int64_t m_first = m0 + c * 32;
-        const int64_t rows64 = p.M - m_first;
-        const int rows = rows64 >= 32 ? 32 : static_cast<int>(rows64);
-        if (n_ok && rows > 0) {
-          const int64_t off = m_first * p.N + n;
-          if (p.y_dtype == DIMQ_BF16) store_chunk_t<__nv_bfloat16>(r, p.y, p.residual, off, p.N, rows, bias, p.epilogue);
-          else if (p.y_dtype == DIMQ_F16) store_chunk_t<__half>(r, p.y, p.residual, off, p.N, rows, bias, p.epilogue);
-          else store_chunk_t<float>(r, p.y, p.residual, off, p.N, rows, bias, p.epilogue);
+        if (!p.conv) {
+          const int64_t m_first = m0 + c * 32;
+          const int64_t rows64 = p.M - m_first;
+          const int rows = rows64 >= 32 ? 32 : static_cast<int>(rows64);
+          if (n_ok && rows > 0) {
+            const int64_t off = m_first * p.N + n;
+            if (p.y_dtype == DIMQ_BF16) store_chunk_t<__nv_bfloat16>(r, p.y, p.residual, off, p.N, rows, bias, p.epilogue);
+            else if (p.y_dtype == DIMQ_F16) store_chunk_t<__half>(r, p.y, p.residual, off, p.N, rows, bias, p.epilogue);
+            else store_chunk_t<float>(r, p.y, p.residual, off, p.N, rows, bias, p.epilogue);
+          }
+        } else if (n_ok) {
+          if (p.y_dtype == DIMQ_BF16) store_chunk_conv<__nv_bfloat16>(r, p, c * 32, m_blk, n, bias);
+          else if (p.y_dtype == DIMQ_F16) store_chunk_conv<__half>(r, p, c * 32, m_blk, n, bias);
+          else store_chunk_conv<float>(r, p, c * 32, m_blk, n, bias);
         }
       }
       if (++as == kAccStages) { as = 0; aph ^= 1u; }
@@ -611,7 +683,7 @@ EncodeTiledFn get_encode_tiled() {
 }
 
 template <int BITS, bool PAIR, bool SPLIT>
-int launch_tc(const CUtensorMap& tmap, const TcParams& p, size_t smem, int grid, cudaStream_t st) {
+int launch_tc(const TmapSet& tmap, const TcParams& p, size_t smem, int grid, cudaStream_t st) {
   auto kern = linear_wq_tc_kernel<BITS, PAIR, SPLIT>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return static_cast<int>(e);
@@ -635,25 +707,13 @@ bool tc_supported(const void* x, int x_dtype, const dimq_wq_weight* w, int64_t M
   return tiles < 0x7FFFFFFF;
 }
 
-int launch_linear_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
-                        const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K, int epilogue,
-                        int precision, cudaStream_t st) {
-  if (!tc_supported(x, x_dtype, w, M, N, K)) return DIMQ_ERR_UNSUPPORTED;
-  EncodeTiledFn encode = get_encode_tiled();
-  if (encode == nullptr) return DIMQ_ERR_DRIVER;
-  CUtensorMap tmap;
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
-  const cuuint32_t box[2] = {kBlockK, kTileX};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = encode(&tmap, x_dtype == DIMQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                            2, const_cast<void*>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return DIMQ_ERR_DRIVER;
+namespace {
 
-  TcParams p;
-  p.packed = w->packed;
+// Fills the fields shared by the GEMM and the convolution, sizes shared memory and launches.
+int finish_launch(const TmapSet& tmaps, TcParams& p, const dimq_wq_weight* w, const uint8_t* packed, int x_dtype,
+                  const void* bias, int bias_dtype, const void* residual, void* y, int y_dtype, int epilogue,
+                  int precision, cudaStream_t st) {
+  p.packed = packed;
   p.codebooks = w->codebooks;
   p.cb_dtype = w->cb_dtype;
   p.entries = w->entries;
@@ -664,9 +724,6 @@ int launch_linear_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, con
   p.residual = residual;
   p.y = y;
   p.y_dtype = y_dtype;
-  p.M = M;
-  p.N = N;
-  p.K = K;
   p.epilogue = epilogue;
   // Both MMA operands must have the same 16-bit format (a bf16 x fp16 mix is rejected by the
   // hardware as an illegal instruction).  fp16 activations: fp16 codewords.  bf16 activations:
@@ -674,14 +731,15 @@ int launch_linear_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, con
   const int w_fmt = x_dtype == DIMQ_BF16 ? 1 : 0;
   const bool split = w_fmt == 1 && precision != 1 && w->cb_dtype != DIMQ_BF16;
   p.w_fmt = w_fmt;
-  p.idesc = tc::make_idesc_f16(w_fmt, w_fmt, kTileW, kTileX);
+  p.idesc = tc::make_idesc_f16(w_fmt, w_fmt, kTileW, p.tx);
+  p.x_stage_bytes = static_cast<uint32_t>(p.tx) * kBlockK * 2;
   p.prof = nullptr;
   p.dbg = 0;
   if (const char* env = getenv("DIMQ_B200_TC_DEBUG")) p.dbg = atoi(env);
   if (const char* env = getenv("DIMQ_B200_PROFILE_PTR")) p.prof = reinterpret_cast<unsigned long long*>(strtoull(env, nullptr, 0));
-  p.m_tiles = static_cast<int>((M + kTileX - 1) / kTileX);
-  p.n_tiles = static_cast<int>((N + kTileW - 1) / kTileW);
+  p.n_tiles = static_cast<int>((p.N + kTileW - 1) / kTileW);
   const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
+  if (tiles >= 0x7FFFFFFF) return DIMQ_ERR_TOO_LARGE;
   const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
 
   const bool pair = w->bits != 8 && table_bytes(w->bits, w->groups, true, split) <= (size_t)kMaxTableBytes;
@@ -691,17 +749,17 @@ int launch_linear_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, con
                        (p.rep ? static_cast<size_t>(kNumDequantGroups) * kRepWords * 4 : 0) +
                        table_bytes(w->bits, w->groups, pair, split);
   const size_t kSmemMax = 227 * 1024;
-  int x_stages = static_cast<int>((kSmemMax - fixed) / kXStageBytes);
+  int x_stages = static_cast<int>((kSmemMax - fixed) / p.x_stage_bytes);
   if (x_stages > kXStages) x_stages = kXStages;
   if (x_stages < 3) return DIMQ_ERR_UNSUPPORTED;
   p.x_stages = x_stages;
-  const size_t smem = fixed + static_cast<size_t>(x_stages) * kXStageBytes;
-#define DIMQ_TC_CASE(B)                                                                            \
-  case B:                                                                                          \
-    if (B != 8 && pair) return split ? launch_tc<B, B != 8, true>(tmap, p, smem, grid, st)         \
-                                     : launch_tc<B, B != 8, false>(tmap, p, smem, grid, st);       \
-    return split ? launch_tc<B, false, true>(tmap, p, smem, grid, st)                              \
-                 : launch_tc<B, false, false>(tmap, p, smem, grid, st);
+  const size_t smem = fixed + static_cast<size_t>(x_stages) * p.x_stage_bytes;
+#define DIMQ_TC_CASE(B)                                                                             \
+  case B:                                                                                           \
+    if (B != 8 && pair) return split ? launch_tc<B, B != 8, true>(tmaps, p, smem, grid, st)         \
+                                     : launch_tc<B, B != 8, false>(tmaps, p, smem, grid, st);       \
+    return split ? launch_tc<B, false, true>(tmaps, p, smem, grid, st)                              \
+                 : launch_tc<B, false, false>(tmaps, p, smem, grid, st);
   switch (w->bits) {
     DIMQ_TC_CASE(2)
     DIMQ_TC_CASE(3)
@@ -710,6 +768,135 @@ int launch_linear_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, con
     default: return DIMQ_ERR_BAD_BITS;
   }
 #undef DIMQ_TC_CASE
+}
+
+}  // namespace
+
+int launch_linear_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
+                        const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K, int epilogue,
+                        int precision, cudaStream_t st) {
+  if (!tc_supported(x, x_dtype, w, M, N, K)) return DIMQ_ERR_UNSUPPORTED;
+  EncodeTiledFn encode = get_encode_tiled();
+  if (encode == nullptr) return DIMQ_ERR_DRIVER;
+  TmapSet tmaps;
+  memset(&tmaps, 0, sizeof(tmaps));
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
+  const cuuint32_t box[2] = {kBlockK, kTileX};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = encode(&tmaps.m[0], x_dtype == DIMQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                            2, const_cast<void*>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return DIMQ_ERR_DRIVER;
+  TcParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.tx = kTileX;
+  p.m_tiles = static_cast<int>((M + kTileX - 1) / kTileX);
+  return finish_launch(tmaps, p, w, w->packed, x_dtype, bias, bias_dtype, residual, y, y_dtype, epilogue, precision, st);
+}
+
+// ---- implicit-GEMM convolution ----------------------------------------------------------------
+
+bool conv_tc_supported(const void* x, int x_dtype, const dimq_wq_weight* w, const dimq_conv_geom* g, int y_dtype) {
+  if (w->packed_khwc == nullptr) return false;
+  if (x_dtype != DIMQ_BF16 && x_dtype != DIMQ_F16) return false;
+  if (y_dtype != x_dtype && y_dtype != DIMQ_F32) return false;
+  if (g->groups != 1 || g->in_channels % kBlockK != 0) return false;
+  if (g->stride_h != g->stride_w || (g->stride_h != 1 && g->stride_h != 2)) return false;
+  // channels_last storage of both tensors
+  const int64_t C = g->in_channels, W = g->in_w, H = g->in_h;
+  if (g->x_stride[1] != 1 || g->x_stride[3] != C || g->x_stride[2] != W * C || g->x_stride[0] != H * W * C) return false;
+  const int64_t OC = g->out_channels, OW = g->out_w, OH = g->out_h;
+  if (g->y_stride[1] != 1 || g->y_stride[3] != OC || g->y_stride[2] != OW * OC || g->y_stride[0] != OH * OW * OC) return false;
+  if (!aligned(x, 16) || !aligned(w->packed_khwc, 16)) return false;
+  if (table_bytes(w->bits, w->groups, false, true) > (size_t)kMaxTableBytes) return false;
+  return g->batch >= 1 && OW >= 1 && OH >= 1;
+}
+
+int launch_conv2d_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
+                        const void* residual, void* y, int y_dtype, const dimq_conv_geom* g, int epilogue,
+                        cudaStream_t st) {
+  if (!conv_tc_supported(x, x_dtype, w, g, y_dtype)) return DIMQ_ERR_UNSUPPORTED;
+  EncodeTiledFn encode = get_encode_tiled();
+  if (encode == nullptr) return DIMQ_ERR_DRIVER;
+  const int OW = g->out_w, OH = g->out_h, B = g->batch;
+  // Tile = tw x th x tb output pixels (tx = tw*th*tb, a multiple of 16 up to 192).  Prefer the shape
+  // that wastes the fewest MMA columns on positions outside the image, then the largest tile.
+  int best_tx = 0, best_tw = 0, best_th = 0, best_tb = 0;
+  double best_score = -1.0;
+  for (int tx = kTileX; tx >= 16; tx -= 16) {
+    for (int tw = 1; tw <= tx && tw <= 256; ++tw) {
+      if (tx % tw != 0 || tw > OW + 15) continue;
+      const int rest = tx / tw;
+      for (int th = 1; th <= rest && th <= 256; ++th) {
+        if (rest % th != 0 || th > OH + 15) continue;
+        const int tb = rest / th;
+        if (tb > 256) continue;
+        const double covered = static_cast<double>((OW + tw - 1) / tw) * tw * ((OH + th - 1) / th) * th *
+                               ((B + tb - 1) / tb) * tb;
+        const double useful = static_cast<double>(OW) * OH * B / covered;
+        // throughput model: a stage costs max(MMA time ~ tx, a fixed issue overhead ~ 96 columns)
+        const double score = useful * tx / (tx > 96 ? tx : 96) + 1e-4 * tw;
+        if (score > best_score) { best_score = score; best_tx = tx; best_tw = tw; best_th = th; best_tb = tb; }
+      }
+    }
+  }
+  if (best_tx == 0) return DIMQ_ERR_UNSUPPORTED;
+
+  TcParams p;
+  memset(&p, 0, sizeof(p));
+  p.conv = 1;
+  p.tx = best_tx;
+  p.tw = best_tw;
+  p.th = best_th;
+  p.tb = best_tb;
+  p.tiles_w = (OW + best_tw - 1) / best_tw;
+  p.tiles_h = (OH + best_th - 1) / best_th;
+  const int tiles_b = (B + best_tb - 1) / best_tb;
+  p.m_tiles = p.tiles_w * p.tiles_h * tiles_b;
+  p.OW = OW;
+  p.OH = OH;
+  p.Bn = B;
+  p.stride = g->stride_h;
+  p.pad_h = g->pad_h;
+  p.pad_w = g->pad_w;
+  p.dil_h = g->dilation_h;
+  p.dil_w = g->dilation_w;
+  p.KW = g->kernel_w;
+  p.c_blocks = g->in_channels / kBlockK;
+  p.M = static_cast<int64_t>(B) * OH * OW;
+  p.N = g->out_channels;
+  p.K = static_cast<int64_t>(g->kernel_h) * g->kernel_w * g->in_channels;
+
+  TmapSet tmaps;
+  memset(&tmaps, 0, sizeof(tmaps));
+  const int s = g->stride_h;
+  const int64_t C = g->in_channels, W = g->in_w, H = g->in_h;
+  const CUtensorMapDataType dt = x_dtype == DIMQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  for (int py = 0; py < s; ++py) {
+    for (int px = 0; px < s; ++px) {
+      const int64_t Wp = (W - px + s - 1) / s, Hp = (H - py + s - 1) / s;
+      CUtensorMap* m = &tmaps.m[py * s + px];
+      if (Wp <= 0 || Hp <= 0) { *m = tmaps.m[0]; continue; }   // parity without pixels: every tap there is padding
+      const cuuint64_t dims[4] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(Wp), static_cast<cuuint64_t>(Hp),
+                                  static_cast<cuuint64_t>(B)};
+      const cuuint64_t strides[3] = {static_cast<cuuint64_t>(s * C * 2), static_cast<cuuint64_t>(s * W * C * 2),
+                                     static_cast<cuuint64_t>(H * W * C * 2)};
+      const cuuint32_t box[4] = {kBlockK, static_cast<cuuint32_t>(best_tw), static_cast<cuuint32_t>(best_th),
+                                 static_cast<cuuint32_t>(best_tb)};
+      const cuuint32_t estr[4] = {1, 1, 1, 1};
+      void* base = const_cast<char*>(static_cast<const char*>(x)) + (py * W + px) * C * 2;
+      const CUresult r = encode(m, dt, 4, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (r != CUDA_SUCCESS) return DIMQ_ERR_DRIVER;
+    }
+  }
+  return finish_launch(tmaps, p, w, w->packed_khwc, x_dtype, bias, bias_dtype, residual, y, y_dtype, epilogue, 0, st);
 }
 
 int read_device_status(uint32_t* status) {

@@ -105,9 +105,8 @@ linear_wq_generic_kernel(const void* __restrict__ x, int x_dtype, dimq_wq_weight
   for (int j = 0; j < 4; ++j) {
     const int64_t m = m0 + ty + 8 * j;
     if (m < M) {
-      float v = apply_epilogue(acc[j] + b, epilogue);
-      if (residual != nullptr) v += load_as_float(residual, y_dtype, m * N + n);
-      store_from_float(y, y_dtype, m * N + n, v);
+      const float res = residual != nullptr ? load_as_float(residual, y_dtype, m * N + n) : 0.0f;
+      store_from_float(y, y_dtype, m * N + n, finish_value(acc[j] + b, epilogue, residual != nullptr, res));
     }
   }
 }
@@ -170,10 +169,34 @@ conv2d_direct_kernel(const void* __restrict__ x, int x_dtype, dimq_wq_weight w, 
   if (bias != nullptr) acc += load_as_float(bias, bias_dtype, co);
   const int64_t yo = b * g.y_stride[0] + co * g.y_stride[1] + oh * g.y_stride[2] + ow * g.y_stride[3];
   if (!A4) {
-    acc = apply_epilogue(acc, epilogue);
-    if (residual != nullptr) acc += load_as_float(residual, y_dtype, yo);
+    const float res = residual != nullptr ? load_as_float(residual, y_dtype, yo) : 0.0f;
+    acc = finish_value(acc, epilogue, residual != nullptr, res);
   }
   store_from_float(y, y_dtype, yo, acc);
+}
+
+// kcrs -> khwc re-ordering of a packed index stream: 8 output indices (= `bits` output bytes) per thread.
+__global__ void __launch_bounds__(kThreads)
+conv_prepack_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int bits, int64_t oc, int64_t icg,
+                    int64_t kh, int64_t kw) {
+  const int64_t n = oc * icg * kh * kw;
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  const int64_t base = t * 8;
+  if (base >= n) return;
+  const int64_t src_bytes = (n * bits + 7) / 8;
+  unsigned long long stream = 0ull;
+  for (int i = 0; i < 8; ++i) {
+    const int64_t o = base + i;              // position in [oc][kh][kw][ci]
+    if (o >= n) break;
+    const int64_t ci = o % icg;
+    const int64_t tap = (o / icg) % (kh * kw);
+    const int64_t co = o / (icg * kh * kw);
+    const int64_t e = (co * icg + ci) * (kh * kw) + tap;   // position in [oc][ci][kh][kw]
+    stream |= static_cast<unsigned long long>(get_index(src, e, bits, src_bytes)) << (i * bits);
+  }
+  const int64_t off = t * bits;
+  for (int b = 0; b < bits; ++b)
+    if (off + b < src_bytes) dst[off + b] = static_cast<uint8_t>(stream >> (8 * b));
 }
 
 }  // namespace
@@ -220,6 +243,20 @@ int launch_conv2d_direct(bool a4, const void* x, int x_dtype, const dimq_wq_weig
 }  // namespace dimq
 
 using namespace dimq;
+
+extern "C" int dimq_conv_prepack(const uint8_t* packed_kcrs, int bits, int64_t out_channels,
+                                 int64_t in_channels_per_group, int64_t kernel_h, int64_t kernel_w,
+                                 uint8_t* packed_khwc, void* stream) {
+  if (!(bits == 2 || bits == 3 || bits == 4 || bits == 8)) return DIMQ_ERR_BAD_BITS;
+  if (out_channels <= 0 || in_channels_per_group <= 0 || kernel_h <= 0 || kernel_w <= 0) return DIMQ_ERR_BAD_SIZE;
+  if (packed_kcrs == nullptr || packed_khwc == nullptr) return DIMQ_ERR_NULL_POINTER;
+  const int64_t n = out_channels * in_channels_per_group * kernel_h * kernel_w;
+  const int64_t blocks = ((n + 7) / 8 + kThreads - 1) / kThreads;
+  if (blocks > 0x7FFFFFFFll) return DIMQ_ERR_TOO_LARGE;
+  conv_prepack_kernel<<<(unsigned)blocks, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      packed_kcrs, packed_khwc, bits, out_channels, in_channels_per_group, kernel_h, kernel_w);
+  return launch_status();
+}
 
 extern "C" int dimq_conv_out_size(dimq_conv_geom* g) {
   if (g == nullptr) return DIMQ_ERR_NULL_POINTER;
@@ -277,6 +314,7 @@ extern "C" int dimq_conv2d_lut(const void* x, int x_dtype, const uint8_t* packed
   w.entries = 16;
   w.groups = 1;
   w.group_rows = g.out_channels;
+  w.packed_khwc = nullptr;
   return launch_conv2d_direct(true, x, x_dtype, &w, act_scale, act_zp, bias, bias_dtype, nullptr, y, DIMQ_F32, &g,
                               DIMQ_EPI_NONE, static_cast<cudaStream_t>(stream));
 }

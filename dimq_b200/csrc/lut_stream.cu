@@ -137,10 +137,9 @@ linear_wq_stream_kernel(const void* __restrict__ x, int x_dtype, dimq_wq_weight 
       if (lane == m) mine = acc[m];
     if (lane < M) {
       float v = mine + (bias != nullptr ? load_as_float(bias, bias_dtype, n) : 0.0f);
-      v = apply_epilogue(v, epilogue);
       const int64_t o = static_cast<int64_t>(lane) * N + n;
-      if (residual != nullptr) v += load_as_float(residual, y_dtype, o);
-      store_from_float(y, y_dtype, o, v);
+      const float res = residual != nullptr ? load_as_float(residual, y_dtype, o) : 0.0f;
+      store_from_float(y, y_dtype, o, finish_value(v, epilogue, residual != nullptr, res));
     }
   }
 }

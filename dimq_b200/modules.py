@@ -105,6 +105,14 @@ class DIMQConv2d(_PackedBase):
         self.padding = _pair(padding)
         self.dilation = _pair(dilation)
         self.groups = int(groups)
+        self._khwc = None  # indices re-ordered for the tensor-core conv, built on first use on the GPU
+
+    def _prepacked(self) -> torch.Tensor | None:
+        if self.groups != 1 or self.weight_shape[1] % 64 != 0:
+            return None
+        if self._khwc is None or self._khwc.device != self.packed_weight.device:
+            self._khwc = ops.conv_prepack(self.packed_weight, self.weight_shape, self.bits)
+        return self._khwc
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
         self._check_input(x)
@@ -112,7 +120,7 @@ class DIMQConv2d(_PackedBase):
             return ops.dimq_conv2d_wq(x, self.packed_weight, self.codebook, self.bias, self.weight_shape,
                                       self.stride, self.padding, self.dilation, self.groups, bits=self.bits,
                                       group_rows=self.group_rows, out_dtype=self.out_dtype, epilogue=self.epilogue,
-                                      residual=residual)
+                                      residual=residual, packed_khwc=self._prepacked())
         if residual is not None:
             raise RuntimeError("a fused residual needs the weight-only mode")
         return ops.dimq_conv2d_lut(x, self.packed_weight, self.codebook, self.act_scale, self.act_zero_point,

@@ -20,7 +20,7 @@ import torch
 from . import _lib
 from ._lib import ALGO_AUTO, ALGO_GENERIC, ALGO_STREAM, ALGO_TCGEN05, EPI_GELU, EPI_NONE, EPI_RELU  # noqa: F401
 
-_EPILOGUES = {None: EPI_NONE, "none": EPI_NONE, "relu": EPI_RELU, "gelu": EPI_GELU}
+_EPILOGUES = {None: EPI_NONE, "none": EPI_NONE, "relu": EPI_RELU, "gelu": EPI_GELU, "add_relu": _lib.EPI_ADD_RELU}
 _ALGOS = {None: ALGO_AUTO, "auto": ALGO_AUTO, "generic": ALGO_GENERIC, "stream": ALGO_STREAM,
           "tcgen05": ALGO_TCGEN05, "tcgen05_bf16w": ALGO_TCGEN05 + 100}
 
@@ -406,7 +406,7 @@ def hard_quantize(w: torch.Tensor, codebooks: torch.Tensor, *, group_rows: int |
 
 
 def _wq_weight(packed_weight: torch.Tensor, codebooks: torch.Tensor, bits: int, out_rows: int, numel: int,
-               group_rows: int | None):
+               group_rows: int | None, packed_khwc: torch.Tensor | None = None):
     _require_cuda(packed_weight, "weight-only op")
     _require_cuda(codebooks, "weight-only op")
     if packed_weight.dtype != torch.uint8:
@@ -432,8 +432,14 @@ def _wq_weight(packed_weight: torch.Tensor, codebooks: torch.Tensor, bits: int, 
         grp = int(group_rows)
         if groups * grp < out_rows:
             raise RuntimeError("not enough codebooks for the output rows")
-    w = _lib.WqWeight(pw.data_ptr(), bits, cb.data_ptr(), _lib.dtype_code(cb, "codebook"), entries, groups, grp)
-    return w, (pw, cb)
+    khwc = None
+    if packed_khwc is not None:
+        khwc = packed_khwc.contiguous().view(-1)
+        if khwc.dtype != torch.uint8 or not khwc.is_cuda or khwc.numel() < (numel * bits + 7) // 8:
+            raise RuntimeError("packed_khwc must be a CUDA uint8 tensor as large as packed_weight")
+    w = _lib.WqWeight(pw.data_ptr(), bits, cb.data_ptr(), _lib.dtype_code(cb, "codebook"), entries, groups, grp,
+                      0 if khwc is None else khwc.data_ptr())
+    return w, (pw, cb, khwc)
 
 
 def dimq_linear_wq(x: torch.Tensor, packed_weight: torch.Tensor, codebooks: torch.Tensor,
@@ -480,8 +486,14 @@ def dimq_conv2d_wq(x: torch.Tensor, packed_weight: torch.Tensor, codebooks: torc
                    bias: torch.Tensor | None, weight_shape: Sequence[int], stride=(1, 1), padding=(0, 0),
                    dilation=(1, 1), groups: int = 1, *, bits: int = 4, group_rows: int | None = None,
                    out_dtype: torch.dtype | None = None, epilogue: str | None = None,
-                   residual: torch.Tensor | None = None, algo: str | None = None) -> torch.Tensor:
-    """Weight-only LUT convolution (logical NCHW; channels_last storage is used as is)."""
+                   residual: torch.Tensor | None = None, algo: str | None = None,
+                   packed_khwc: torch.Tensor | None = None) -> torch.Tensor:
+    """Weight-only LUT convolution (logical NCHW; channels_last storage is used as is).
+
+    With ``packed_khwc`` (the indices re-ordered by :func:`conv_prepack`), channels_last bf16/fp16
+    activations, ``groups == 1``, a multiple of 64 input channels and stride 1 or 2, the convolution
+    runs as an implicit GEMM on the tensor cores; otherwise as a direct convolution.
+    """
     require_extension()
     _require_cuda(x, "conv2d_wq")
     if x.dim() != 4:
@@ -492,7 +504,7 @@ def dimq_conv2d_wq(x: torch.Tensor, packed_weight: torch.Tensor, codebooks: torc
     numel = 1
     for v in weight_shape:
         numel *= int(v)
-    w, keep = _wq_weight(packed_weight, codebooks, int(bits), g.out_channels, numel, group_rows)
+    w, keep = _wq_weight(packed_weight, codebooks, int(bits), g.out_channels, numel, group_rows, packed_khwc)
     b, b_dt = _bias_arg(bias, g.out_channels, x.device, "out_channels")
     out_dtype = out_dtype or torch.float32
     xc, y = _conv_io(x, g, out_dtype)
@@ -510,6 +522,23 @@ def dimq_conv2d_wq(x: torch.Tensor, packed_weight: torch.Tensor, codebooks: torc
     _lib.check(st, "conv2d_wq")
     del keep
     return y
+
+
+def conv_prepack(packed_weight: torch.Tensor, weight_shape: Sequence[int], bits: int = 4) -> torch.Tensor:
+    """Indices of a ``[OC, ICg, KH, KW]`` weight re-ordered to ``[OC, KH, KW, ICg]`` (same bit width)."""
+    require_extension()
+    _require_cuda(packed_weight, "conv_prepack")
+    oc, icg, kh, kw = (int(v) for v in weight_shape)
+    numel = oc * icg * kh * kw
+    src = packed_weight.contiguous().view(-1)
+    if src.dtype != torch.uint8 or src.numel() < (numel * bits + 7) // 8:
+        raise RuntimeError("packed_weight is too small for the weight shape")
+    dst = torch.empty(((numel * bits + 7) // 8,), dtype=torch.uint8, device=src.device)
+    with torch.cuda.device(src.device):
+        st = _lib.lib().dimq_conv_prepack(_lib.ptr(src), C.c_int(bits), C.c_int64(oc), C.c_int64(icg), C.c_int64(kh),
+                                          C.c_int64(kw), _lib.ptr(dst), _lib.stream_ptr(src.device))
+    _lib.check(st, "conv_prepack")
+    return dst
 
 
 def add_layer_norm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, bias: torch.Tensor,

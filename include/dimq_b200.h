@@ -57,6 +57,7 @@ extern "C" {
 #define DIMQ_EPI_NONE 0
 #define DIMQ_EPI_RELU 1
 #define DIMQ_EPI_GELU 2       /* exact (erf) GELU */
+#define DIMQ_EPI_ADD_RELU 3   /* relu(acc + bias + residual): the residual is added before the ReLU */
 
 DIMQ_API int dimq_version(void);
 DIMQ_API const char* dimq_status_string(int status);
@@ -146,6 +147,8 @@ typedef struct dimq_wq_weight {
   int32_t entries;           /* <= 2^bits */
   int64_t groups;
   int64_t group_rows;        /* output rows (channels) per codebook */
+  const uint8_t* packed_khwc; /* optional, convolution only: the same indices re-ordered to
+                                [OC][KH][KW][ICg] by dimq_conv_prepack; enables the tensor-core conv */
 } dimq_wq_weight;
 
 /* y[m][n] = sum_k x[m][k] * codebooks[n / group_rows][idx(n, k)] + bias[n], then
@@ -162,6 +165,15 @@ DIMQ_API int dimq_linear_wq(const void* x, int x_dtype, const dimq_wq_weight* w,
 DIMQ_API int dimq_conv2d_wq(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
                    const void* residual, void* y, int y_dtype, const dimq_conv_geom* geom, int epilogue,
                    int algo, void* stream);
+
+/* Re-orders the `bits`-wide index stream of a [OC][ICg][KH][KW] convolution weight (the reference's
+ * "conv_kcrs" layout, dimq_backend/export.py:232) to [OC][KH][KW][ICg], so that 64 consecutive
+ * indices of a row are 64 input channels of one filter tap — the k order of the implicit-GEMM
+ * convolution over NHWC activations.  `dst` holds (OC*ICg*KH*KW*bits + 7) / 8 bytes and is scratch
+ * the caller owns (typically built once per layer and cached).  No counterpart in the reference
+ * (its direct convolution reads the kcrs stream in place). */
+DIMQ_API int dimq_conv_prepack(const uint8_t* packed_kcrs, int bits, int64_t out_channels, int64_t in_channels_per_group,
+                               int64_t kernel_h, int64_t kernel_w, uint8_t* packed_khwc, void* stream);
 
 /* ---- dense helper of the whole-model harness --------------------------- */
 
