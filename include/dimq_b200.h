@@ -41,6 +41,7 @@ extern "C" {
 #define DIMQ_ERR_DRIVER (-9)        /* a driver entry point (tensor-map encode) is unavailable or failed */
 #define DIMQ_ERR_DEVICE_TIMEOUT (-10) /* a bounded wait inside a kernel expired (see dimq_last_device_status) */
 #define DIMQ_ERR_TOO_LARGE (-11)
+#define DIMQ_ERR_SCRATCH_TOO_SMALL (-12) /* the weight does not fit the built-in scratch of dimq_conv2d_wq_static */
 
 /* element types of floating tensors */
 #define DIMQ_F32 0
@@ -174,6 +175,20 @@ DIMQ_API int dimq_conv2d_wq(const void* x, int x_dtype, const dimq_wq_weight* w,
  * (its direct convolution reads the kcrs stream in place). */
 DIMQ_API int dimq_conv_prepack(const uint8_t* packed_kcrs, int bits, int64_t out_channels, int64_t in_channels_per_group,
                                int64_t kernel_h, int64_t kernel_w, uint8_t* packed_khwc, void* stream);
+
+/* The tensor-core path of dimq_conv2d_wq for callers that cannot allocate device memory (a plug-in
+ * inside a runtime that owns the whole device pool, a process under a fixed memory budget): it takes
+ * the canonical packed stream (w->packed; w->packed_khwc is ignored) and keeps the re-ordered indices
+ * in a 4 MiB array built into the library, so nothing is allocated by either side.  Limits: the index
+ * stream (OC*ICg*KH*KW*bits/8 bytes) must fit 4 MiB (else DIMQ_ERR_SCRATCH_TOO_SMALL); the geometry
+ * must be one the tensor-core convolution takes (else DIMQ_ERR_UNSUPPORTED: use dimq_conv2d_wq, which
+ * then needs no scratch); the array is shared by all calls on a GPU, so calls that may overlap on the
+ * device race — keep them on one stream.  The first call on a device resolves the array's address;
+ * make it before any stream capture.  Every GPU the library runs on holds the 4 MiB until exit.
+ * This entry point has no counterpart in the reference. */
+DIMQ_API int dimq_conv2d_wq_static(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias,
+                                   int bias_dtype, const void* residual, void* y, int y_dtype,
+                                   const dimq_conv_geom* geom, int epilogue, void* stream);
 
 /* ---- dense helper of the whole-model harness --------------------------- */
 
