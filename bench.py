@@ -32,8 +32,13 @@ ROOT = Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-BATCH_PER_GPU = 128
-WORKLOAD = "vit_b16_w3_g128_batch128_per_gpu"
+# name -> (config.workload, images per GPU and step, weight description)
+WORKLOADS = {
+    "vit_b16": ("vit_b16_w3_g128_batch128_per_gpu", 128,
+                "3-bit indices, 8-entry bf16 codebook per 128 output rows, random init"),
+    "resnet18": ("resnet18_w4_stem_fc_w8_batch256_per_gpu", 256,
+                 "BN folded; 4-bit per-layer bf16 codebooks, 8-bit for the stem conv and the classifier, random init"),
+}
 FALLBACK_TFLOPS = 1590.0
 CPU_SAMPLE_IMAGES = 8
 
@@ -108,12 +113,15 @@ def run_reference(args) -> None:
         return
     import torch
 
-    from oracle.models_oracle import ViTOracle, build_vit_b16_checkpoint_cpu
+    from oracle import models_oracle as mo
 
+    WORKLOAD, BATCH_PER_GPU, _ = WORKLOADS[args.workload]
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    ckpt = build_vit_b16_checkpoint_cpu(seed=0)
-    model = ViTOracle(ckpt)
+    if args.workload == "vit_b16":
+        model = mo.ViTOracle(mo.build_vit_b16_checkpoint_cpu(seed=0))
+    else:
+        model = mo.ResNet18Oracle(mo.build_resnet18_checkpoint_cpu(seed=0))
     images = torch.randn(CPU_SAMPLE_IMAGES, 3, 224, 224, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16)
     for _ in range(max(1, min(args.warmup, 2))):
         model.forward(images)
@@ -124,7 +132,7 @@ def run_reference(args) -> None:
     value = CPU_SAMPLE_IMAGES * args.steps / dt
     sample = f"{CPU_SAMPLE_IMAGES} images per step (of the {BATCH_PER_GPU}-image batch), fp32, {cores} threads"
     print(json.dumps({
-        "impl": "reference", "metric": "vit_b16_dimq_images_per_s", "value": value, "unit": "images/s",
+        "impl": "reference", "metric": f"{args.workload}_dimq_images_per_s", "value": value, "unit": "images/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "sample": sample},
@@ -133,18 +141,18 @@ def run_reference(args) -> None:
     }), flush=True)
 
 
-def cpu_baseline(ckpt) -> dict:
+def cpu_baseline(ckpt, workload: str) -> dict:
     import torch
 
-    from oracle.models_oracle import ViTOracle
+    from oracle.models_oracle import ResNet18Oracle, ViTOracle
 
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    cpu_ckpt = {"config": ckpt["config"],
+    cpu_ckpt = {"config": ckpt.get("config"),
                 "layers": {k: {kk: (vv.cpu() if hasattr(vv, "cpu") else vv) for kk, vv in v.items()}
                            for k, v in ckpt["layers"].items()},
                 "non_quantized_state_dict": {k: v.cpu() for k, v in ckpt["non_quantized_state_dict"].items()}}
-    model = ViTOracle(cpu_ckpt)
+    model = ViTOracle(cpu_ckpt) if workload == "vit_b16" else ResNet18Oracle(cpu_ckpt)
     images = torch.randn(CPU_SAMPLE_IMAGES, 3, 224, 224, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16)
     model.forward(images)
     passes, t0 = 0, time.perf_counter()
@@ -165,6 +173,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="vit_b16", choices=["vit_b16", "resnet18"],
+                    help="vit_b16 is the headline line; resnet18 prints the same line for the ResNet-18 config")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -177,7 +187,7 @@ def main() -> None:
 
     from dimq_b200 import _lib, ops
     from dimq_b200.dist import gather_logits
-    from dimq_b200.workloads import DIMQViT, build_vit_b16_checkpoint
+    from dimq_b200.workloads import DIMQResNet18, DIMQViT, build_resnet18_checkpoint, build_vit_b16_checkpoint
 
     ops.require_extension()  # no CPU fallback: fail loudly when the CUDA library is missing
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -190,11 +200,17 @@ def main() -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    B = BATCH_PER_GPU
+    WORKLOAD, B, weight_desc = WORKLOADS[args.workload]
     with torch.no_grad():
-        ckpt = build_vit_b16_checkpoint(seed=0, device=dev)
-        model = DIMQViT(ckpt).to(dev).eval()
-        n_bufs = 4  # 4 x 38.5 MB of images: more than the 126 MB L2, rotated every step
+        if args.workload == "vit_b16":
+            ckpt = build_vit_b16_checkpoint(seed=0, device=dev)
+            model = DIMQViT(ckpt).to(dev).eval()
+            flops_per_step = model.lut_gemm_flops(B)
+        else:
+            ckpt = build_resnet18_checkpoint(seed=0, device=dev)
+            model = DIMQResNet18(ckpt).to(dev).eval()
+            flops_per_step = model.lut_flops(B)
+        n_bufs = 4  # rotating image buffers (4 x 38.5 MB or more): larger than the 126 MB L2
         gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
         host_images = [torch.randn(B, 3, 224, 224, generator=gen).to(torch.bfloat16).pin_memory() for _ in range(n_bufs)]
         dev_images = [h.to(dev, non_blocking=True) for h in host_images]
@@ -235,7 +251,7 @@ def main() -> None:
                 gather_logits(outs[n_bufs])
             host_logits.copy_(outs[n_bufs], non_blocking=True)
 
-        def timed(step_fn) -> float:
+        def run_timed(step_fn) -> float:
             with torch.cuda.stream(stream):
                 for i in range(args.warmup):
                     step_fn(i)
@@ -255,26 +271,29 @@ def main() -> None:
         sampler = ClockSampler(local_rank)
         if rank == 0:
             sampler.start()
-        ms_resident = timed(step_resident)
+        ms_resident = run_timed(step_resident)
         clocks = sampler.stop() if rank == 0 else None
-        ms_e2e = timed(step_e2e)
+        ms_e2e = run_timed(step_e2e)
 
         # ---- roofline of the dominant kernel: eager pass with events around every LUT-GEMM launch ----
         events = []
-        orig = ops.dimq_linear_wq
+        orig, orig_conv = ops.dimq_linear_wq, ops.dimq_conv2d_wq
 
-        def timed_linear(*a, **kw):
-            s = torch.cuda.Event(enable_timing=True)
-            e = torch.cuda.Event(enable_timing=True)
-            s.record(torch.cuda.current_stream())
-            y = orig(*a, **kw)
-            e.record(torch.cuda.current_stream())
-            events.append((s, e))
-            return y
+        def timed(fn):
+            def wrapper(*a, **kw):
+                s = torch.cuda.Event(enable_timing=True)
+                e = torch.cuda.Event(enable_timing=True)
+                s.record(torch.cuda.current_stream())
+                y = fn(*a, **kw)
+                e.record(torch.cuda.current_stream())
+                events.append((s, e))
+                return y
+            return wrapper
 
         roof_steps = 3
         from dimq_b200 import modules as _modules
-        _modules.ops.dimq_linear_wq = timed_linear
+        _modules.ops.dimq_linear_wq = timed(orig)
+        _modules.ops.dimq_conv2d_wq = timed(orig_conv)
         try:
             with torch.cuda.stream(stream):
                 for i in range(roof_steps):
@@ -285,6 +304,7 @@ def main() -> None:
                 stream.synchronize()
         finally:
             _modules.ops.dimq_linear_wq = orig
+            _modules.ops.dimq_conv2d_wq = orig_conv
         gemm_ms = sum(s.elapsed_time(e) for s, e in events)
         gemm_launches = len(events)
 
@@ -299,27 +319,26 @@ def main() -> None:
     value = images_total / (ms_resident / 1e3)
     e2e_value = images_total / (ms_e2e / 1e3)
     peak, peak_kind = _peaks()
-    flops = model.lut_gemm_flops(B) * roof_steps
+    flops = flops_per_step * roof_steps
     achieved = flops / (gemm_ms / 1e3) / 1e12
     line = {
-        "metric": "vit_b16_dimq_images_per_s", "value": value, "unit": "images/s", "n_gpus": world,
+        "metric": f"{args.workload}_dimq_images_per_s", "value": value, "unit": "images/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_resident / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "global_batch": world * B, "tokens_per_image": 197,
-                   "weights": "3-bit indices, 8-entry bf16 codebook per 128 output rows, random init",
-                   "l2": f"{n_bufs} rotating image buffers (154 MB) and >126 MB of activations per step",
+        "config": {"workload": WORKLOAD, "global_batch": world * B, "weights": weight_desc,
+                   "l2": f"{n_bufs} rotating image buffers and >126 MB of activations per step",
                    "parallelism": f"dp{world} (batch-sharded replicas, all-gather of logits)"},
         "e2e": {"value": e2e_value, "unit": "images/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": world * B * 3 * 224 * 224 * 2, "d2h_bytes_per_step": world * B * 1000 * 4},
         "gpu_launches": launches_per_forward * args.steps,
         "clocks": clocks,
-        "roofline": {"kernel": "linear_wq_tc_kernel (tcgen05 LUT GEMM)", "bound": "tensor", "achieved": achieved,
+        "roofline": {"kernel": "linear_wq_tc_kernel (tcgen05 LUT GEMM / implicit-GEMM conv)", "bound": "tensor", "achieved": achieved,
                      "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peak_kind,
                      "launches_timed": gemm_launches, "avg_launch_ms": gemm_ms / max(gemm_launches, 1),
                      "flops_per_step": flops / roof_steps, "traffic": None},
     }
     if world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline(ckpt)
+        line["cpu_baseline"] = cpu_baseline(ckpt, args.workload)
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

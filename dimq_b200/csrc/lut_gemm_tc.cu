@@ -40,10 +40,10 @@ constexpr int kAccCol = 0;                         // accumulators: columns [0, 
 constexpr int kWCol = kAccStages * kTileX;         // weight stages: 32 columns each
 static_assert(kWCol + kWStages * (kBlockK / 2) <= kTmemCols, "TMEM layout");
 constexpr int kXStageBytes = kTileX * kBlockK * 2;  // 24 KB
-constexpr int kNumDequantGroups = 3;   // each group of 4 warps (one per TMEM lane quarter) takes every 3rd stage
+constexpr int kNumDequantGroups = 2;   // each group of 4 warps (one per TMEM lane quarter) takes every 2nd stage
 constexpr int kNumDequantWarps = 4 * kNumDequantGroups;
 constexpr int kRepWords = 2048;          // replicated lookup table of one dequantisation group (8 KB)
-constexpr int kNumEpilogueWarps = 4;
+constexpr int kNumEpilogueWarps = 8;   // two per TMEM lane quarter, alternating 32-column chunks
 constexpr int kThreads = (2 + kNumEpilogueWarps + kNumDequantWarps) * 32;
 constexpr int kMaxTableBytes = 40 * 1024;
 
@@ -178,21 +178,28 @@ __device__ __forceinline__ void store_chunk_t(const uint32_t (&r)[32], void* y, 
 // (b0 + bb, oh0 + hh, ow0 + ww) with ww fastest; y and the residual are NHWC.
 template <typename T>
 __device__ __forceinline__ void store_chunk_conv(const uint32_t (&r)[32], const TcParams& p, int p0, int m_blk,
-                                                 int64_t n, float bias) {
-  const int ow0 = (m_blk % p.tiles_w) * p.tw;
-  const int oh0 = ((m_blk / p.tiles_w) % p.tiles_h) * p.th;
-  const int b0 = (m_blk / (p.tiles_w * p.tiles_h)) * p.tb;
-  int ww = p0 % p.tw, hh = (p0 / p.tw) % p.th, bb = p0 / (p.tw * p.th);
+                                                 int64_t n, bool n_ok, float bias) {
+  // lane j works out where pixel (p0 + j) of the tile lives (or that it is outside the image); the
+  // offsets are then handed round with shuffles instead of being recomputed by every lane
+  const int lane = threadIdx.x & 31;
+  const int pj = p0 + lane;
+  const int ww = pj % p.tw, hh = (pj / p.tw) % p.th, bb = pj / (p.tw * p.th);
+  const int ow = (m_blk % p.tiles_w) * p.tw + ww;
+  const int oh = ((m_blk / p.tiles_w) % p.tiles_h) * p.th + hh;
+  const int ob = (m_blk / (p.tiles_w * p.tiles_h)) * p.tb + bb;
+  long long mine = -1;
+  if (pj < p.tx && ob < p.Bn && oh < p.OH && ow < p.OW)
+    mine = ((static_cast<long long>(ob) * p.OH + oh) * p.OW + ow) * p.N;
   T* y = static_cast<T*>(p.y);
   const T* res = static_cast<const T*>(p.residual);
 #pragma unroll
   for (int j = 0; j < 32; ++j) {
-    if (p0 + j < p.tx && b0 + bb < p.Bn && oh0 + hh < p.OH && ow0 + ww < p.OW) {
-      const int64_t off = ((static_cast<int64_t>(b0 + bb) * p.OH + (oh0 + hh)) * p.OW + (ow0 + ww)) * p.N + n;
+    const long long base = __shfl_sync(0xFFFFFFFFu, mine, j);
+    if (base >= 0 && n_ok) {
+      const long long off = base + n;
       const float v = __uint_as_float(r[j]) + bias;
       y[off] = from_float<T>(res != nullptr ? finish<T, true>(v, p.epilogue, res + off) : finish<T, false>(v, p.epilogue, nullptr));
     }
-    if (++ww == p.tw) { ww = 0; if (++hh == p.th) { hh = 0; ++bb; } }
   }
 }
 
@@ -438,6 +445,7 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
   } else if (warp < 2 + kNumEpilogueWarps) {
     // ===================== epilogue =====================
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32)
+    const int sub = (warp - 2) >> 2;  // which of the two warps of this quarter: chunks sub, sub + 2, ...
     uint32_t as = 0, aph = 0;
     bool ok = true;
     unsigned long long w_df = 0;
@@ -456,12 +464,17 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
 #pragma unroll 1
       if (p.dbg & 1) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(smem_u32(&hdr->d_empty[as])); }
       else
-      for (int c = 0; c < n_chunks; ++c) {
+      if (sub >= n_chunks) {   // fewer chunks than warps: nothing to read, release at once
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&hdr->d_empty[as]));
+      }
+      for (int c = sub; c < n_chunks; c += 2) {
         uint32_t r[32];
         __syncwarp();
         tmem_ld32(d_tmem + c * 32, r);
         tmem_ld_wait();
-        if (c == n_chunks - 1) {
+        if (c + 2 >= n_chunks) {
           // every column of this buffer is in registers: hand it back to the MMA warp
           tc_fence_before();
           __syncwarp();
@@ -477,10 +490,10 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
             else if (p.y_dtype == DIMQ_F16) store_chunk_t<__half>(r, p.y, p.residual, off, p.N, rows, bias, p.epilogue);
             else store_chunk_t<float>(r, p.y, p.residual, off, p.N, rows, bias, p.epilogue);
           }
-        } else if (n_ok) {
-          if (p.y_dtype == DIMQ_BF16) store_chunk_conv<__nv_bfloat16>(r, p, c * 32, m_blk, n, bias);
-          else if (p.y_dtype == DIMQ_F16) store_chunk_conv<__half>(r, p, c * 32, m_blk, n, bias);
-          else store_chunk_conv<float>(r, p, c * 32, m_blk, n, bias);
+        } else {
+          if (p.y_dtype == DIMQ_BF16) store_chunk_conv<__nv_bfloat16>(r, p, c * 32, m_blk, n, n_ok, bias);
+          else if (p.y_dtype == DIMQ_F16) store_chunk_conv<__half>(r, p, c * 32, m_blk, n, n_ok, bias);
+          else store_chunk_conv<float>(r, p, c * 32, m_blk, n, n_ok, bias);
         }
       }
       if (++as == kAccStages) { as = 0; aph ^= 1u; }
@@ -488,15 +501,15 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
     if (p.prof && warp == 2 && lane == 0) { p.prof[blockIdx.x * 16 + 6] = w_df; p.prof[blockIdx.x * 16 + 7] = clock64() - t_begin; }
   } else {
     // ===================== dequantisation =====================
-    // 12 warps in 3 groups of 4 (one warp per TMEM lane quarter).  Group g dequantises stages
-    // g, g + 3, g + 6, ... completely (64 k of 128 weight rows: thread = weight row), so a warp has
-    // three stage periods for one stage's latency chain.
+    // 8 warps in 2 groups of 4 (one warp per TMEM lane quarter).  Group g dequantises stages
+    // g, g + 2, g + 4, ... completely (64 k of 128 weight rows: thread = weight row), so a warp has
+    // two stage periods for one stage's latency chain.
     // A group may run at most one mbarrier phase ahead of the MMA warp, which holds when the number
     // of active groups does not exceed the number of weight stages (2 in split mode): the third
     // group idles there.
     constexpr int kGroups = SPLIT ? 2 : kNumDequantGroups;
     static_assert(kGroups <= (SPLIT ? kWStages / 2 : kWStages), "dequant groups vs weight stages");
-    const int dw = warp - (2 + kNumEpilogueWarps);  // 0..11
+    const int dw = warp - (2 + kNumEpilogueWarps);  // 0..7
     const int grp = dw >> 2;
     const int quarter = warp & 3;                   // TMEM lane quarter this warp may write
     const int row_in_tile = quarter * 32 + lane;

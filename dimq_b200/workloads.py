@@ -190,3 +190,150 @@ class DIMQViT(nn.Module):
             m = batch if name == "head" else batch * t
             total += 2.0 * m * mod.out_features * mod.in_features
         return total
+
+
+# ---------------------------------------------------------------------------------------------
+# ResNet-18 (BN folded), every Conv2d / Linear quantised: 4-bit per-layer codebooks, except the
+# first conv and the classifier at 8 bits
+# ---------------------------------------------------------------------------------------------
+
+RESNET18_STAGES = ((64, 1), (128, 2), (256, 2), (512, 2))   # (channels, stride of the first block)
+
+
+def quantize_conv(weight: torch.Tensor, bias: torch.Tensor, bits: int, codebook_dtype: torch.dtype, name: str,
+                  stride: int, padding: int) -> dict[str, Any]:
+    """Float conv weight ``[OC, C, KH, KW]`` on a CUDA device -> packed layer entry (per-layer codebook)."""
+    oc = weight.shape[0]
+    books = quantile_codebooks(weight.reshape(oc, -1), 1 << bits, oc).to(codebook_dtype)
+    _, packed = ops.hard_quantize(weight.float().contiguous(), books.float().reshape(-1), bits=bits,
+                                  return_indices=False)
+    return {"name": name, "type": "conv2d", "bit_w": bits, "weight_shape": list(weight.shape),
+            "weight_numel": weight.numel(), "packed_weight": packed, "codebook": books.reshape(-1),
+            "codebook_granularity": "per_layer", "act_scale": None, "act_zero_point": None, "bias": bias,
+            "layout": "conv_kcrs", "out_channels": oc, "in_channels_per_group": weight.shape[1],
+            "kernel_size": list(weight.shape[2:]), "stride": [stride, stride], "padding": [padding, padding],
+            "dilation": [1, 1], "groups": 1}
+
+
+@torch.no_grad()
+def build_resnet18_checkpoint(*, seed: int = 0, device="cuda", codebook_dtype: torch.dtype = torch.bfloat16,
+                              dtype: torch.dtype = torch.bfloat16, classes: int = 1000) -> dict[str, Any]:
+    """Random-init ResNet-18 with BatchNorm already folded into conv weight and bias (Kaiming-normal
+    weights times a random per-channel BN scale, random folded bias), quantised layer by layer."""
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    dev = torch.device(device)
+    layers: dict[str, dict[str, Any]] = {}
+
+    def conv(name, oc, ic, k, stride, bits=4):
+        w = torch.randn(oc, ic, k, k, generator=gen) * (2.0 / (ic * k * k)) ** 0.5
+        scale = 0.5 + torch.rand(oc, generator=gen)          # folded BN gamma / sqrt(var + eps)
+        bias = (torch.randn(oc, generator=gen) * 0.1).to(dev).to(dtype)
+        layers[name] = quantize_conv((w * scale.view(-1, 1, 1, 1)).to(dev), bias, bits, codebook_dtype, name, stride,
+                                     k // 2)
+
+    conv("conv1", 64, 3, 7, 2, bits=8)
+    in_ch = 64
+    for si, (ch, stride) in enumerate(RESNET18_STAGES, start=1):
+        for bi in range(2):
+            s = stride if bi == 0 else 1
+            conv(f"layer{si}.{bi}.conv1", ch, in_ch, 3, s)
+            conv(f"layer{si}.{bi}.conv2", ch, ch, 3, 1)
+            if s != 1 or in_ch != ch:
+                conv(f"layer{si}.{bi}.downsample", ch, in_ch, 1, s)
+            in_ch = ch
+    fc_w = (torch.randn(classes, 512, generator=gen) * 0.02).to(dev)
+    fc_b = (torch.randn(classes, generator=gen) * 0.02).to(dev).to(dtype)
+    layers["fc"] = quantize_linear(fc_w, fc_b, 8, None, codebook_dtype, "fc")
+    return {"format": "dimq_packed_lut", "format_version": 2, "model_name": "resnet18_synthetic",
+            "weight_encoding": "packed_bitstream_indices", "activation_quantization": "none", "layers": layers,
+            "non_quantized_state_dict": {}}
+
+
+class DIMQResNet18(nn.Module):
+    """ResNet-18 forward over packed DIMQ layers, channels_last bf16 activations.
+
+    3x3 / 1x1 convolutions with a multiple of 64 input channels run as tensor-core implicit GEMMs with
+    bias + ReLU (+ residual) in the epilogue.  The 7x7 stem (3 input channels) is lowered to a GEMM
+    over an explicit im2col matrix (K = 147 padded to 192) and runs through the LUT GEMM; max-pool and
+    the global average pool are PyTorch ops.
+    """
+
+    def __init__(self, checkpoint: dict[str, Any], *, act_dtype: torch.dtype = torch.bfloat16,
+                 fuse_residual: bool = True) -> None:
+        super().__init__()
+        from .modules import DIMQConv2d
+
+        self.act_dtype = act_dtype
+        self.fuse_residual = bool(fuse_residual)
+        self.convs = nn.ModuleDict()
+        for name, layer in checkpoint["layers"].items():
+            if name in ("conv1", "fc"):
+                continue
+            self.convs[name.replace(".", "__")] = DIMQConv2d.from_export_layer(layer, out_dtype=act_dtype)
+        fc = checkpoint["layers"]["fc"]
+        self.fc = DIMQLinear.from_export_layer(fc, out_dtype=torch.float32)
+        # stem: indices re-ordered to (kh, kw, c) and padded from K = 147 to 192 columns
+        stem = checkpoint["layers"]["conv1"]
+        oc, ic, kh, kw = stem["weight_shape"]
+        khwc = ops.conv_prepack(stem["packed_weight"], stem["weight_shape"], 8)
+        idx = ops.unpack_bits(khwc, oc * ic * kh * kw, 8).view(oc, kh * kw * ic)
+        self.stem_k = kh * kw * ic
+        self.stem_kp = (self.stem_k + 63) // 64 * 64
+        padded = torch.zeros(oc, self.stem_kp, dtype=torch.uint8, device=idx.device)
+        padded[:, : self.stem_k] = idx
+        self.stem = DIMQLinear(ops.pack_bits(padded, 8), stem["codebook"], None, None, oc, self.stem_kp, stem["bias"],
+                               bits=8, out_dtype=act_dtype, epilogue="relu")
+
+    def _conv(self, name: str):
+        return self.convs[name.replace(".", "__")]
+
+    def _stem(self, images: torch.Tensor) -> torch.Tensor:
+        b, _, h, w = images.shape
+        x = F.pad(images.to(self.act_dtype).permute(0, 2, 3, 1), (0, 0, 3, 3, 3, 3))   # NHWC, padded by 3
+        hp, wp = h + 6, w + 6
+        oh, ow = (h + 6 - 7) // 2 + 1, (w + 6 - 7) // 2 + 1
+        x = x.contiguous()
+        # window (oh, ow) = 7 rows of 21 contiguous elements (7 pixels x 3 channels)
+        win = x.as_strided((b, oh, ow, 7, 21), (hp * wp * 3, 2 * wp * 3, 6, wp * 3, 1))
+        cols = torch.zeros(b * oh * ow, self.stem_kp, dtype=self.act_dtype, device=x.device)
+        cols.view(b, oh, ow, self.stem_kp)[..., : self.stem_k] = win.reshape(b, oh, ow, self.stem_k)
+        y = self.stem(cols)                                                              # [B*OH*OW, 64], ReLU fused
+        return y.view(b, oh, ow, -1).permute(0, 3, 1, 2)                                 # logical NCHW, NHWC storage
+
+    def forward(self, images: torch.Tensor) -> torch.Tensor:
+        x = self._stem(images)
+        x = F.max_pool2d(x, 3, 2, 1)
+        in_ch = 64
+        for si, (ch, stride) in enumerate(RESNET18_STAGES, start=1):
+            for bi in range(2):
+                s = stride if bi == 0 else 1
+                pre = f"layer{si}.{bi}."
+                identity = x
+                if s != 1 or in_ch != ch:
+                    identity = self._conv(pre + "downsample")(x)
+                c1 = self._conv(pre + "conv1")
+                c1.epilogue = "relu"
+                y = c1(x)
+                c2 = self._conv(pre + "conv2")
+                if self.fuse_residual:
+                    c2.epilogue = "add_relu"
+                    x = c2(y, residual=identity)
+                else:
+                    c2.epilogue = None
+                    x = torch.relu_(c2(y) + identity)
+                in_ch = ch
+        pooled = x.mean(dim=(2, 3)).to(self.act_dtype)
+        return self.fc(pooled.contiguous())
+
+    def lut_flops(self, batch: int, image: int = 224) -> float:
+        """Algorithmic flops (2 * outputs * K) of every quantised layer for one forward."""
+        total = 0.0
+        size = (image + 6 - 7) // 2 + 1
+        total += 2.0 * batch * size * size * 64 * self.stem_k
+        size = (size + 2 - 3) // 2 + 1
+        for name, mod in self.convs.items():
+            oc, ic, kh, kw = mod.weight_shape
+            if name.endswith("__0__conv1") and mod.stride[0] == 2:
+                size = (size + 2 - 3) // 2 + 1
+            total += 2.0 * batch * size * size * oc * ic * kh * kw
+        return total + 2.0 * batch * self.fc.out_features * self.fc.in_features

@@ -112,3 +112,81 @@ def build_vit_b16_checkpoint_cpu(*, seed: int = 0, bits: int = 3, group_rows: in
     qlayers["head"] = qlayer("head", cfg["classes"], hid)
     return {"format": "dimq_packed_lut", "format_version": 2, "config": cfg, "layers": qlayers,
             "non_quantized_state_dict": dense}
+
+
+class ResNet18Oracle:
+    """fp32 CPU ResNet-18 (BN folded) over the dequantised weights: ``F.conv2d`` + bias + ReLU, the
+    computation of the reference's wrapper forward (quant/dimq_wrapper.py:189-197) layer by layer.
+    ``round_dtype`` rounds activations where the GPU path stores them."""
+
+    STAGES = ((64, 1), (128, 2), (256, 2), (512, 2))
+
+    def __init__(self, checkpoint: dict, round_dtype: torch.dtype | None = None) -> None:
+        self.round_dtype = round_dtype
+        self.w, self.b, self.meta = {}, {}, {}
+        for name, layer in checkpoint["layers"].items():
+            self.w[name] = dequantize_layer(layer)
+            self.b[name] = layer["bias"].float().cpu()
+            self.meta[name] = layer
+
+    def _r(self, x):
+        return x if self.round_dtype is None else x.to(self.round_dtype).float()
+
+    def _conv(self, name, x):
+        m = self.meta[name]
+        return F.conv2d(x, self.w[name], self.b[name], tuple(m["stride"]), tuple(m["padding"]))
+
+    @torch.no_grad()
+    def forward(self, images: torch.Tensor) -> torch.Tensor:
+        x = self._r(torch.relu(self._conv("conv1", self._r(images.float().cpu()))))
+        x = F.max_pool2d(x, 3, 2, 1)
+        in_ch = 64
+        for si, (ch, stride) in enumerate(self.STAGES, start=1):
+            for bi in range(2):
+                s = stride if bi == 0 else 1
+                pre = f"layer{si}.{bi}."
+                identity = x
+                if s != 1 or in_ch != ch:
+                    identity = self._r(self._conv(pre + "downsample", x))
+                y = self._r(torch.relu(self._conv(pre + "conv1", x)))
+                x = self._r(torch.relu(self._conv(pre + "conv2", y) + identity))
+                in_ch = ch
+        pooled = self._r(x.mean(dim=(2, 3)))
+        return F.linear(pooled, self.w["fc"], self.b["fc"])
+
+
+def build_resnet18_checkpoint_cpu(*, seed: int = 0, classes: int = 1000) -> dict:
+    """Synthetic packed ResNet-18 (BN folded) made on the CPU with the oracle's own functions:
+    4-bit per-layer quantile codebooks, 8 bits for the stem and the classifier."""
+    from . import c_oracle
+
+    rng = np.random.default_rng(seed)
+    layers = {}
+
+    def quant(name, w, bits, extra):
+        flat = w.reshape(w.shape[0], -1)
+        book = o.quantile_codebook(flat, 1 << bits)
+        idx = c_oracle.hard_quantize(flat, book)
+        layers[name] = {"name": name, "bit_w": bits, "weight_shape": list(w.shape),
+                        "packed_weight": torch.from_numpy(c_oracle.pack_bits(idx, bits)),
+                        "codebook": torch.from_numpy(book), "group_rows": w.shape[0],
+                        "bias": torch.from_numpy((rng.standard_normal(w.shape[0]) * 0.1).astype(np.float32)), **extra}
+
+    def conv(name, oc, ic, k, stride, bits=4):
+        w = (rng.standard_normal((oc, ic, k, k)) * (2.0 / (ic * k * k)) ** 0.5).astype(np.float32)
+        w *= (0.5 + rng.random(oc)).astype(np.float32).reshape(-1, 1, 1, 1)
+        quant(name, w, bits, {"type": "conv2d", "stride": [stride, stride], "padding": [k // 2, k // 2]})
+
+    conv("conv1", 64, 3, 7, 2, bits=8)
+    in_ch = 64
+    for si, (ch, stride) in enumerate(ResNet18Oracle.STAGES, start=1):
+        for bi in range(2):
+            s = stride if bi == 0 else 1
+            conv(f"layer{si}.{bi}.conv1", ch, in_ch, 3, s)
+            conv(f"layer{si}.{bi}.conv2", ch, ch, 3, 1)
+            if s != 1 or in_ch != ch:
+                conv(f"layer{si}.{bi}.downsample", ch, in_ch, 1, s)
+            in_ch = ch
+    quant("fc", (rng.standard_normal((classes, 512)) * 0.02).astype(np.float32), 8,
+          {"type": "linear", "out_features": classes, "in_features": 512})
+    return {"format": "dimq_packed_lut", "format_version": 2, "layers": layers, "non_quantized_state_dict": {}}

@@ -115,3 +115,33 @@ def test_add_layer_norm_matches_torch(cuda_device, dtype):
     assert (h3.float() - want_h3).abs().max().item() <= (4e-2 if dtype == torch.bfloat16 else 6e-3)
     with pytest.raises(RuntimeError):
         ops.add_layer_norm(x[..., :100].contiguous(), None, w[:100], b[:100])
+
+
+def _cpu_ckpt(ckpt):
+    return {"config": ckpt.get("config"),
+            "layers": {k: {kk: (vv.cpu() if hasattr(vv, "cpu") else vv) for kk, vv in v.items()}
+                       for k, v in ckpt["layers"].items()},
+            "non_quantized_state_dict": {k: v.cpu() for k, v in ckpt["non_quantized_state_dict"].items()}}
+
+
+@pytest.mark.parametrize("fuse", [True, False])
+def test_resnet18_forward_matches_cpu_oracle(cuda_device, fuse):
+    from dimq_b200.workloads import DIMQResNet18, build_resnet18_checkpoint
+    from oracle.models_oracle import ResNet18Oracle
+
+    ckpt = build_resnet18_checkpoint(seed=2, device=cuda_device)
+    model = DIMQResNet18(ckpt, fuse_residual=fuse).to(cuda_device).eval()
+    images = torch.randn(4, 3, 224, 224, generator=torch.Generator().manual_seed(9)).to(torch.bfloat16)
+    with torch.no_grad():
+        got = model(images.cuda()).float().cpu().numpy()
+    cpu = _cpu_ckpt(ckpt)
+    want_bf16 = ResNet18Oracle(cpu, round_dtype=torch.bfloat16).forward(images).numpy()
+    want_fp32 = ResNet18Oracle(cpu).forward(images).numpy()
+    assert got.shape == (4, 1000)
+    from dimq_b200 import ops
+    assert ops.last_device_status() == 0
+    _, rel_b = o.parity_metrics(got, want_bf16)
+    _, rel_f = o.parity_metrics(got, want_fp32)
+    assert rel_b <= 1.5e-2, rel_b      # bf16 activations: see the module docstring
+    assert rel_f <= 3e-2, rel_f
+    assert abs(model.lut_flops(256) - 928.8e9) / 928.8e9 < 0.01   # per-batch work of the reference config
