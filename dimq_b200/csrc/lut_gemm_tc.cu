@@ -74,6 +74,9 @@ struct TcParams {
   int tw, th, tb, tiles_w, tiles_h;
   int OW, OH, Bn;
   int stride, pad_h, pad_w, dil_h, dil_w, KW, c_blocks;
+  // epilogue through shared memory and TMA stores (epi_tma != 0); chunk box of the conv output
+  int epi_tma, epi_res;       // epi_res: the residual is fetched with TMA too
+  int cbw, cbh;               // pixels of one 32-pixel chunk along w and h (conv)
   int rep;                    // 1: every 128-row tile lies in one codebook group -> replicated tables
   int dbg;                    // diagnostics: 1 skip epilogue work, 2 skip dequant work, 4 skip MMAs
   unsigned long long* prof;   // optional per-CTA wait-cycle counters (diagnostics), else null
@@ -81,15 +84,19 @@ struct TcParams {
 
 struct TmapSet {
   CUtensorMap m[4];   // GEMM: m[0]; conv: one map per (row, column) parity of a stride-2 input
+  CUtensorMap y;      // output, boxes of 32 features x 32 rows / pixels (TMA-store epilogue)
+  CUtensorMap r;      // residual, same geometry as y
 };
 
 struct SharedHeader {
   uint64_t x_full[kXStages], x_empty[kXStages];
   uint64_t w_full[kWStages], w_empty[kWStages];
   uint64_t d_full[kAccStages], d_empty[kAccStages];
+  uint64_t r_full[kNumEpilogueWarps][2];   // residual tiles of the TMA epilogue, per warp, double-buffered
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
 };
+constexpr int kHeaderBytes = 512;
 
 // Diagnostics: cycles spent inside one bounded wait, accumulated per role when p.prof is set.
 #define DIMQ_TIMED(acc, expr)                                   \
@@ -203,6 +210,49 @@ __device__ __forceinline__ void store_chunk_conv(const uint32_t (&r)[32], const 
   }
 }
 
+// ---- epilogue through shared memory + TMA (p.epi_tma) -----------------------------------------
+// Box coordinates of chunk c (32 rows / pixels) of tile t for the warp of TMEM lane quarter `quarter`.
+__device__ __forceinline__ void epi_coords(const TcParams& p, int t, int c, int quarter, int& c0, int& c1, int& c2,
+                                           int& c3) {
+  const int m_blk = t % p.m_tiles, n_blk = t / p.m_tiles;
+  c0 = n_blk * kTileW + quarter * 32;
+  if (!p.conv) {
+    c1 = m_blk * p.tx + c * 32;
+    c2 = c3 = 0;
+    return;
+  }
+  const int p0 = c * 32;                      // tw divides 32 or 32 divides tw * th: a chunk is a box
+  const int hh0 = (p0 / p.tw) % p.th, bb0 = p0 / (p.tw * p.th);
+  c1 = (m_blk % p.tiles_w) * p.tw;
+  c2 = ((m_blk / p.tiles_w) % p.tiles_h) * p.th + hh0;
+  c3 = (m_blk / (p.tiles_w * p.tiles_h)) * p.tb + bb0;
+}
+
+__device__ __forceinline__ void epi_issue_residual(const TmapSet& tmaps, const TcParams& p, SharedHeader* hdr,
+                                                   unsigned char* dst, int ew, int buf, int t, int c, int quarter) {
+  int c0, c1, c2, c3;
+  epi_coords(p, t, c, quarter, c0, c1, c2, c3);
+  const uint32_t bar = smem_u32(&hdr->r_full[ew][buf]);
+  mbar_arrive_expect_tx(bar, 32u * 32u * 2u);
+  if (p.conv) tma_load_4d(smem_u32(dst), &tmaps.r, bar, c0, c1, c2, c3);
+  else tma_load_2d(smem_u32(dst), &tmaps.r, bar, c0, c1);
+}
+
+// thread = feature (lane), r[j] = row / pixel j of the chunk: write the [32 rows][32 features] tile
+template <typename T>
+__device__ __forceinline__ void stage_chunk(const uint32_t (&r)[32], unsigned char* out, const unsigned char* res,
+                                            int lane, float bias, int epilogue) {
+  T* o = reinterpret_cast<T*>(out) + lane;
+  const T* rs = reinterpret_cast<const T*>(res) + lane;
+  if (res != nullptr) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) o[j * 32] = from_float<T>(finish<T, true>(__uint_as_float(r[j]) + bias, epilogue, rs + j * 32));
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) o[j * 32] = from_float<T>(finish<T, false>(__uint_as_float(r[j]) + bias, epilogue, nullptr));
+  }
+}
+
 __device__ __forceinline__ void cp_async(uint32_t dst, const void* src, int bytes) {
   if (bytes == 16)
     asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
@@ -270,11 +320,15 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
   unsigned char* x_stage = smem;
   const uint32_t n_xs = static_cast<uint32_t>(p.x_stages);
   SharedHeader* hdr = reinterpret_cast<SharedHeader*>(smem + n_xs * p.x_stage_bytes);
-  unsigned char* idx_ring = reinterpret_cast<unsigned char*>(hdr) + 256;  // [kIdxPrefetch][dequant threads][slot]
+  unsigned char* epi_stage = reinterpret_cast<unsigned char*>(hdr) + kHeaderBytes;   // TMA epilogue staging, per warp
+  const int out_esize = p.y_dtype == DIMQ_F32 ? 4 : 2;
+  const uint32_t epi_out_bytes = 32u * 32u * out_esize;
+  const uint32_t epi_warp_bytes = p.epi_tma ? epi_out_bytes * (p.epi_res ? 3u : 1u) : 0u;
+  unsigned char* idx_ring = epi_stage + kNumEpilogueWarps * epi_warp_bytes;  // [kIdxPrefetch][dequant threads][slot]
   constexpr int kRingBytes = kIdxPrefetch * kNumDequantWarps * 32 * IdxSlot<BITS>::kBytes;
   uint32_t* rep_tables = reinterpret_cast<uint32_t*>(idx_ring + kRingBytes);  // [groups of warps][kRepWords]
   uint32_t* table = rep_tables + (p.rep ? kNumDequantGroups * kRepWords : 0);
-  static_assert(sizeof(SharedHeader) <= 256, "header");
+  static_assert(sizeof(SharedHeader) <= kHeaderBytes, "header");
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -288,6 +342,7 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
     for (int s = 0; s < kXStages; ++s) { mbar_init(smem_u32(&hdr->x_full[s]), 1); mbar_init(smem_u32(&hdr->x_empty[s]), 1); }
     for (int s = 0; s < kWStages; ++s) { mbar_init(smem_u32(&hdr->w_full[s]), 4); mbar_init(smem_u32(&hdr->w_empty[s]), 1); }
     for (int s = 0; s < kAccStages; ++s) { mbar_init(smem_u32(&hdr->d_full[s]), 1); mbar_init(smem_u32(&hdr->d_empty[s]), kNumEpilogueWarps); }
+    for (int e = 0; e < kNumEpilogueWarps; ++e) { mbar_init(smem_u32(&hdr->r_full[e][0]), 1); mbar_init(smem_u32(&hdr->r_full[e][1]), 1); }
     hdr->abort_flag = 0u;
     fence_barrier_init();
     prefetch_tensormap(&tmaps.m[0]);
@@ -446,6 +501,17 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
     // ===================== epilogue =====================
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32)
     const int sub = (warp - 2) >> 2;  // which of the two warps of this quarter: chunks sub, sub + 2, ...
+    const int ew = warp - 2;          // epilogue warp index, 0..7
+    unsigned char* my_out = epi_stage + ew * epi_warp_bytes;
+    unsigned char* my_res = my_out + epi_out_bytes;
+    uint32_t res_ph[2] = {0u, 0u};
+    int res_buf = 0;
+    if (p.epi_tma && p.epi_res && lane == 0) {
+      // residual tile of this warp's first chunk
+      const int t0 = blockIdx.x;
+      if (t0 < num_tiles && sub < (p.tx + 31) / 32 && (t0 / p.m_tiles) * kTileW + quarter * 32 < p.N)
+        epi_issue_residual(tmaps, p, hdr, my_res, ew, 0, t0, sub, quarter);
+    }
     uint32_t as = 0, aph = 0;
     bool ok = true;
     unsigned long long w_df = 0;
@@ -469,6 +535,54 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&hdr->d_empty[as]));
       }
+      if (p.epi_tma) {
+        const int n_box = n_blk * kTileW + quarter * 32;   // first feature of this warp's boxes
+        const bool warp_has_n = n_box < p.N;
+        for (int c = sub; c < n_chunks; c += 2) {
+          uint32_t r[32];
+          __syncwarp();
+          tmem_ld32(d_tmem + c * 32, r);
+          tmem_ld_wait();
+          if (c + 2 >= n_chunks) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&hdr->d_empty[as]));
+          }
+          if (!warp_has_n) continue;
+          // the next chunk of this warp (same tile, or the first one of its next tile)
+          int t_next = t, c_next = c + 2;
+          if (c_next >= n_chunks) { t_next = t + gridDim.x; c_next = sub; }
+          const bool has_next = t_next < num_tiles && c_next < n_chunks &&
+                                (t_next / p.m_tiles) * kTileW + quarter * 32 < p.N;
+          if (p.epi_res) {
+            if (lane == 0) {
+              if (has_next) epi_issue_residual(tmaps, p, hdr, my_res + (res_buf ^ 1) * epi_out_bytes, ew, res_buf ^ 1, t_next, c_next, quarter);
+            }
+            uint32_t got = 0;
+            if (lane == 0) got = mbar_wait(smem_u32(&hdr->r_full[ew][res_buf]), res_ph[res_buf], abort_flag, 0x700u | ew) ? 1u : 0u;
+            if (!__shfl_sync(0xFFFFFFFFu, got, 0)) { ok = false; break; }
+            res_ph[res_buf] ^= 1u;
+          }
+          // the previous store of this warp must have finished reading the staging tile
+          if (lane == 0) tma_store_wait_read();
+          __syncwarp();
+          const unsigned char* res_tile = my_res + res_buf * epi_out_bytes;
+          if (p.y_dtype == DIMQ_BF16) stage_chunk<__nv_bfloat16>(r, my_out, p.epi_res ? res_tile : nullptr, lane, bias, p.epilogue);
+          else if (p.y_dtype == DIMQ_F16) stage_chunk<__half>(r, my_out, p.epi_res ? res_tile : nullptr, lane, bias, p.epilogue);
+          else stage_chunk<float>(r, my_out, nullptr, lane, bias, p.epilogue);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            int c0, c1, c2, c3;
+            epi_coords(p, t, c, quarter, c0, c1, c2, c3);
+            if (p.conv) tma_store_4d(&tmaps.y, smem_u32(my_out), c0, c1, c2, c3);
+            else tma_store_2d(&tmaps.y, smem_u32(my_out), c0, c1);
+            tma_store_commit();
+          }
+          if (p.epi_res) res_buf ^= 1;
+        }
+        if (!ok) break;
+      } else
       for (int c = sub; c < n_chunks; c += 2) {
         uint32_t r[32];
         __syncwarp();
@@ -498,6 +612,7 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
       }
       if (++as == kAccStages) { as = 0; aph ^= 1u; }
     }
+    if (p.epi_tma && lane == 0) tma_store_wait_all();
     if (p.prof && warp == 2 && lane == 0) { p.prof[blockIdx.x * 16 + 6] = w_df; p.prof[blockIdx.x * 16 + 7] = clock64() - t_begin; }
   } else {
     // ===================== dequantisation =====================
@@ -722,6 +837,39 @@ bool tc_supported(const void* x, int x_dtype, const dimq_wq_weight* w, int64_t M
 
 namespace {
 
+bool epi_tma_enabled() {
+  const char* env = getenv("DIMQ_B200_TC_EPI");
+  return env == nullptr || atoi(env) != 0;
+}
+
+CUtensorMapDataType tmap_dtype(int dtype) {
+  return dtype == DIMQ_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                           : (dtype == DIMQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+}
+
+// Tensor map over an output-like tensor (y or the residual): rank 2 [rows][N] for the GEMM, rank 4
+// [B][OH][OW][N] for the convolution; boxes of 32 features x 32 rows / pixels, no swizzle.
+bool encode_out_map(EncodeTiledFn encode, CUtensorMap* m, const void* base, int dtype, int rank,
+                    const cuuint64_t* dims, const cuuint32_t* box) {
+  const cuuint64_t es = dtype == DIMQ_F32 ? 4 : 2;
+  cuuint64_t strides[3];
+  cuuint64_t acc = dims[0] * es;
+  for (int i = 0; i < rank - 1; ++i) { strides[i] = acc; acc *= dims[i + 1]; }
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  return encode(m, tmap_dtype(dtype), rank, const_cast<void*>(base), dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Whether y (and the residual) can go through the TMA epilogue.
+bool epi_tma_possible(const void* y, int y_dtype, const void* residual, int64_t N) {
+  if (!epi_tma_enabled()) return false;
+  const int64_t es = y_dtype == DIMQ_F32 ? 4 : 2;
+  if (!aligned(y, 16) || (N * es) % 16 != 0) return false;
+  if (residual != nullptr && (y_dtype == DIMQ_F32 || !aligned(residual, 16))) return false;
+  return true;
+}
+
 // Fills the fields shared by the GEMM and the convolution, sizes shared memory and launches.
 int finish_launch(const TmapSet& tmaps, TcParams& p, const dimq_wq_weight* w, const uint8_t* packed, int x_dtype,
                   const void* bias, int bias_dtype, const void* residual, void* y, int y_dtype, int epilogue,
@@ -758,7 +906,8 @@ int finish_launch(const TmapSet& tmaps, TcParams& p, const dimq_wq_weight* w, co
   const bool pair = w->bits != 8 && table_bytes(w->bits, w->groups, true, split) <= (size_t)kMaxTableBytes;
   p.rep = 0;
   if (const char* env = getenv("DIMQ_B200_TC_REP")) p.rep = (atoi(env) != 0 && (w->groups == 1 || w->group_rows % kTileW == 0)) ? 1 : 0;
-  const size_t fixed = 1024 + 256 + static_cast<size_t>(kIdxPrefetch) * kNumDequantWarps * 32 * (w->bits == 8 ? 64 : 32) +
+  const size_t epi_bytes = p.epi_tma ? static_cast<size_t>(kNumEpilogueWarps) * 32 * 32 * (y_dtype == DIMQ_F32 ? 4 : 2) * (p.epi_res ? 3 : 1) : 0;
+  const size_t fixed = 1024 + kHeaderBytes + epi_bytes + static_cast<size_t>(kIdxPrefetch) * kNumDequantWarps * 32 * (w->bits == 8 ? 64 : 32) +
                        (p.rep ? static_cast<size_t>(kNumDequantGroups) * kRepWords * 4 : 0) +
                        table_bytes(w->bits, w->groups, pair, split);
   const size_t kSmemMax = 227 * 1024;
@@ -809,6 +958,13 @@ int launch_linear_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, con
   p.K = K;
   p.tx = kTileX;
   p.m_tiles = static_cast<int>((M + kTileX - 1) / kTileX);
+  if (epi_tma_possible(y, y_dtype, residual, N)) {
+    const cuuint64_t odims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M)};
+    const cuuint32_t obox[2] = {32, 32};
+    bool ok_maps = encode_out_map(encode, &tmaps.y, y, y_dtype, 2, odims, obox);
+    if (ok_maps && residual != nullptr) ok_maps = encode_out_map(encode, &tmaps.r, residual, y_dtype, 2, odims, obox);
+    if (ok_maps) { p.epi_tma = 1; p.epi_res = residual != nullptr ? 1 : 0; }
+  }
   return finish_launch(tmaps, p, w, w->packed, x_dtype, bias, bias_dtype, residual, y, y_dtype, epilogue, precision, st);
 }
 
@@ -841,6 +997,10 @@ int launch_conv2d_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, con
   // that wastes the fewest MMA columns on positions outside the image, then the largest tile.
   int best_tx = 0, best_tw = 0, best_th = 0, best_tb = 0;
   double best_score = -1.0;
+  // the TMA epilogue stores 32-pixel chunks as boxes: that needs tw and th to be powers of two
+  // (tw <= 32) and tx a multiple of 32
+  int pow_tx = 0, pow_tw = 0, pow_th = 0, pow_tb = 0;
+  double pow_score = -1.0;
   for (int tx = kTileX; tx >= 16; tx -= 16) {
     for (int tw = 1; tw <= tx && tw <= 256; ++tw) {
       if (tx % tw != 0 || tw > OW + 15) continue;
@@ -855,9 +1015,13 @@ int launch_conv2d_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, con
         // throughput model: a stage costs max(MMA time ~ tx, a fixed issue overhead ~ 96 columns)
         const double score = useful * tx / (tx > 96 ? tx : 96) + 1e-4 * tw;
         if (score > best_score) { best_score = score; best_tx = tx; best_tw = tw; best_th = th; best_tb = tb; }
+        const bool pow2 = (tw & (tw - 1)) == 0 && (th & (th - 1)) == 0 && tw <= 32 && tx % 32 == 0;
+        if (pow2 && score > pow_score) { pow_score = score; pow_tx = tx; pow_tw = tw; pow_th = th; pow_tb = tb; }
       }
     }
   }
+  bool use_tma_epi = pow_tx != 0 && pow_score >= 0.8 * best_score && epi_tma_possible(y, y_dtype, residual, g->out_channels);
+  if (use_tma_epi) { best_tx = pow_tx; best_tw = pow_tw; best_th = pow_th; best_tb = pow_tb; }
   if (best_tx == 0) return DIMQ_ERR_UNSUPPORTED;
 
   TcParams p;
@@ -908,6 +1072,18 @@ int launch_conv2d_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, con
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
       if (r != CUDA_SUCCESS) return DIMQ_ERR_DRIVER;
     }
+  }
+  if (use_tma_epi) {
+    p.cbw = best_tw;                                         // tw <= 32
+    p.cbh = best_th < 32 / best_tw ? best_th : 32 / best_tw;
+    const int cbb = 32 / (p.cbw * p.cbh);
+    const cuuint64_t odims[4] = {static_cast<cuuint64_t>(g->out_channels), static_cast<cuuint64_t>(OW),
+                                 static_cast<cuuint64_t>(OH), static_cast<cuuint64_t>(B)};
+    const cuuint32_t obox[4] = {32, static_cast<cuuint32_t>(p.cbw), static_cast<cuuint32_t>(p.cbh),
+                                static_cast<cuuint32_t>(cbb)};
+    bool ok_maps = encode_out_map(encode, &tmaps.y, y, y_dtype, 4, odims, obox);
+    if (ok_maps && residual != nullptr) ok_maps = encode_out_map(encode, &tmaps.r, residual, y_dtype, 4, odims, obox);
+    if (ok_maps) { p.epi_tma = 1; p.epi_res = residual != nullptr ? 1 : 0; }
   }
   return finish_launch(tmaps, p, w, w->packed_khwc, x_dtype, bias, bias_dtype, residual, y, y_dtype, epilogue, 0, st);
 }
