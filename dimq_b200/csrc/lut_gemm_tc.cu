@@ -238,19 +238,52 @@ __device__ __forceinline__ void epi_issue_residual(const TmapSet& tmaps, const T
   else tma_load_2d(smem_u32(dst), &tmaps.r, bar, c0, c1);
 }
 
-// thread = feature (lane), r[j] = row / pixel j of the chunk: write the [32 rows][32 features] tile
-template <typename T>
-__device__ __forceinline__ void stage_chunk(const uint32_t (&r)[32], unsigned char* out, const unsigned char* res,
-                                            int lane, float bias, int epilogue) {
-  T* o = reinterpret_cast<T*>(out) + lane;
-  const T* rs = reinterpret_cast<const T*>(res) + lane;
-  if (res != nullptr) {
+// thread = feature (lane), r[j] = row / pixel j of the chunk.  The epilogue kind and the residual are
+// template parameters so that the 32 elements form straight-line code (a run-time switch inside the
+// loop serialises them: measured ~100 cycles per element).
+template <int EPI, bool RES, typename RT>
+__device__ __forceinline__ void finish_chunk(uint32_t (&r)[32], float bias, const RT* res) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) o[j * 32] = from_float<T>(finish<T, true>(__uint_as_float(r[j]) + bias, epilogue, rs + j * 32));
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) o[j * 32] = from_float<T>(finish<T, false>(__uint_as_float(r[j]) + bias, epilogue, nullptr));
+  for (int j = 0; j < 32; ++j) {
+    float v = __uint_as_float(r[j]) + bias;
+    if (EPI == DIMQ_EPI_ADD_RELU) {
+      if (RES) v += to_float<RT>(res[j * 32]);
+      v = fmaxf(v, 0.0f);
+    } else {
+      if (EPI == DIMQ_EPI_RELU) v = fmaxf(v, 0.0f);
+      if (EPI == DIMQ_EPI_GELU) v = 0.5f * v * (1.0f + fast_erf(v * 0.70710678118654752440f));
+      if (RES) v += to_float<RT>(res[j * 32]);
+    }
+    r[j] = __float_as_uint(v);
   }
+}
+
+template <bool RES, typename RT>
+__device__ __forceinline__ void finish_chunk_epi(uint32_t (&r)[32], float bias, const RT* res, int epilogue) {
+  switch (epilogue) {
+    case DIMQ_EPI_RELU: finish_chunk<DIMQ_EPI_RELU, RES, RT>(r, bias, res); break;
+    case DIMQ_EPI_GELU: finish_chunk<DIMQ_EPI_GELU, RES, RT>(r, bias, res); break;
+    case DIMQ_EPI_ADD_RELU: finish_chunk<DIMQ_EPI_ADD_RELU, RES, RT>(r, bias, res); break;
+    default: finish_chunk<DIMQ_EPI_NONE, RES, RT>(r, bias, res); break;
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], unsigned char* out, int lane) {
+  T* o = reinterpret_cast<T*>(out) + lane;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) o[j * 32] = from_float<T>(__uint_as_float(r[j]));
+}
+
+// [32 rows][32 features] staging tile of one chunk; `res` is the residual tile in the same layout.
+__device__ __forceinline__ void stage_chunk(uint32_t (&r)[32], unsigned char* out, const unsigned char* res, int lane,
+                                            float bias, int epilogue, int y_dtype) {
+  if (res == nullptr) finish_chunk_epi<false, float>(r, bias, nullptr, epilogue);
+  else if (y_dtype == DIMQ_BF16) finish_chunk_epi<true, __nv_bfloat16>(r, bias, reinterpret_cast<const __nv_bfloat16*>(res) + lane, epilogue);
+  else finish_chunk_epi<true, __half>(r, bias, reinterpret_cast<const __half*>(res) + lane, epilogue);
+  if (y_dtype == DIMQ_BF16) write_chunk<__nv_bfloat16>(r, out, lane);
+  else if (y_dtype == DIMQ_F16) write_chunk<__half>(r, out, lane);
+  else write_chunk<float>(r, out, lane);
 }
 
 __device__ __forceinline__ void cp_async(uint32_t dst, const void* src, int bytes) {
@@ -461,31 +494,49 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
         if (!DIMQ_TIMED(w_de, mbar_wait(smem_u32(&hdr->d_empty[as]), aph ^ 1u, abort_flag, 0x200u | as))) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + kAccCol + as * kTileX;
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!DIMQ_TIMED(w_xf, mbar_wait2(smem_u32(&hdr->x_full[xs]), xph, smem_u32(&hdr->w_full[ws]), wph, abort_flag, 0x300u | xs))) { ok = false; break; }
-          long long tq0 = p.prof ? clock64() : 0;
-          tc_fence_after();
-          if (p.prof) { const long long tq1 = clock64(); t_fe += tq1 - tq0; tq0 = tq1; }
-          const uint64_t b_desc = desc0 + static_cast<uint64_t>(xs * (p.x_stage_bytes >> 4));
-          const uint32_t a_tmem = a0 + ws * kWStageCols;
-          // advance 16 k: 32 bytes inside the swizzled row (encoded >> 4), 8 TMEM columns
+        // k blocks are issued two at a time: the four barrier polls of a pair overlap, which halves the
+        // time this thread spends waiting per MMA (its latency, not the tensor pipe, bounds the loop)
+        auto issue_block = [&](int kb, uint32_t xs_, uint32_t ws_) {
+          const uint64_t b_desc = desc0 + static_cast<uint64_t>(xs_ * (p.x_stage_bytes >> 4));
+          const uint32_t a_tmem = a0 + ws_ * kWStageCols;
           if (!(p.dbg & 4)) {
-          if (kb == 0) mma_f16_ts(d_tmem, a_tmem, b_desc, p.idesc, 0u);
-          else mma_f16_ts_acc(d_tmem, a_tmem, b_desc, p.idesc);
-          if (SPLIT) mma_f16_ts_acc(d_tmem, a_tmem + kBlockK / 2, b_desc, p.idesc);
+            // advance 16 k: 32 bytes inside the swizzled row (encoded >> 4), 8 TMEM columns
+            if (kb == 0) mma_f16_ts(d_tmem, a_tmem, b_desc, p.idesc, 0u);
+            else mma_f16_ts_acc(d_tmem, a_tmem, b_desc, p.idesc);
+            if (SPLIT) mma_f16_ts_acc(d_tmem, a_tmem + kBlockK / 2, b_desc, p.idesc);
 #pragma unroll
-          for (int j = 1; j < kBlockK / 16; ++j) {
-            mma_f16_ts_acc(d_tmem, a_tmem + j * 8, b_desc + static_cast<uint64_t>(j * 2), p.idesc);
-            if (SPLIT) mma_f16_ts_acc(d_tmem, a_tmem + kBlockK / 2 + j * 8, b_desc + static_cast<uint64_t>(j * 2), p.idesc);
+            for (int j = 1; j < kBlockK / 16; ++j) {
+              mma_f16_ts_acc(d_tmem, a_tmem + j * 8, b_desc + static_cast<uint64_t>(j * 2), p.idesc);
+              if (SPLIT) mma_f16_ts_acc(d_tmem, a_tmem + kBlockK / 2 + j * 8, b_desc + static_cast<uint64_t>(j * 2), p.idesc);
+            }
           }
+          // one commit per k block: the producer (activation slot) and the dequantisation group
+          // that will reuse this weight slot both wait on it
+          mma_commit(smem_u32(&hdr->x_empty[xs_]));
+        };
+        for (int kb = 0; kb < k_blocks;) {
+          const bool two = kb + 1 < k_blocks;
+          uint32_t xs1 = xs + 1, xph1 = xph, ws1 = ws + 1, wph1 = wph;
+          if (xs1 == n_xs) { xs1 = 0; xph1 ^= 1u; }
+          if (ws1 == kWStagesUsed) { ws1 = 0; wph1 ^= 1u; }
+          const long long tq0 = p.prof ? clock64() : 0;
+          const bool got = two ? mbar_wait4(smem_u32(&hdr->x_full[xs]), xph, smem_u32(&hdr->w_full[ws]), wph,
+                                            smem_u32(&hdr->x_full[xs1]), xph1, smem_u32(&hdr->w_full[ws1]), wph1,
+                                            abort_flag, 0x300u | xs)
+                               : mbar_wait2(smem_u32(&hdr->x_full[xs]), xph, smem_u32(&hdr->w_full[ws]), wph,
+                                            abort_flag, 0x300u | xs);
+          if (!got) { ok = false; break; }
+          tc_fence_after();
+          const long long tq1 = p.prof ? clock64() : 0;
+          issue_block(kb, xs, ws);
+          if (two) issue_block(kb + 1, xs1, ws1);
+          if (p.prof) { w_xf += tq1 - tq0; t_mm += clock64() - tq1; }
+          const int nb = two ? 2 : 1;
+          for (int i = 0; i < nb; ++i) {
+            if (++xs == n_xs) { xs = 0; xph ^= 1u; }
+            if (++ws == kWStagesUsed) { ws = 0; wph ^= 1u; }
           }
-          if (p.prof) { const long long tq1 = clock64(); t_mm += tq1 - tq0; tq0 = tq1; }
-          // one commit per k block: the producer (activation slot xs) and the dequantisation
-          // group that will reuse this weight slot both wait on it
-          mma_commit(smem_u32(&hdr->x_empty[xs]));
-          if (p.prof) { const long long tq1 = clock64(); t_cm += tq1 - tq0; }
-          if (++xs == n_xs) { xs = 0; xph ^= 1u; }
-          if (++ws == kWStagesUsed) { ws = 0; wph ^= 1u; }
+          kb += nb;
         }
         if (!ok) break;
         mma_commit(smem_u32(&hdr->d_full[as]));
@@ -514,7 +565,7 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
     }
     uint32_t as = 0, aph = 0;
     bool ok = true;
-    unsigned long long w_df = 0;
+    unsigned long long w_df = 0, t_ewait = 0, t_estage = 0;
     const long long t_begin = clock64();
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       const int m_blk = t % p.m_tiles, n_blk = t / p.m_tiles;
@@ -564,14 +615,15 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
             res_ph[res_buf] ^= 1u;
           }
           // the previous store of this warp must have finished reading the staging tile
+          const long long te0 = p.prof ? clock64() : 0;
           if (lane == 0) tma_store_wait_read();
           __syncwarp();
+          const long long te1 = p.prof ? clock64() : 0;
           const unsigned char* res_tile = my_res + res_buf * epi_out_bytes;
-          if (p.y_dtype == DIMQ_BF16) stage_chunk<__nv_bfloat16>(r, my_out, p.epi_res ? res_tile : nullptr, lane, bias, p.epilogue);
-          else if (p.y_dtype == DIMQ_F16) stage_chunk<__half>(r, my_out, p.epi_res ? res_tile : nullptr, lane, bias, p.epilogue);
-          else stage_chunk<float>(r, my_out, nullptr, lane, bias, p.epilogue);
+          stage_chunk(r, my_out, p.epi_res ? res_tile : nullptr, lane, bias, p.epilogue, p.y_dtype);
           fence_proxy_async_smem();
           __syncwarp();
+          if (p.prof) { const long long te2 = clock64(); t_ewait += te1 - te0; t_estage += te2 - te1; }
           if (lane == 0) {
             int c0, c1, c2, c3;
             epi_coords(p, t, c, quarter, c0, c1, c2, c3);
@@ -613,7 +665,7 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
       if (++as == kAccStages) { as = 0; aph ^= 1u; }
     }
     if (p.epi_tma && lane == 0) tma_store_wait_all();
-    if (p.prof && warp == 2 && lane == 0) { p.prof[blockIdx.x * 16 + 6] = w_df; p.prof[blockIdx.x * 16 + 7] = clock64() - t_begin; }
+    if (p.prof && warp == 2 && lane == 0) { p.prof[blockIdx.x * 16 + 14] = t_ewait; p.prof[blockIdx.x * 16 + 15] = t_estage; p.prof[blockIdx.x * 16 + 6] = w_df; p.prof[blockIdx.x * 16 + 7] = clock64() - t_begin; }
   } else {
     // ===================== dequantisation =====================
     // 8 warps in 2 groups of 4 (one warp per TMEM lane quarter).  Group g dequantises stages
@@ -724,6 +776,10 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
       if (++slot == kIdxPrefetch) slot = 0;
       uint32_t out[32];
       uint32_t out_lo[SPLIT ? 32 : 1];
+      if (p.dbg & 16) {   // diagnostics: no lookups
+#pragma unroll
+        for (int q = 0; q < 32; ++q) { out[q] = cur[q % (2 * BITS)]; if (SPLIT) out_lo[SPLIT ? q : 0] = 0u; }
+      } else
       if (PAIR) {
         const int stride = rep ? kRep * kWpe : kWpe;  // words between consecutive entries
 #pragma unroll

@@ -106,6 +106,23 @@ __device__ __forceinline__ bool mbar_wait2(uint32_t bar_a, uint32_t par_a, uint3
   return false;
 }
 
+// The same for two (activation, weight) barrier pairs: four polls in flight.
+__device__ __forceinline__ bool mbar_wait4(uint32_t a0, uint32_t pa0, uint32_t b0, uint32_t pb0, uint32_t a1,
+                                           uint32_t pa1, uint32_t b1, uint32_t pb1, volatile uint32_t* abort_flag,
+                                           uint32_t code) {
+  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+    const bool r0 = mbar_try_wait(a0, pa0);
+    const bool r1 = mbar_try_wait(b0, pb0);
+    const bool r2 = mbar_try_wait(a1, pa1);
+    const bool r3 = mbar_try_wait(b1, pb1);
+    if (r0 && r1 && r2 && r3) return true;
+    if ((it & 255u) == 255u && *abort_flag != 0u) return false;
+  }
+  *abort_flag = 1u;
+  atomicOr(&g_device_status, 0x80000000u | code);
+  return false;
+}
+
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
