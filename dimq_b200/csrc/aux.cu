@@ -108,3 +108,138 @@ extern "C" int dimq_add_layer_norm(const void* x, const void* delta, const void*
         static_cast<int>(cols), eps);
   return launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------
+// Explicit im2col for convolutions whose channel count does not fit the implicit-GEMM kernel (the
+// 3-channel ResNet stem), and a 16-bit NHWC max-pool.  Both are streaming kernels: 16-byte stores,
+// consecutive threads write consecutive vectors.
+// ---------------------------------------------------------------------------------------------
+namespace dimq {
+namespace {
+
+constexpr int kAuxThreads = 256;
+
+// cols[(b, oh, ow)][k], k = (kh * KW + kw) * C + c for k < KH*KW*C, zero for the padding columns up
+// to kp.  One thread writes 8 consecutive k of one output pixel.
+template <typename T>
+__global__ void __launch_bounds__(kAuxThreads)
+im2col_kernel(const T* __restrict__ x, T* __restrict__ cols, dimq_conv_geom g, int kp) {
+  const int vec_per_row = kp / 8;
+  const int64_t total = static_cast<int64_t>(g.batch) * g.out_h * g.out_w * vec_per_row;
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * kAuxThreads + threadIdx.x;
+  if (i >= total) return;
+  const int v = static_cast<int>(i % vec_per_row);
+  const int64_t pix = i / vec_per_row;
+  const int ow = static_cast<int>(pix % g.out_w);
+  const int oh = static_cast<int>((pix / g.out_w) % g.out_h);
+  const int b = static_cast<int>(pix / (static_cast<int64_t>(g.out_w) * g.out_h));
+  const int C = g.in_channels, k_real = g.kernel_h * g.kernel_w * C;
+  uint4 out;
+  T* o = reinterpret_cast<T*>(&out);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const int k = v * 8 + e;
+    T val = from_float<T>(0.0f);
+    if (k < k_real) {
+      const int c = k % C, tap = k / C;
+      const int kw = tap % g.kernel_w, kh = tap / g.kernel_w;
+      const int ih = oh * g.stride_h + kh * g.dilation_h - g.pad_h;
+      const int iw = ow * g.stride_w + kw * g.dilation_w - g.pad_w;
+      if (ih >= 0 && ih < g.in_h && iw >= 0 && iw < g.in_w)
+        val = x[b * g.x_stride[0] + c * g.x_stride[1] + ih * g.x_stride[2] + iw * g.x_stride[3]];
+    }
+    o[e] = val;
+  }
+  reinterpret_cast<uint4*>(cols)[i] = out;
+}
+
+// y[b][oh][ow][c] = max over the window of x[b][ih][iw][c], NHWC 16-bit, 8 channels per thread.
+template <typename T>
+__global__ void __launch_bounds__(kAuxThreads)
+max_pool_nhwc_kernel(const T* __restrict__ x, T* __restrict__ y, int B, int H, int W, int C, int OH, int OW, int k,
+                     int stride, int pad) {
+  const int cv = C / 8;
+  const int64_t total = static_cast<int64_t>(B) * OH * OW * cv;
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * kAuxThreads + threadIdx.x;
+  if (i >= total) return;
+  const int c8 = static_cast<int>(i % cv);
+  const int64_t pix = i / cv;
+  const int ow = static_cast<int>(pix % OW), oh = static_cast<int>((pix / OW) % OH);
+  const int b = static_cast<int>(pix / (static_cast<int64_t>(OW) * OH));
+  float m[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) m[e] = -INFINITY;
+  for (int dy = 0; dy < k; ++dy) {
+    const int ih = oh * stride + dy - pad;
+    if (ih < 0 || ih >= H) continue;
+    for (int dx = 0; dx < k; ++dx) {
+      const int iw = ow * stride + dx - pad;
+      if (iw < 0 || iw >= W) continue;
+      const uint4 q = __ldg(reinterpret_cast<const uint4*>(x + ((static_cast<int64_t>(b) * H + ih) * W + iw) * C) + c8);
+      const T* e8 = reinterpret_cast<const T*>(&q);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) m[e] = fmaxf(m[e], to_float<T>(e8[e]));
+    }
+  }
+  uint4 out;
+  T* o = reinterpret_cast<T*>(&out);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) o[e] = from_float<T>(m[e]);
+  reinterpret_cast<uint4*>(y + ((static_cast<int64_t>(b) * OH + oh) * OW + ow) * C)[c8] = out;
+}
+
+}  // namespace
+}  // namespace dimq
+
+extern "C" int dimq_im2col(const void* x, int dtype, const dimq_conv_geom* geom, int64_t padded_k, void* cols,
+                           void* stream) {
+  if (geom == nullptr) return DIMQ_ERR_NULL_POINTER;
+  if (dtype != DIMQ_BF16 && dtype != DIMQ_F16) return DIMQ_ERR_BAD_DTYPE;
+  dimq_conv_geom g = *geom;
+  const int rc = dimq_conv_out_size(&g);
+  if (rc != DIMQ_OK) return rc;
+  if (g.groups != 1) return DIMQ_ERR_UNSUPPORTED;
+  const int64_t k_real = static_cast<int64_t>(g.kernel_h) * g.kernel_w * g.in_channels;
+  if (padded_k < k_real || padded_k % 8 != 0 || padded_k > (1 << 20)) return DIMQ_ERR_BAD_SIZE;
+  const int64_t total = static_cast<int64_t>(g.batch) * g.out_h * g.out_w * (padded_k / 8);
+  if (total == 0) return DIMQ_OK;
+  if (x == nullptr || cols == nullptr) return DIMQ_ERR_NULL_POINTER;
+  if (!aligned(cols, 16)) return DIMQ_ERR_ALIGNMENT;
+  const int64_t blocks = (total + kAuxThreads - 1) / kAuxThreads;
+  if (blocks > 0x7FFFFFFFll) return DIMQ_ERR_TOO_LARGE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == DIMQ_BF16)
+    im2col_kernel<__nv_bfloat16><<<(unsigned)blocks, kAuxThreads, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(cols), g, static_cast<int>(padded_k));
+  else
+    im2col_kernel<__half><<<(unsigned)blocks, kAuxThreads, 0, st>>>(static_cast<const __half*>(x),
+                                                                   static_cast<__half*>(cols), g,
+                                                                   static_cast<int>(padded_k));
+  return launch_status();
+}
+
+extern "C" int dimq_max_pool_nhwc(const void* x, void* y, int dtype, int64_t batch, int64_t height, int64_t width,
+                                  int64_t channels, int kernel, int stride, int pad, void* stream) {
+  if (dtype != DIMQ_BF16 && dtype != DIMQ_F16) return DIMQ_ERR_BAD_DTYPE;
+  if (batch < 0 || height <= 0 || width <= 0 || channels <= 0 || kernel <= 0 || stride <= 0 || pad < 0 || 2 * pad > kernel)
+    return DIMQ_ERR_BAD_SIZE;
+  if (channels % 8 != 0) return DIMQ_ERR_UNSUPPORTED;
+  const int64_t oh = (height + 2 * pad - kernel) / stride + 1, ow = (width + 2 * pad - kernel) / stride + 1;
+  if (oh <= 0 || ow <= 0) return DIMQ_ERR_BAD_SHAPE;
+  const int64_t total = batch * oh * ow * (channels / 8);
+  if (total == 0) return DIMQ_OK;
+  if (x == nullptr || y == nullptr) return DIMQ_ERR_NULL_POINTER;
+  if (!aligned(x, 16) || !aligned(y, 16)) return DIMQ_ERR_ALIGNMENT;
+  const int64_t blocks = (total + kAuxThreads - 1) / kAuxThreads;
+  if (blocks > 0x7FFFFFFFll) return DIMQ_ERR_TOO_LARGE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == DIMQ_BF16)
+    max_pool_nhwc_kernel<__nv_bfloat16><<<(unsigned)blocks, kAuxThreads, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), (int)batch, (int)height, (int)width,
+        (int)channels, (int)oh, (int)ow, kernel, stride, pad);
+  else
+    max_pool_nhwc_kernel<__half><<<(unsigned)blocks, kAuxThreads, 0, st>>>(
+        static_cast<const __half*>(x), static_cast<__half*>(y), (int)batch, (int)height, (int)width, (int)channels,
+        (int)oh, (int)ow, kernel, stride, pad);
+  return launch_status();
+}

@@ -541,6 +541,41 @@ def conv_prepack(packed_weight: torch.Tensor, weight_shape: Sequence[int], bits:
     return dst
 
 
+def im2col(x: torch.Tensor, weight_shape: Sequence[int], stride, padding, dilation=(1, 1), padded_k: int | None = None):
+    """Patch matrix ``[B*OH*OW, padded_k]`` of a ``groups == 1`` convolution, columns in (kh, kw, c) order."""
+    require_extension()
+    _require_cuda(x, "im2col")
+    g = _conv_geom(x, weight_shape, _pair(stride), _pair(padding), _pair(dilation), 1)
+    k_real = g.kernel_h * g.kernel_w * g.in_channels
+    kp = int(padded_k) if padded_k is not None else (k_real + 7) // 8 * 8
+    for i in range(4):
+        g.x_stride[i] = x.stride(i)
+    cols = torch.empty((g.batch * g.out_h * g.out_w, kp), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        st = _lib.lib().dimq_im2col(_lib.ptr(x), _lib.dtype_code(x, "x"), C.byref(g), C.c_int64(kp), _lib.ptr(cols),
+                                    _lib.stream_ptr(x.device))
+    _lib.check(st, "im2col")
+    return cols, (g.out_h, g.out_w)
+
+
+def max_pool_nhwc(x: torch.Tensor, kernel: int, stride: int, padding: int) -> torch.Tensor:
+    """Max-pool of a channels_last 16-bit tensor (logical NCHW in, logical NCHW / channels_last out)."""
+    require_extension()
+    _require_cuda(x, "max_pool_nhwc")
+    if x.dim() != 4 or not x.is_contiguous(memory_format=torch.channels_last):
+        raise RuntimeError("max_pool_nhwc expects a channels_last 4-D tensor")
+    b, c, h, w = x.shape
+    oh = (h + 2 * padding - kernel) // stride + 1
+    ow = (w + 2 * padding - kernel) // stride + 1
+    y = torch.empty((b, c, oh, ow), dtype=x.dtype, device=x.device, memory_format=torch.channels_last)
+    with torch.cuda.device(x.device):
+        st = _lib.lib().dimq_max_pool_nhwc(_lib.ptr(x), _lib.ptr(y), _lib.dtype_code(x, "x"), C.c_int64(b), C.c_int64(h),
+                                           C.c_int64(w), C.c_int64(c), C.c_int(kernel), C.c_int(stride),
+                                           C.c_int(padding), _lib.stream_ptr(x.device))
+    _lib.check(st, "max_pool_nhwc")
+    return y
+
+
 def add_layer_norm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, bias: torch.Tensor,
                    eps: float = 1e-6):
     """``(x + delta, LayerNorm(x + delta))`` over the last dimension (``delta=None``: ``(x, LayerNorm(x))``).

@@ -288,21 +288,14 @@ class DIMQResNet18(nn.Module):
         return self.convs[name.replace(".", "__")]
 
     def _stem(self, images: torch.Tensor) -> torch.Tensor:
-        b, _, h, w = images.shape
-        x = F.pad(images.to(self.act_dtype).permute(0, 2, 3, 1), (0, 0, 3, 3, 3, 3))   # NHWC, padded by 3
-        hp, wp = h + 6, w + 6
-        oh, ow = (h + 6 - 7) // 2 + 1, (w + 6 - 7) // 2 + 1
-        x = x.contiguous()
-        # window (oh, ow) = 7 rows of 21 contiguous elements (7 pixels x 3 channels)
-        win = x.as_strided((b, oh, ow, 7, 21), (hp * wp * 3, 2 * wp * 3, 6, wp * 3, 1))
-        cols = torch.zeros(b * oh * ow, self.stem_kp, dtype=self.act_dtype, device=x.device)
-        cols.view(b, oh, ow, self.stem_kp)[..., : self.stem_k] = win.reshape(b, oh, ow, self.stem_k)
-        y = self.stem(cols)                                                              # [B*OH*OW, 64], ReLU fused
-        return y.view(b, oh, ow, -1).permute(0, 3, 1, 2)                                 # logical NCHW, NHWC storage
+        b = images.shape[0]
+        cols, (oh, ow) = ops.im2col(images.to(self.act_dtype), (64, 3, 7, 7), (2, 2), (3, 3), padded_k=self.stem_kp)
+        y = self.stem(cols)                                        # [B*OH*OW, 64], bias + ReLU fused
+        return y.view(b, oh, ow, -1).permute(0, 3, 1, 2)           # logical NCHW over NHWC storage
 
     def forward(self, images: torch.Tensor) -> torch.Tensor:
         x = self._stem(images)
-        x = F.max_pool2d(x, 3, 2, 1)
+        x = ops.max_pool_nhwc(x, 3, 2, 1)
         in_ch = 64
         for si, (ch, stride) in enumerate(RESNET18_STAGES, start=1):
             for bi in range(2):

@@ -201,6 +201,20 @@ DIMQ_API int dimq_add_layer_norm(const void* x, const void* delta, const void* g
                                  void* x_out, void* h_out, int64_t rows, int64_t cols, float eps, int dtype,
                                  void* stream);
 
+/* cols[(b, oh, ow)][k] = x[b][c][ih][iw] with k = (kh * KW + kw) * C + c (zero outside the image and in
+ * the padding columns k >= KH*KW*C up to padded_k, a multiple of 8): the explicit patch matrix of a
+ * groups == 1 convolution over 16-bit activations addressed by geom->x_stride.  Used for the 3-channel
+ * stem of ResNet, whose k blocks do not fit the implicit-GEMM convolution; the result feeds
+ * dimq_linear_wq with the weight re-ordered by dimq_conv_prepack.  `cols` is caller-owned scratch of
+ * batch*out_h*out_w*padded_k elements.  No counterpart in the reference. */
+DIMQ_API int dimq_im2col(const void* x, int dtype, const dimq_conv_geom* geom, int64_t padded_k, void* cols,
+                         void* stream);
+
+/* Max-pool over NHWC 16-bit activations (channels % 8 == 0); dense helper of the ResNet harness, in the
+ * reference's models this is torch.nn.MaxPool2d. */
+DIMQ_API int dimq_max_pool_nhwc(const void* x, void* y, int dtype, int64_t batch, int64_t height, int64_t width,
+                                int64_t channels, int kernel, int stride, int pad, void* stream);
+
 /* Status word written by the last tcgen05 kernel on this thread's device that
  * gave up a bounded wait (0 = none).  Reading it synchronises the device. */
 DIMQ_API int dimq_last_device_status(uint32_t* status);

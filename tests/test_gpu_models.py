@@ -145,3 +145,19 @@ def test_resnet18_forward_matches_cpu_oracle(cuda_device, fuse):
     assert rel_b <= 1.5e-2, rel_b      # bf16 activations: see the module docstring
     assert rel_f <= 3e-2, rel_f
     assert abs(model.lut_flops(256) - 928.8e9) / 928.8e9 < 0.01   # per-batch work of the reference config
+
+
+def test_im2col_and_max_pool_helpers(cuda_device):
+    from dimq_b200 import ops
+
+    torch.manual_seed(4)
+    x = torch.randn(3, 3, 19, 23, device="cuda").to(torch.bfloat16)
+    cols, (oh, ow) = ops.im2col(x, (8, 3, 7, 7), (2, 2), (3, 3), padded_k=192)
+    want = torch.nn.functional.unfold(x.float(), (7, 7), padding=3, stride=2)       # [B, C*49, L], (c, kh, kw) order
+    want = want.view(3, 3, 49, oh * ow).permute(0, 3, 2, 1).reshape(3 * oh * ow, 147)  # -> (kh, kw, c) order
+    assert cols.shape == (3 * oh * ow, 192)
+    assert torch.equal(cols[:, :147].float(), want) and not cols[:, 147:].any()
+    xcl = torch.randn(2, 16, 13, 11, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    got = ops.max_pool_nhwc(xcl, 3, 2, 1)
+    assert torch.equal(got, torch.nn.functional.max_pool2d(xcl, 3, 2, 1))
+    assert got.is_contiguous(memory_format=torch.channels_last)
