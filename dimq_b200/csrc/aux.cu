@@ -124,6 +124,19 @@ constexpr int kAuxThreads = 256;
 template <typename T>
 __global__ void __launch_bounds__(kAuxThreads)
 im2col_kernel(const T* __restrict__ x, T* __restrict__ cols, dimq_conv_geom g, int kp) {
+  // per column k: (kh * dilation, kw * dilation, c) packed as 8 | 8 | 16 bits, or -1 for a padding
+  // column; built once per block so that the element loop has no divisions
+  extern __shared__ int col_tbl[];
+  const int C = g.in_channels, k_real = g.kernel_h * g.kernel_w * C;
+  for (int k = threadIdx.x; k < kp; k += kAuxThreads) {
+    int code = -1;
+    if (k < k_real) {
+      const int c = k % C, tap = k / C;
+      code = ((tap / g.kernel_w) * g.dilation_h) | (((tap % g.kernel_w) * g.dilation_w) << 8) | (c << 16);
+    }
+    col_tbl[k] = code;
+  }
+  __syncthreads();
   const int vec_per_row = kp / 8;
   const int64_t total = static_cast<int64_t>(g.batch) * g.out_h * g.out_w * vec_per_row;
   const int64_t i = static_cast<int64_t>(blockIdx.x) * kAuxThreads + threadIdx.x;
@@ -133,21 +146,17 @@ im2col_kernel(const T* __restrict__ x, T* __restrict__ cols, dimq_conv_geom g, i
   const int ow = static_cast<int>(pix % g.out_w);
   const int oh = static_cast<int>((pix / g.out_w) % g.out_h);
   const int b = static_cast<int>(pix / (static_cast<int64_t>(g.out_w) * g.out_h));
-  const int C = g.in_channels, k_real = g.kernel_h * g.kernel_w * C;
+  const int ih0 = oh * g.stride_h - g.pad_h, iw0 = ow * g.stride_w - g.pad_w;
+  const T* xb = x + b * g.x_stride[0];
   uint4 out;
   T* o = reinterpret_cast<T*>(&out);
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
-    const int k = v * 8 + e;
+    const int code = col_tbl[v * 8 + e];
+    const int ih = ih0 + (code & 0xFF), iw = iw0 + ((code >> 8) & 0xFF);
     T val = from_float<T>(0.0f);
-    if (k < k_real) {
-      const int c = k % C, tap = k / C;
-      const int kw = tap % g.kernel_w, kh = tap / g.kernel_w;
-      const int ih = oh * g.stride_h + kh * g.dilation_h - g.pad_h;
-      const int iw = ow * g.stride_w + kw * g.dilation_w - g.pad_w;
-      if (ih >= 0 && ih < g.in_h && iw >= 0 && iw < g.in_w)
-        val = x[b * g.x_stride[0] + c * g.x_stride[1] + ih * g.x_stride[2] + iw * g.x_stride[3]];
-    }
+    if (code >= 0 && ih >= 0 && ih < g.in_h && iw >= 0 && iw < g.in_w)
+      val = xb[(code >> 16) * g.x_stride[1] + ih * g.x_stride[2] + iw * g.x_stride[3]];
     o[e] = val;
   }
   reinterpret_cast<uint4*>(cols)[i] = out;
@@ -200,7 +209,8 @@ extern "C" int dimq_im2col(const void* x, int dtype, const dimq_conv_geom* geom,
   if (rc != DIMQ_OK) return rc;
   if (g.groups != 1) return DIMQ_ERR_UNSUPPORTED;
   const int64_t k_real = static_cast<int64_t>(g.kernel_h) * g.kernel_w * g.in_channels;
-  if (padded_k < k_real || padded_k % 8 != 0 || padded_k > (1 << 20)) return DIMQ_ERR_BAD_SIZE;
+  if (padded_k < k_real || padded_k % 8 != 0 || padded_k > 8192) return DIMQ_ERR_BAD_SIZE;
+  if (g.kernel_h * g.dilation_h > 255 || g.kernel_w * g.dilation_w > 255 || g.in_channels > 32767) return DIMQ_ERR_UNSUPPORTED;
   const int64_t total = static_cast<int64_t>(g.batch) * g.out_h * g.out_w * (padded_k / 8);
   if (total == 0) return DIMQ_OK;
   if (x == nullptr || cols == nullptr) return DIMQ_ERR_NULL_POINTER;
@@ -209,10 +219,10 @@ extern "C" int dimq_im2col(const void* x, int dtype, const dimq_conv_geom* geom,
   if (blocks > 0x7FFFFFFFll) return DIMQ_ERR_TOO_LARGE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == DIMQ_BF16)
-    im2col_kernel<__nv_bfloat16><<<(unsigned)blocks, kAuxThreads, 0, st>>>(
+    im2col_kernel<__nv_bfloat16><<<(unsigned)blocks, kAuxThreads, padded_k * sizeof(int), st>>>(
         static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(cols), g, static_cast<int>(padded_k));
   else
-    im2col_kernel<__half><<<(unsigned)blocks, kAuxThreads, 0, st>>>(static_cast<const __half*>(x),
+    im2col_kernel<__half><<<(unsigned)blocks, kAuxThreads, padded_k * sizeof(int), st>>>(static_cast<const __half*>(x),
                                                                    static_cast<__half*>(cols), g,
                                                                    static_cast<int>(padded_k));
   return launch_status();
