@@ -1000,7 +1000,16 @@ int launch_linear_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, con
   memset(&tmaps, 0, sizeof(tmaps));
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
-  const cuuint32_t box[2] = {kBlockK, kTileX};
+  // activation rows per tile: 192 unless M is small or just above a multiple of a smaller tile, where a
+  // narrower tile wastes fewer MMA columns (same throughput model as the convolution's tile choice)
+  int tx_best = kTileX;
+  double tx_score = -1.0;
+  for (int tx = 32; tx <= kTileX; tx += 32) {
+    const double covered = static_cast<double>((M + tx - 1) / tx) * tx;
+    const double score = static_cast<double>(M) / covered * tx / (tx > 96 ? tx : 96);
+    if (score >= tx_score) { tx_score = score; tx_best = tx; }
+  }
+  const cuuint32_t box[2] = {kBlockK, static_cast<cuuint32_t>(tx_best)};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = encode(&tmaps.m[0], x_dtype == DIMQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
                             2, const_cast<void*>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -1012,8 +1021,8 @@ int launch_linear_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, con
   p.M = M;
   p.N = N;
   p.K = K;
-  p.tx = kTileX;
-  p.m_tiles = static_cast<int>((M + kTileX - 1) / kTileX);
+  p.tx = tx_best;
+  p.m_tiles = static_cast<int>((M + tx_best - 1) / tx_best);
   if (epi_tma_possible(y, y_dtype, residual, N)) {
     const cuuint64_t odims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M)};
     const cuuint32_t obox[2] = {32, 32};
