@@ -43,7 +43,7 @@ extern "C" const char* dimq_status_string(int status) {
     case DIMQ_ERR_DRIVER: return "tensor-map encoding through the CUDA driver failed";
     case DIMQ_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel expired";
     case DIMQ_ERR_TOO_LARGE: return "problem too large for this kernel's grid";
-    case DIMQ_ERR_SCRATCH_TOO_SMALL: return "the weight's index stream exceeds the 4 MiB built-in scratch of dimq_conv2d_wq_static";
+    case DIMQ_ERR_SCRATCH_TOO_SMALL: return "scratch too small (the 4 MiB built-in array of dimq_conv2d_wq_static, or the caller's workspace)";
     default: break;
   }
   if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));

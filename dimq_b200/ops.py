@@ -133,6 +133,19 @@ def _bias_arg(bias: torch.Tensor | None, n: int, device: torch.device, what: str
     return b, _lib.dtype_code(b, "bias")
 
 
+# W4A4 problems with at least this many activation rows (output pixels for the convolution) take the
+# tensor-core path (operands rounded to a hi + lo bf16 pair); smaller ones the exact table-lookup kernel.
+A4_TC_MIN_ROWS = 512
+_UNSUPPORTED = -7
+
+
+def _a4_workspace(x_numel: int, conv_weight_numel: int, device: torch.device) -> torch.Tensor:
+    need = C.c_int64(0)
+    _lib.check(_lib.lib().dimq_a4_workspace_bytes(C.c_int64(x_numel), C.c_int64(conv_weight_numel), C.byref(need)),
+               "last_device_status")
+    return torch.empty(need.value, dtype=torch.uint8, device=device)
+
+
 def _linear_lut_impl(x, packed_w, codebook, act_scale, act_zp, bias, out_features, in_features):
     _require_cuda(x, "linear_lut")
     _require_cuda(packed_w, "linear_lut")
@@ -160,6 +173,18 @@ def _linear_lut_impl(x, packed_w, codebook, act_scale, act_zp, bias, out_feature
     b, b_dt = _bias_arg(bias, out_features, xc.device, "out_features")
     m = xc.numel() // in_features
     y = torch.empty((m, out_features), dtype=torch.float32, device=xc.device)
+    if m >= A4_TC_MIN_ROWS and in_features % 64 == 0 and pw.data_ptr() % 16 == 0:
+        ws = _a4_workspace(xc.numel(), 0, xc.device)
+        with torch.cuda.device(xc.device):
+            st = _lib.lib().dimq_linear_lut_tc(_lib.ptr(xc), _lib.dtype_code(xc, "x"), _lib.ptr(pw), _lib.ptr(cb),
+                                               _lib.dtype_code(cb, "codebook"), C.c_float(act_scale), C.c_int(act_zp),
+                                               _lib.ptr(b), b_dt, _lib.ptr(y), C.c_int64(m), C.c_int64(out_features),
+                                               C.c_int64(in_features), _lib.ptr(ws), C.c_int64(ws.numel()),
+                                               _lib.stream_ptr(xc.device))
+        if st != _UNSUPPORTED:
+            _lib.check(st, "linear_lut_tc")
+            _lib.LAUNCH_COUNT[0] += 1  # the activation quantiser and the GEMM
+            return y.view(*x.shape[:-1], out_features)
     with torch.cuda.device(xc.device):
         st = _lib.lib().dimq_linear_lut(_lib.ptr(xc), _lib.dtype_code(xc, "x"), _lib.ptr(pw), _lib.ptr(cb),
                                         _lib.dtype_code(cb, "codebook"), C.c_float(act_scale), C.c_int(act_zp),
@@ -237,6 +262,19 @@ def _conv2d_lut_impl(x, packed_w, codebook, act_scale, act_zp, bias, out_channel
         return y
     pw = packed_w.contiguous().view(-1)
     cb = codebook.contiguous().view(-1)
+    channels_last = g.x_stride[1] == 1 and g.y_stride[1] == 1
+    if (channels_last and groups == 1 and g.in_channels % 64 == 0
+            and g.batch * g.out_h * g.out_w >= A4_TC_MIN_ROWS):
+        ws = _a4_workspace(xc.numel(), numel, x.device)
+        with torch.cuda.device(x.device):
+            st = _lib.lib().dimq_conv2d_lut_tc(_lib.ptr(xc), _lib.dtype_code(xc, "x"), _lib.ptr(pw), _lib.ptr(cb),
+                                               _lib.dtype_code(cb, "codebook"), C.c_float(act_scale), C.c_int(act_zp),
+                                               _lib.ptr(b), b_dt, _lib.ptr(y), C.byref(g), _lib.ptr(ws),
+                                               C.c_int64(ws.numel()), _lib.stream_ptr(x.device))
+        if st != _UNSUPPORTED:
+            _lib.check(st, "conv2d_lut_tc")
+            _lib.LAUNCH_COUNT[0] += 2  # index re-order, activation quantiser, convolution
+            return y
     with torch.cuda.device(x.device):
         st = _lib.lib().dimq_conv2d_lut(_lib.ptr(xc), _lib.dtype_code(xc, "x"), _lib.ptr(pw), _lib.ptr(cb),
                                         _lib.dtype_code(cb, "codebook"), C.c_float(act_scale), C.c_int(act_zp),

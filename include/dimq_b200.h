@@ -41,7 +41,7 @@ extern "C" {
 #define DIMQ_ERR_DRIVER (-9)        /* a driver entry point (tensor-map encode) is unavailable or failed */
 #define DIMQ_ERR_DEVICE_TIMEOUT (-10) /* a bounded wait inside a kernel expired (see dimq_last_device_status) */
 #define DIMQ_ERR_TOO_LARGE (-11)
-#define DIMQ_ERR_SCRATCH_TOO_SMALL (-12) /* the weight does not fit the built-in scratch of dimq_conv2d_wq_static */
+#define DIMQ_ERR_SCRATCH_TOO_SMALL (-12) /* built-in scratch of dimq_conv2d_wq_static or a caller workspace is too small */
 
 /* element types of floating tensors */
 #define DIMQ_F32 0
@@ -189,6 +189,31 @@ DIMQ_API int dimq_conv_prepack(const uint8_t* packed_kcrs, int bits, int64_t out
 DIMQ_API int dimq_conv2d_wq_static(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias,
                                    int bias_dtype, const void* residual, void* y, int y_dtype,
                                    const dimq_conv_geom* geom, int epilogue, void* stream);
+
+/* ---- W4A4 product-table ops on the tensor cores ------------------------- */
+
+/* Same operation as dimq_linear_lut / dimq_conv2d_lut (csrc/dimq_gemm_lut.cu:58-117,
+ * csrc/dimq_conv2d_lut.cu:90-186), computed as sum_k (s*C[w_idx]) * (a_idx - z) on the tcgen05
+ * weight-only kernel: the activation codes are the reference's exactly, the scaled codewords go in as
+ * a hi + lo pair of bf16 values (about 2^-17 relative), accumulation is fp32.  The result is in the
+ * tolerance class of the weight-only ops (max-abs 1e-2, relative L2 1e-3), not bit-equal to the table
+ * lookup; dimq_linear_lut / dimq_conv2d_lut stay the exact path.
+ *
+ * `workspace` is caller-owned device memory, 256-byte aligned, of at least
+ * dimq_a4_workspace_bytes(x_numel, conv_weight_numel) bytes (conv_weight_numel = 0 for the linear op);
+ * it holds the centred activation codes (bf16), the 16 scaled codewords and, for the convolution,
+ * the indices re-ordered to [OC][KH][KW][ICg].  DIMQ_ERR_SCRATCH_TOO_SMALL if it is smaller,
+ * DIMQ_ERR_UNSUPPORTED where the tensor-core kernel does not apply (linear: K a multiple of 64;
+ * convolution: channels_last x and y, groups 1, in_channels a multiple of 64, stride 1 or 2). */
+DIMQ_API int dimq_a4_workspace_bytes(int64_t x_numel, int64_t conv_weight_numel, int64_t* bytes);
+DIMQ_API int dimq_linear_lut_tc(const void* x, int x_dtype, const uint8_t* packed_w, const void* codebook,
+                                int cb_dtype, float act_scale, int act_zp, const void* bias, int bias_dtype,
+                                float* y, int64_t M, int64_t N, int64_t K, void* workspace,
+                                int64_t workspace_bytes, void* stream);
+DIMQ_API int dimq_conv2d_lut_tc(const void* x, int x_dtype, const uint8_t* packed_w, const void* codebook,
+                                int cb_dtype, float act_scale, int act_zp, const void* bias, int bias_dtype,
+                                float* y, const dimq_conv_geom* geom, void* workspace, int64_t workspace_bytes,
+                                void* stream);
 
 /* ---- dense helper of the whole-model harness --------------------------- */
 

@@ -130,6 +130,82 @@ def test_conv2d_lut_matches_c_oracle(ops, dtype):
     np.testing.assert_allclose(got.cpu().numpy(), want, rtol=1e-5, atol=2e-5)
 
 
+# ---- W4A4 on the tensor cores (large problems) -------------------------------------
+# Same op, computed as sum (s*C[w]) * (a - z) with the scaled codewords rounded to a hi + lo bf16 pair:
+# checked against the exact table-lookup oracle at the weight-only tolerance, and observed far inside it.
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m,k,n", [(1024, 768, 384), (777, 128, 130)])
+def test_linear_lut_tensor_core_path(ops, m, k, n, dtype):
+    from dimq_b200 import _lib
+
+    assert m >= ops.A4_TC_MIN_ROWS
+    rng = np.random.default_rng(m + k)
+    x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32) * 1.5).to(dtype)
+    widx = rng.integers(0, 16, size=(n, k), dtype=np.uint8)
+    packed = o.pack_u4(widx)
+    cb = np.sort(rng.standard_normal(16).astype(np.float32) * 0.1)
+    bias = rng.standard_normal(n).astype(np.float32)
+    want = c_oracle.linear_lut_a4(x.float().numpy(), packed, cb, 0.25, 6, n, k, bias)
+    before = _lib.LAUNCH_COUNT[0]
+    got = ops.dimq_linear_lut(x.cuda(), _cuda(packed), _cuda(cb), 0.25, 6, _cuda(bias), n, k)
+    assert _lib.LAUNCH_COUNT[0] - before == 2, "expected the quantiser + tensor-core GEMM pair"
+    assert got.dtype == torch.float32
+    max_abs, rel = o.parity_metrics(got.cpu().numpy(), want)
+    assert max_abs <= 1e-3 and rel <= 1e-4, (max_abs, rel)
+    assert ops.last_device_status() == 0
+
+
+@pytest.mark.parametrize("stride,pad,ksize", [(1, 1, 3), (2, 1, 3), (2, 0, 1)])
+def test_conv2d_lut_tensor_core_path(ops, stride, pad, ksize):
+    from dimq_b200 import _lib
+
+    rng = np.random.default_rng(5 + stride + ksize)
+    x = torch.from_numpy(rng.standard_normal((4, 64, 28, 28)).astype(np.float32)).to(torch.float16)
+    widx = rng.integers(0, 16, size=(96, 64, ksize, ksize), dtype=np.uint8)
+    packed = o.pack_u4(widx)
+    cb = np.sort(rng.standard_normal(16).astype(np.float32) * 0.2)
+    bias = rng.standard_normal(96).astype(np.float32)
+    kw = dict(stride=(stride, stride), padding=(pad, pad), dilation=(1, 1), groups=1)
+    want = c_oracle.conv2d_lut_a4(x.float().numpy(), packed, cb, 0.3, 5, widx.shape, bias, **kw)
+    x_cl = x.cuda().contiguous(memory_format=torch.channels_last)
+    before = _lib.LAUNCH_COUNT[0]
+    got = ops.dimq_conv2d_lut(x_cl, _cuda(packed), _cuda(cb), 0.3, 5, _cuda(bias), widx.shape, kw["stride"],
+                              kw["padding"], kw["dilation"], 1)
+    assert _lib.LAUNCH_COUNT[0] - before == 3, "expected re-order + quantiser + tensor-core convolution"
+    assert got.is_contiguous(memory_format=torch.channels_last)
+    max_abs, rel = o.parity_metrics(got.cpu().numpy(), want)
+    assert max_abs <= 1e-3 and rel <= 1e-4, (max_abs, rel)
+    # NCHW-contiguous input keeps the exact direct kernel
+    exact = ops.dimq_conv2d_lut(x.cuda(), _cuda(packed), _cuda(cb), 0.3, 5, _cuda(bias), widx.shape, kw["stride"],
+                                kw["padding"], kw["dilation"], 1)
+    np.testing.assert_allclose(exact.cpu().numpy(), want, rtol=1e-5, atol=1e-4)
+    assert ops.last_device_status() == 0
+
+
+def test_a4_tensor_core_workspace_checks(ops):
+    import ctypes as C
+
+    from dimq_b200 import _lib
+
+    need = C.c_int64(0)
+    assert _lib.lib().dimq_a4_workspace_bytes(C.c_int64(1024 * 64), C.c_int64(0), C.byref(need)) == 0
+    assert need.value == 256 + 1024 * 64 * 2
+    x = torch.zeros(1024, 64, device="cuda")
+    pw = torch.zeros(64 * 64 // 2, dtype=torch.uint8, device="cuda")
+    cb = torch.linspace(-1, 1, 16, device="cuda")
+    y = torch.empty(1024, 64, device="cuda")
+    ws = torch.empty(need.value, dtype=torch.uint8, device="cuda")
+    args = lambda nbytes, k=64: (_lib.ptr(x), 0, _lib.ptr(pw), _lib.ptr(cb), 0, C.c_float(0.1), 8, None, 0, _lib.ptr(y),
+                                 C.c_int64(1024), C.c_int64(64), C.c_int64(k), _lib.ptr(ws), C.c_int64(nbytes), None)
+    assert _lib.lib().dimq_linear_lut_tc(*args(need.value - 1)) == -12
+    assert _lib.lib().dimq_linear_lut_tc(*args(need.value, 32)) == -7  # K not a multiple of 64: nothing launched
+    assert _lib.lib().dimq_linear_lut_tc(*args(need.value)) == 0
+    torch.cuda.synchronize()
+    # zero activations quantise to code 8 = the zero point: every product is zero
+    assert float(y.abs().max()) == 0.0
+
+
 # ---- weight-only GEMM --------------------------------------------------------------
 
 def test_linear_wq_golden(ops, golden):
