@@ -14,6 +14,10 @@ bool stream_supported(const dimq_wq_weight* w, int64_t M, int64_t N, int64_t K);
 int launch_linear_wq_stream(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
                             const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K,
                             int epilogue, cudaStream_t st);
+bool mma_stream_supported(const void* x, int x_dtype, const dimq_wq_weight* w, int64_t M, int64_t N, int64_t K);
+int launch_linear_wq_mma_stream(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias,
+                                int bias_dtype, const void* residual, void* y, int y_dtype, int64_t M, int64_t N,
+                                int64_t K, int epilogue, cudaStream_t st);
 bool tc_supported(const void* x, int x_dtype, const dimq_wq_weight* w, int64_t M, int64_t N, int64_t K);
 int launch_linear_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
                         const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K, int epilogue,
@@ -68,8 +72,9 @@ extern "C" int dimq_linear_wq(const void* x, int x_dtype, const dimq_wq_weight* 
   if (x == nullptr || y == nullptr) return DIMQ_ERR_NULL_POINTER;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (algo == DIMQ_ALGO_AUTO) {
-    if (stream_supported(w, M, N, K)) algo = DIMQ_ALGO_STREAM;
-    else if (M > 8 && tc_supported(x, x_dtype, w, M, N, K)) algo = DIMQ_ALGO_TCGEN05;
+    if (mma_stream_supported(x, x_dtype, w, M, N, K)) algo = DIMQ_ALGO_MMA_STREAM;
+    else if (stream_supported(w, M, N, K)) algo = DIMQ_ALGO_STREAM;
+    else if (tc_supported(x, x_dtype, w, M, N, K)) algo = DIMQ_ALGO_TCGEN05;
     else algo = DIMQ_ALGO_GENERIC;
   }
   switch (algo) {
@@ -77,6 +82,8 @@ extern "C" int dimq_linear_wq(const void* x, int x_dtype, const dimq_wq_weight* 
       return launch_linear_wq_generic(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, st);
     case DIMQ_ALGO_STREAM:
       return launch_linear_wq_stream(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, st);
+    case DIMQ_ALGO_MMA_STREAM:
+      return launch_linear_wq_mma_stream(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, st);
     case DIMQ_ALGO_TCGEN05:
       return launch_linear_wq_tc(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, 0, st);
     case DIMQ_ALGO_TCGEN05 + 100:  // codewords rounded to the activations' 16-bit format, never split (measurement only)

@@ -51,8 +51,10 @@ extern "C" {
 /* kernel selection for the weight-only ops */
 #define DIMQ_ALGO_AUTO 0
 #define DIMQ_ALGO_GENERIC 1   /* exact fp32 SIMT kernel, any shape */
-#define DIMQ_ALGO_STREAM 2    /* small-M index-streaming kernel (HBM-bound regime) */
+#define DIMQ_ALGO_STREAM 2    /* small-M index-streaming kernel, fp32 arithmetic (any activation type, M <= 8) */
 #define DIMQ_ALGO_TCGEN05 3   /* TMA + in-pipeline dequantisation + tcgen05 MMA (tensor-core regime) */
+#define DIMQ_ALGO_MMA_STREAM 4 /* small-M index-streaming kernel for 16-bit activations (M <= 32): pair-table
+                                  lookups feeding warp-level MMAs; the HBM-bound regime */
 
 /* fused epilogues of the weight-only ops */
 #define DIMQ_EPI_NONE 0

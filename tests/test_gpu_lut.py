@@ -260,6 +260,69 @@ def test_linear_wq_stream_small_m(ops, bits, m):
     np.testing.assert_allclose(got.cpu().numpy(), want, rtol=2e-4, atol=2e-4)
 
 
+# ---- small-M index-streaming kernel for 16-bit activations (pair tables + warp MMA) ---------
+
+MS_MODES = [(torch.bfloat16, "bf16", torch.bfloat16), (torch.float16, np.float16, torch.float16),
+            (torch.float16, np.float32, torch.float32)]
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("bits", [2, 3, 4])
+@pytest.mark.parametrize("m,k,n,grp", [(1, 128, 16, None), (3, 768, 100, None), (8, 1024, 520, 128), (9, 1024, 4096, None),
+                                       (16, 4096, 1024, None), (17, 256, 33, 16), (32, 2048, 300, 32),
+                                       (5, 8192, 64, None), (2, 384, 2304, 128)])
+def test_linear_wq_mma_stream(ops, bits, m, k, n, grp, mode):
+    x_dtype, cb_np, cb_torch = MS_MODES[mode]
+    case = make_weight(n, k, bits, seed=bits * 7 + m, group_rows=grp, cb_dtype=cb_np)
+    rng = np.random.default_rng(m + k + n)
+    x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(x_dtype)
+    bias = rng.standard_normal(n).astype(np.float32)
+    # fp16 operands: the codewords the kernel multiplies are the fp16 roundings of the codebook
+    cbs = case["codebooks"].astype(np.float16).astype(np.float32) if x_dtype == torch.float16 else case["codebooks"]
+    want = o.linear_wq(x.float().numpy(), case["packed"], cbs, bits, n, k, bias, case["group_rows"])
+    got = ops.dimq_linear_wq(x.cuda(), _cuda(case["packed"]), _cuda(case["codebooks"], cb_torch), _cuda(bias), n, k,
+                             bits=bits, group_rows=grp, algo="mma_stream")
+    _assert_close(got, want, f"mma_stream bits={bits} {m}x{k}x{n} mode={mode}")
+    np.testing.assert_allclose(got.cpu().numpy(), want, rtol=2e-4, atol=2e-4)
+
+
+@pytest.mark.parametrize("y_dtype", [torch.float32, torch.bfloat16])
+def test_linear_wq_mma_stream_epilogues(ops, y_dtype):
+    m, k, n = 12, 512, 200
+    case = make_weight(n, k, 4, seed=3, cb_dtype="bf16")
+    rng = np.random.default_rng(8)
+    x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(torch.bfloat16)
+    bias = rng.standard_normal(n).astype(np.float32)
+    res = torch.from_numpy(rng.standard_normal((m, n)).astype(np.float32)).to(y_dtype)
+    lin = o.linear_wq(x.float().numpy(), case["packed"], case["codebooks"], 4, n, k, bias)
+    for epi, fn in (("relu", lambda v: np.maximum(v, 0)), ("gelu", None), (None, lambda v: v)):
+        want = torch.nn.functional.gelu(torch.from_numpy(lin)).numpy() if fn is None else fn(lin)
+        want = want + res.float().numpy()
+        got = ops.dimq_linear_wq(x.cuda(), _cuda(case["packed"]), _cuda(case["codebooks"], torch.bfloat16), _cuda(bias),
+                                 n, k, bits=4, out_dtype=y_dtype, epilogue=epi, residual=res.cuda(), algo="mma_stream")
+        assert got.dtype == y_dtype
+        max_abs, rel = o.parity_metrics(got.float().cpu().numpy(), want)
+        assert max_abs <= (3e-2 if y_dtype == torch.bfloat16 else 1e-3) and rel <= (5e-3 if y_dtype == torch.bfloat16 else 1e-4), (epi, max_abs, rel)
+    want = np.maximum(lin + res.float().numpy(), 0)
+    got = ops.dimq_linear_wq(x.cuda(), _cuda(case["packed"]), _cuda(case["codebooks"], torch.bfloat16), _cuda(bias), n, k,
+                             bits=4, out_dtype=y_dtype, epilogue="add_relu", residual=res.cuda(), algo="mma_stream")
+    max_abs, rel = o.parity_metrics(got.float().cpu().numpy(), want)
+    assert rel <= (5e-3 if y_dtype == torch.bfloat16 else 1e-4), (max_abs, rel)
+
+
+def test_linear_wq_mma_stream_rejects_what_it_cannot_take(ops):
+    case = make_weight(64, 256, 4, seed=1)
+    x = torch.zeros(4, 256, device="cuda")
+    pw, cb = _cuda(case["packed"]), _cuda(case["codebooks"])
+    with pytest.raises(RuntimeError):  # fp32 activations
+        ops.dimq_linear_wq(x, pw, cb, None, 64, 256, bits=4, algo="mma_stream")
+    with pytest.raises(RuntimeError):  # bf16 activations with an fp32 codebook would need a second term
+        ops.dimq_linear_wq(x.to(torch.bfloat16), pw, cb, None, 64, 256, bits=4, algo="mma_stream")
+    with pytest.raises(RuntimeError):  # more than 32 rows
+        ops.dimq_linear_wq(torch.zeros(33, 256, device="cuda", dtype=torch.float16), pw, cb, None, 64, 256, bits=4,
+                           algo="mma_stream")
+
+
 TC_SHAPES = [(192, 64, 128), (200, 128, 130), (577, 768, 384), (64, 1024, 256), (16, 256, 128)]
 
 
