@@ -27,6 +27,7 @@ int launch_conv2d_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, con
                         const void* residual, void* y, int y_dtype, const dimq_conv_geom* g, int epilogue,
                         cudaStream_t st);
 int read_device_status(uint32_t* status);
+int read_ms_status(uint32_t* status);
 }  // namespace dimq
 
 using namespace dimq;
@@ -56,7 +57,13 @@ extern "C" const char* dimq_status_string(int status) {
 
 extern "C" int dimq_last_device_status(uint32_t* status) {
   if (status == nullptr) return DIMQ_ERR_NULL_POINTER;
-  return read_device_status(status);
+  uint32_t tc = 0, ms = 0;
+  int rc = read_device_status(&tc);
+  if (rc != DIMQ_OK) return rc;
+  rc = read_ms_status(&ms);
+  if (rc != DIMQ_OK) return rc;
+  *status = tc | ms;
+  return DIMQ_OK;
 }
 
 extern "C" int dimq_linear_wq(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias,

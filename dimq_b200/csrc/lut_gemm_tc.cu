@@ -881,6 +881,24 @@ size_t table_bytes(int bits, int64_t groups, bool pair, bool split) {
 
 }  // namespace
 
+// Tiled tensor map over plain bytes (elem_bytes 1) or 16-bit elements (2), no swizzle, zero fill;
+// `out` points at a CUtensorMap.  For kernels outside this file that stage tiles with TMA.
+int encode_plain_tensor_map(void* out, int elem_bytes, int rank, const void* base, const uint64_t* dims,
+                            const uint64_t* strides_bytes, const uint32_t* box) {
+  EncodeTiledFn encode = get_encode_tiled();
+  if (encode == nullptr || rank < 1 || rank > 5) return DIMQ_ERR_DRIVER;
+  cuuint64_t d[5], st[4];
+  cuuint32_t b[5], es[5];
+  for (int i = 0; i < rank; ++i) { d[i] = dims[i]; b[i] = box[i]; es[i] = 1; }
+  for (int i = 0; i + 1 < rank; ++i) st[i] = strides_bytes[i];
+  const CUresult r = encode(static_cast<CUtensorMap*>(out),
+                            elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16, rank,
+                            const_cast<void*>(base), d, st, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? DIMQ_OK : DIMQ_ERR_DRIVER;
+}
+
 bool tc_supported(const void* x, int x_dtype, const dimq_wq_weight* w, int64_t M, int64_t N, int64_t K) {
   if (x_dtype != DIMQ_BF16 && x_dtype != DIMQ_F16) return false;
   if (M < 1 || N < 1 || K < kBlockK || K % kBlockK != 0) return false;

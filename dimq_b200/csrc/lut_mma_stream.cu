@@ -1,15 +1,18 @@
 // Small-M weight-only LUT GEMM for 16-bit activations (M <= 32): the index-streaming regime.
 //
-// The packed indices are read from HBM exactly once with coalesced vector loads and never touch
-// shared memory; the work per weight is one table lookup for every TWO weights (four at 2 bits) and
+// The packed indices are read from HBM exactly once: TMA box copies (16 rows x 128 k per unit) land in
+// a per-warp ring in shared memory, several units ahead of the arithmetic.  (A first version loaded
+// the indices with per-lane vector loads into a register ring; with the shared-memory carve-out this
+// kernel needs, the few loads the L1 could keep in flight capped it near 1.5 TB/s whatever the
+// arithmetic did.  Bulk copies do not pass through L1.)  The work per weight is one table lookup for every TWO weights (four at 2 bits) and
 // a share of a warp-level mma.sync, which stands in for the M fused multiply-adds per weight that a
 // SIMT kernel cannot issue fast enough beyond M = 2.  The tensor pipe is nowhere near busy here: the
 // kernel is bound by HBM and by shared-memory lookups, so the warp-level MMA is the right tool and
 // the tcgen05 path (which would need the weights staged as operands) is not.
 //
-// Work unit: 16 output rows x 128 k.  Lane (g = lane / 4, t = lane % 4) of a warp loads, for rows g
+// Work unit: 16 output rows x 128 k.  Lane (g = lane / 4, t = lane % 4) of a warp takes, for rows g
 // and g + 8 of the block, the 32 consecutive indices k = 32 t .. 32 t + 31 of the chunk (16 B at
-// 4 bits, 12 B at 3 bits, 8 B at 2 bits; a quad covers a contiguous span of the row).  Because a dot
+// 4 bits, 12 B at 3 bits, 8 B at 2 bits) out of the unit's ring slot.  Because a dot
 // product does not care about the order of k, MMA step s (of 8) takes from every lane its indices
 // 4 s .. 4 s + 3: the A fragment registers a0/a2 (row g) and a1/a3 (row g + 8) each hold two
 // k-adjacent codewords, which is exactly one entry of a PAIR table indexed by the two packed indices
@@ -22,19 +25,40 @@
 // A CTA (16 warps) works on G row blocks at a time and deals their (block, chunk) units round-robin
 // to its warps; partial sums meet in a double-buffered shared-memory accumulator with one
 // __syncthreads per iteration, after which bias / epilogue / residual are applied and y is stored.
-// Index loads run PF units ahead of the arithmetic in a register ring.
+#include <cuda.h>
+
 #include <cstdlib>
 #include <type_traits>
 
 #include "common.cuh"
 
 namespace dimq {
+int encode_plain_tensor_map(void* out, int elem_bytes, int rank, const void* base, const uint64_t* dims,
+                            const uint64_t* strides_bytes, const uint32_t* box);
+
 namespace {
 
 constexpr int kWarps = 16;
 constexpr int kThreads = kWarps * 32;
 constexpr int kChunkK = 128;
-constexpr size_t kSmemLimit = 220 * 1024;
+constexpr uint32_t kSmemWindow = 227 * 1024;  // dynamic shared memory a CTA may ask for
+constexpr uint32_t kLowStart = 1024;          // the dynamic window starts at or below this shared address
+
+// Absolute shared-memory addresses.  The lookup table sits on a boundary of its own size so that a
+// lookup address is (index bits, masked in place) OR (table base | lane offset): no add.
+//   [start, table)    codewords of the current group, mbarriers, the first activation rows
+//   [table, +size)    pair table, one copy per lane
+//   [table + size, )  the other activation rows, per-warp partial sums, per-warp index rings
+template <int BITS>
+struct Cfg {
+  static constexpr int kWords = BITS;  // 32 indices per lane, row and unit
+  static constexpr uint32_t kUnitBytes = 16 * kChunkK * BITS / 8;  // one ring slot: [16 rows][128 k]
+  static constexpr int kTableEntries = BITS == 3 ? 64 : 256;
+  static constexpr int kEntryWords = BITS == 2 ? 2 : 1;
+  static constexpr uint32_t kTableBytes = kTableEntries * 32 * 4 * kEntryWords;
+  static constexpr uint32_t kTableAddr = BITS == 2 ? 65536u : 32768u;
+  static constexpr uint32_t kXAddr = kTableAddr + kTableBytes;
+};
 
 struct MsParams {
   const void* x;
@@ -51,23 +75,24 @@ struct MsParams {
   int64_t N, K;
   int epilogue;
   int G;         // row blocks a CTA works on at a time
+  int wpr;       // warps per row block
+  int cpw;       // consecutive k chunks per warp
   int chunks;    // K / 128
-  int units;     // G * chunks
-  int upw;       // units per warp and iteration
   int total_it;  // ceil(ceil(N / 16) / G)
   int ipc;       // iterations per CTA
   int xs;        // activation row stride in shared memory, elements
-  int dbg;       // measurement only: 1 skip the MMAs, 2 skip the table lookups, 4 skip the activation reads
+  int rows_low;  // activation rows 0 .. rows_low-1 live below the table (at x_low), the rest above it
+  uint32_t x_low;  // shared address of row 0 when rows_low > 0
+  uint32_t x_high; // shared address of row rows_low
+  uint32_t zero;   // shared address of 256 zero bytes (the activations of MMA columns beyond M)
+  int pf;          // ring slots per warp
+  uint32_t part;   // shared address of the partial sums: [2][warp][16 rows][MR]
+  uint32_t ring;   // shared address of the rings: [warp][pf][unit]
+  uint32_t bars;   // shared address of the slots' mbarriers: [warp][pf]
+  uint32_t* status;  // device status word (set when the shared-memory window is not where it is expected)
 };
 
-template <int BITS>
-struct Cfg {
-  static constexpr int kWords = BITS;                                   // 32 indices per lane, row and unit
-  static constexpr int kPrefetch = BITS == 4 ? 6 : (BITS == 3 ? 8 : 12);  // units in flight per warp (48 registers)
-  static constexpr int kTableEntries = BITS == 3 ? 64 : 256;
-  static constexpr int kEntryWords = BITS == 2 ? 2 : 1;
-  static constexpr int kTableBytes = kTableEntries * 32 * 4 * kEntryWords;
-};
+static __device__ uint32_t g_ms_status;
 
 template <bool F16>
 __device__ __forceinline__ uint32_t to_operand(float c) {
@@ -79,36 +104,15 @@ template <bool F16>
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                           uint32_t b0, uint32_t b1) {
   if constexpr (F16) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
   } else {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
   }
 }
-
-// Position of a warp in its sequence of units: iteration `it` (global numbering) and the i-th unit of
-// the warp inside it.  `u = warp + 16 i` is the unit, `slot = u / chunks` the row block of the
-// iteration it belongs to, `chunk = u % chunks` its k chunk.
-struct Cursor {
-  int it, i, slot, chunk;
-  __device__ __forceinline__ void reset(int warp, int chunks) {
-    i = 0;
-    slot = warp / chunks;
-    chunk = warp - slot * chunks;
-  }
-  __device__ __forceinline__ void advance(int upw, int warp, int chunks) {
-    if (++i == upw) {
-      ++it;
-      reset(warp, chunks);
-    } else {
-      chunk += kWarps;
-      while (chunk >= chunks) { chunk -= chunks; ++slot; }
-    }
-  }
-};
 
 template <int BITS>
 __device__ __forceinline__ void load_row_words(const uint8_t* p, uint32_t (&w)[BITS]) {
@@ -133,9 +137,71 @@ __device__ __forceinline__ void static_for(F&& f) {
   }
 }
 
+constexpr uint32_t kPollLimit = 1u << 15;  // bounded wait: polls of up to 20 us each, then give up
+constexpr uint32_t kPollHintNs = 20000u;
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(kPollHintNs)
+      : "memory");
+  return ok != 0;
+}
+// TMA box copy of a [16 rows][chunk bytes] tile of the packed index matrix into this CTA's shared memory
+__device__ __forceinline__ void tma_load_unit(uint32_t dst, const CUtensorMap* map, uint32_t bar, int byte0, int row0) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(byte0), "r"(row0)
+      : "memory");
+}
+
+// Table lookups: their addresses depend on index words read after the slot's wait, so the compiler
+// cannot move them ahead of the data they need, and the table only changes between two barriers that
+// no lookup can cross for the same reason.  Not volatile: the scheduler is free to issue the lookups of
+// later MMA steps early.
+__device__ __forceinline__ uint32_t lookup_u32(uint32_t addr) {
+  uint32_t v;
+  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint2 lookup_u64(uint32_t addr) {
+  uint2 v;
+  asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
 __device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
   uint32_t v;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint4 lds_u128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
 }
 __device__ __forceinline__ uint2 lds_u64(uint32_t addr) {
@@ -145,17 +211,26 @@ __device__ __forceinline__ uint2 lds_u64(uint32_t addr) {
 }
 
 template <int BITS, int NB, bool F16>
-__global__ void __launch_bounds__(kThreads, 1) linear_wq_mma_stream_kernel(const MsParams p) {
+__global__ void __launch_bounds__(kThreads, 1)
+linear_wq_mma_stream_kernel(const __grid_constant__ CUtensorMap wmap, const MsParams p) {
   using C = Cfg<BITS>;
   constexpr int W = C::kWords;
-  constexpr int PF = C::kPrefetch;
-  constexpr int MR = 8 * NB;  // activation rows held (M rounded up)
+  constexpr int MR = 8 * NB;  // columns of the MMA tiles (activation rows, M rounded up)
   extern __shared__ __align__(16) unsigned char smem[];
-  uint32_t* table = reinterpret_cast<uint32_t*>(smem);
-  uint16_t* x_s = reinterpret_cast<uint16_t*>(smem + C::kTableBytes);
-  const uint32_t x_bytes = (static_cast<uint32_t>(MR) * p.xs * 2 + 15) & ~15u;
-  float* slots = reinterpret_cast<float*>(smem + C::kTableBytes + x_bytes);  // [2][G][MR][16]
-  float* cb_s = slots + 2 * p.G * MR * 16;                                     // codewords of the current group
+  const uint32_t s0 = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  if (s0 > kLowStart) {  // the fixed layout below would not fit the window: report, do nothing
+    if (threadIdx.x == 0) atomicOr(p.status, 0x80000901u);
+    return;
+  }
+  unsigned char* const abs0 = smem - s0;  // generic address of shared address 0
+  float* cb_s = reinterpret_cast<float*>(abs0 + kLowStart);                  // codewords of the current group
+  float* part = reinterpret_cast<float*>(abs0 + p.part);                     // [2][warp][16 rows][MR]
+  uint32_t* table = reinterpret_cast<uint32_t*>(abs0 + C::kTableAddr);
+  // shared address of activation row m
+  auto x_row_addr = [&](int m) -> uint32_t {
+    return m < p.rows_low ? p.x_low + static_cast<uint32_t>(m) * p.xs * 2
+                          : p.x_high + static_cast<uint32_t>(m - p.rows_low) * p.xs * 2;
+  };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -164,23 +239,63 @@ __global__ void __launch_bounds__(kThreads, 1) linear_wq_mma_stream_kernel(const
   const int my_iters = it_end - it_begin;
   if (my_iters <= 0) return;
 
-  // ---- one-time staging: activations (zero rows beyond M), accumulator slots ----
+  // ---- this warp's share: row block `slot` of every iteration, k chunks [c0, c0 + nch) ----
+  const int slot = warp / p.wpr;
+  const int c0 = (warp - slot * p.wpr) * p.cpw;
+  const int nch = slot < p.G ? max(0, min(p.cpw, p.chunks - c0)) : 0;
+
+
+  // ---- the warp's ring: p.pf slots of one unit each, one mbarrier per slot; lane 0 issues the copies ----
+  constexpr int kChunkBytes = kChunkK * BITS / 8;  // per row
+  const uint32_t ring_w = p.ring + warp * p.pf * C::kUnitBytes;
+  const uint32_t bars_w = p.bars + warp * p.pf * 8;
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(abs0 + p.bars + kWarps * p.pf * 8);
+  const int total = my_iters * nch;
+  int ld_seq = 0, ld_j = 0, ld_slot = 0;
+  int ld_row0 = (it_begin * p.G + slot) * 16;
+  int pr_j = 0, pr_it = it_begin, pr_slot = 0;
+  uint32_t pr_phase = 0;
+  bool seq_live = true;  // false once a wait of this warp gave up
+
+  // issue the copy of the next unit of the sequence (lane 0 only; the slot must be free)
+  auto issue_unit = [&]() {
+    const uint32_t bar = bars_w + ld_slot * 8;
+    mbar_expect_tx(bar, C::kUnitBytes);
+    tma_load_unit(ring_w + ld_slot * C::kUnitBytes, &wmap, bar, (c0 + ld_j) * kChunkBytes, ld_row0);
+    ++ld_seq;
+    if (++ld_slot == p.pf) ld_slot = 0;
+    if (++ld_j == nch) {
+      ld_j = 0;
+      ld_row0 += p.G * 16;
+    }
+  };
+  if (nch > 0) {
+    if (lane == 0) {
+      for (int q = 0; q < p.pf; ++q) mbar_init(bars_w + q * 8, 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      // the first copies fly while the activations and the table are being set up
+      for (int q = 0; q < p.pf && ld_seq < total; ++q) issue_unit();
+    }
+    __syncwarp();
+  }
+  if (tid == 0) *abort_flag = 0u;
+
+  // ---- one-time staging: activations (asynchronous copies), a chunk of zeros ----
   {
-    const int vec_per_row = static_cast<int>(p.K >> 2);  // 4 elements = 8 bytes
-    const uint2* xg = static_cast<const uint2*>(p.x);
-    // group v = k / 4 of a row is [chunk | t (2 bits) | s (3 bits)]; it is stored at [chunk | s | t], so
-    // that MMA step s finds the four lanes of a quad in adjacent 8-byte slots
-    for (int m = 0; m < MR; ++m) {
-      uint2* dst = reinterpret_cast<uint2*>(x_s + static_cast<size_t>(m) * p.xs);
-      if (m < p.M) {
-        const uint2* src = xg + static_cast<int64_t>(m) * vec_per_row;
-        for (int v = tid; v < vec_per_row; v += kThreads)
-          dst[(v & ~31) | ((v & 7) << 2) | ((v >> 3) & 3)] = __ldg(src + v);
-      } else {
-        for (int v = tid; v < vec_per_row; v += kThreads) dst[v] = make_uint2(0u, 0u);
+    // 16-byte group v = k / 8 of a row is [chunk | t (2 bits) | s / 2 (2 bits)]; it is stored at
+    // [chunk | s / 2 | t], so that a pair of MMA steps finds the four lanes of a quad in adjacent slots
+    const int vec_per_row = static_cast<int>(p.K >> 3);  // 8 elements = 16 bytes
+    const uint4* xg = static_cast<const uint4*>(p.x);
+    for (int m = 0; m < p.M; ++m) {
+      const uint32_t row = x_row_addr(m);
+      const uint4* src = xg + static_cast<int64_t>(m) * vec_per_row;
+      for (int v = tid; v < vec_per_row; v += kThreads) {
+        const int dv = (v & ~15) | ((v & 3) << 2) | ((v >> 2) & 3);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(row + dv * 16), "l"(src + v) : "memory");
       }
     }
-    for (int idx = tid; idx < 2 * p.G * MR * 16; idx += kThreads) slots[idx] = 0.0f;
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    if (tid < 16) reinterpret_cast<uint4*>(abs0 + p.zero)[tid] = make_uint4(0u, 0u, 0u, 0u);
   }
 
   // pair table of one codebook group, one copy per lane: word (entry * 32 + lane)
@@ -205,84 +320,141 @@ __global__ void __launch_bounds__(kThreads, 1) linear_wq_mma_stream_kernel(const
   };
   int64_t cur_group = group_of_iteration(it_begin);
   build_table(cur_group);
+  asm volatile("cp.async.wait_all;" ::: "memory");
   __syncthreads();
 
-  const int64_t row_bytes = p.K * BITS / 8;
-  constexpr int kLaneBytes = 4 * BITS;             // 32 indices
-  constexpr int kChunkBytes = kChunkK * BITS / 8;  // per row
-  // shared-window addresses (32-bit arithmetic from here on)
-  const uint32_t tbl_addr = static_cast<uint32_t>(__cvta_generic_to_shared(table)) + lane * (4 * C::kEntryWords);
-  const uint32_t x_addr = static_cast<uint32_t>(__cvta_generic_to_shared(x_s)) + g * p.xs * 2 + 8 * t;
-  const uint32_t x_nb_stride = 8u * p.xs * 2u;
-  const uint8_t* lane_base = p.packed + static_cast<int64_t>(g) * row_bytes + t * kLaneBytes;
-  const int64_t half_stride = 8 * row_bytes;
-
-  uint32_t ring[PF][2][W];
-
-  // the unit at cursor (it, i): u = warp + 16 i -> (slot, chunk); loads rows g and g + 8
-  auto load_unit = [&](const Cursor& c, uint32_t (&buf)[2][W]) {
-    const bool ok = c.it < it_end && c.slot < p.G;
-    const int slot = ok ? c.slot : 0, chunk = ok ? c.chunk : 0;
-    const int64_t r0 = (static_cast<int64_t>(c.it) * p.G + slot) * 16;
-    const uint8_t* src = lane_base + r0 * row_bytes + chunk * kChunkBytes;
+  // two accumulator sets (even / odd MMA steps) halve the dependent chain through the MMAs
+  float acc[2][NB][4];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      if (ok && r0 + g + 8 * h < p.N) {
-        load_row_words<BITS>(src + h * half_stride, buf[h]);
-      } else {
+  for (int e = 0; e < 2; ++e)
 #pragma unroll
-        for (int j = 0; j < W; ++j) buf[h][j] = 0u;
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[e][nb][j] = 0.0f;
+
+  // The warp's partial sums of its row block go to its own buffer (no atomics: with all warps of a row
+  // block adding into the same words at the same moment, shared-memory float adds serialise badly).
+  auto flush = [&](int it) {
+    float* s = part + (static_cast<size_t>(it & 1) * kWarps + warp) * (16 * MR);
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+      const int m = nb * 8 + 2 * t;
+      *reinterpret_cast<float2*>(s + g * MR + m) =
+          make_float2(acc[0][nb][0] + acc[1][nb][0], acc[0][nb][1] + acc[1][nb][1]);
+      *reinterpret_cast<float2*>(s + (g + 8) * MR + m) =
+          make_float2(acc[0][nb][2] + acc[1][nb][2], acc[0][nb][3] + acc[1][nb][3]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[0][nb][j] = acc[1][nb][j] = 0.0f;
+    }
+  };
+
+  // after the iteration's __syncthreads: sum the partials of each row block's warps, then bias,
+  // epilogue, residual, store
+  auto write_iteration = [&](int it) {
+    const float* base = part + static_cast<size_t>(it & 1) * kWarps * (16 * MR);
+    const int total_out = p.G * MR * 16;
+    for (int idx = tid; idx < total_out; idx += kThreads) {
+      const int r = idx & 15;
+      const int m = (idx >> 4) % MR;
+      const int sl = idx / (MR * 16);
+      const float* src = base + static_cast<size_t>(sl) * p.wpr * (16 * MR) + r * MR + m;
+      float v = 0.0f;
+      for (int wi = 0; wi < p.wpr; ++wi) v += src[wi * (16 * MR)];
+      const int64_t n = (static_cast<int64_t>(it) * p.G + sl) * 16 + r;
+      if (m < p.M && n < p.N) {
+        const float vb = v + (p.bias != nullptr ? load_as_float(p.bias, p.bias_dtype, n) : 0.0f);
+        const int64_t o = static_cast<int64_t>(m) * p.N + n;
+        const float res = p.residual != nullptr ? load_as_float(p.residual, p.y_dtype, o) : 0.0f;
+        store_from_float(p.y, p.y_dtype, o, finish_value(vb, p.epilogue, p.residual != nullptr, res));
       }
     }
   };
 
-  float acc[NB][4];
-#pragma unroll
-  for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) acc[nb][j] = 0.0f;
-  int acc_slot = -1;
-
-  auto flush = [&](int it) {
-    float* s = slots + (static_cast<size_t>(it & 1) * p.G + acc_slot) * (MR * 16);
-#pragma unroll
-    for (int nb = 0; nb < NB; ++nb) {
-      const int m = nb * 8 + 2 * t;
-      atomicAdd(s + m * 16 + g, acc[nb][0]);
-      atomicAdd(s + (m + 1) * 16 + g, acc[nb][1]);
-      atomicAdd(s + m * 16 + g + 8, acc[nb][2]);
-      atomicAdd(s + (m + 1) * 16 + g + 8, acc[nb][3]);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) acc[nb][j] = 0.0f;
+  // every warp of the CTA passes here once per iteration, in the same order
+  auto end_iteration = [&](int it) {
+    __syncthreads();
+    write_iteration(it);
+    if (it + 1 < it_end) {
+      const int64_t ng = group_of_iteration(it + 1);
+      if (ng != cur_group) {  // uniform over the CTA: nobody reads the table between the barriers
+        cur_group = ng;
+        build_table(ng);
+        __syncthreads();
+      }
     }
-    acc_slot = -1;
+  };
+
+  if (nch == 0) {  // a warp without chunks only keeps the barriers and helps with the write-back
+    for (int it = it_begin; it < it_end; ++it) end_iteration(it);
+    return;
+  }
+
+  // lookup address = (index bits masked in place) | tbl: the table base has those bits clear
+  const uint32_t tbl = C::kTableAddr + lane * (4 * C::kEntryWords);
+  // B fragments: column n = g of MMA tile nb is activation row nb * 8 + g; columns beyond M read a
+  // chunk of zeros (and do not advance with the k chunk)
+  uint32_t xrow[NB], xstep[NB];
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) {
+    const int m = nb * 8 + g;
+    const bool live = m < p.M;
+    xrow[nb] = live ? x_row_addr(m) + 16 * t + c0 * (kChunkK * 2) : p.zero + 16 * t;
+    xstep[nb] = live ? kChunkK * 2 : 0;
+  }
+
+  // Wait (bounded) for the slot of the next unit, copy the lane's indices out, refill the slot.
+  // Returns false when the unit has no data (a wait gave up here or elsewhere in the CTA).
+  auto fetch_unit = [&](uint32_t (&buf)[2][W]) -> bool {
+    const uint32_t bar = bars_w + pr_slot * 8;
+    bool ok = seq_live && mbar_test_wait(bar, pr_phase);  // usually the copy landed long ago
+    if (!ok && seq_live) {
+      for (uint32_t poll = 0; poll < kPollLimit; ++poll) {
+        if (mbar_try_wait(bar, pr_phase)) { ok = true; break; }
+        if ((poll & 63u) == 63u && *abort_flag != 0u) break;
+      }
+      if (!ok) {  // give up: no more copies are issued by this warp, the units left are skipped
+        *abort_flag = 1u;
+        atomicOr(p.status, 0x80000902u);
+        seq_live = false;
+      }
+    }
+    const uint32_t src = ring_w + pr_slot * C::kUnitBytes + g * kChunkBytes + t * (4 * BITS);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t a = src + h * 8 * kChunkBytes;
+      if constexpr (BITS == 4) {
+        const uint4 q = lds_u128(a);
+        buf[h][0] = q.x; buf[h][1] = q.y; buf[h][2] = q.z; buf[h][3] = q.w;
+      } else if constexpr (BITS == 2) {
+        const uint2 q = lds_u64(a);
+        buf[h][0] = q.x; buf[h][1] = q.y;
+      } else {
+#pragma unroll
+        for (int j = 0; j < W; ++j) buf[h][j] = lds_u32(a + 4 * j);
+      }
+    }
+    __syncwarp();  // every lane has its words: the slot may be overwritten
+    if (lane == 0 && ok && ld_seq < total) issue_unit();
+    if (++pr_slot == p.pf) { pr_slot = 0; pr_phase ^= 1u; }
+    return ok;
   };
 
   // eight MMA steps over the 128 k of one unit
-  auto process = [&](const Cursor& c, const uint32_t (&buf)[2][W]) {
-    if (c.slot >= p.G) return;
-    const int slot = c.slot, chunk = c.chunk;
-    if (acc_slot >= 0 && acc_slot != slot) flush(c.it);
-    acc_slot = slot;
-    const uint32_t xb = x_addr + chunk * (kChunkK * 2);
+  auto process = [&](const uint32_t (&buf)[2][W]) {
+    uint4 bfrag[NB];
     static_for<0, 8>([&](auto sc) {
       constexpr int s = decltype(sc)::value;
       uint32_t a0, a1, a2, a3;
-      if (p.dbg & 2) {
-        a0 = buf[0][s % W]; a1 = buf[1][s % W]; a2 = a0 >> 3; a3 = a1 >> 5;
-      } else if constexpr (BITS == 4) {
-        // two bytes of each row: entry * 128 bytes, taken straight out of the word with a mask
-        constexpr int word = s / 2, sh = (2 * s % 4) * 8;
+      if constexpr (BITS == 4) {
+        // byte b of the word, times 128 bytes per entry: (w >> (8 b - 7)) & 0x7F80
+        constexpr int word = s / 2, b = 2 * s % 4;
         const uint32_t wg = buf[0][word], wh = buf[1][word];
-        // byte b at bit sh: (w >> sh & 0xFF) * 128 == (w << 7 >> sh) & 0x7F80 (for sh >= 8: w >> (sh - 7))
-        const uint32_t g0 = sh == 0 ? (wg << 7) & 0x7F80u : (wg >> (sh - 7)) & 0x7F80u;
-        const uint32_t g1 = (wg >> (sh + 1)) & 0x7F80u;
-        const uint32_t h0 = sh == 0 ? (wh << 7) & 0x7F80u : (wh >> (sh - 7)) & 0x7F80u;
-        const uint32_t h1 = (wh >> (sh + 1)) & 0x7F80u;
-        a0 = lds_u32(tbl_addr + g0);
-        a2 = lds_u32(tbl_addr + g1);
-        a1 = lds_u32(tbl_addr + h0);
-        a3 = lds_u32(tbl_addr + h1);
+        const uint32_t g0 = b == 0 ? (wg << 7) : (wg >> (8 * b - 7));
+        const uint32_t h0 = b == 0 ? (wh << 7) : (wh >> (8 * b - 7));
+        a0 = lookup_u32((g0 & 0x7F80u) | tbl);
+        a2 = lookup_u32(((wg >> (8 * b + 1)) & 0x7F80u) | tbl);
+        a1 = lookup_u32((h0 & 0x7F80u) | tbl);
+        a3 = lookup_u32(((wh >> (8 * b + 1)) & 0x7F80u) | tbl);
       } else if constexpr (BITS == 3) {
         constexpr int bit = 12 * s, word = bit >> 5, sh = bit & 31;
         uint32_t vg, vh;
@@ -293,119 +465,107 @@ __global__ void __launch_bounds__(kThreads, 1) linear_wq_mma_stream_kernel(const
           vg = buf[0][word] >> sh;
           vh = buf[1][word] >> sh;
         }
-        a0 = lds_u32(tbl_addr + ((vg << 7) & 0x1F80u));
-        a2 = lds_u32(tbl_addr + ((vg << 1) & 0x1F80u));
-        a1 = lds_u32(tbl_addr + ((vh << 7) & 0x1F80u));
-        a3 = lds_u32(tbl_addr + ((vh << 1) & 0x1F80u));
+        a0 = lookup_u32(((vg << 7) & 0x1F80u) | tbl);
+        a2 = lookup_u32(((vg << 1) & 0x1F80u) | tbl);
+        a1 = lookup_u32(((vh << 7) & 0x1F80u) | tbl);
+        a3 = lookup_u32(((vh << 1) & 0x1F80u) | tbl);
       } else {
-        // one byte -> four codewords (a0 and a2 of its row): entry * 256 bytes
-        constexpr int word = s / 4, sh = (s % 4) * 8;
-        const uint32_t wg = buf[0][word], wh = buf[1][word];
-        const uint32_t og = sh == 0 ? (wg << 8) & 0xFF00u : (wg >> (sh - 8)) & 0xFF00u;
-        const uint32_t oh = sh == 0 ? (wh << 8) & 0xFF00u : (wh >> (sh - 8)) & 0xFF00u;
-        const uint2 eg = lds_u64(tbl_addr + og), eh = lds_u64(tbl_addr + oh);
+        // one byte -> four codewords (a0 and a2 of its row), 256 bytes per entry: the byte drops into
+        // byte 1 of the table address with one permute
+        constexpr int word = s / 4, b = s % 4;
+        constexpr uint32_t sel = 0x7604u | (b << 4);
+        const uint2 eg = lookup_u64(__byte_perm(buf[0][word], tbl, sel));
+        const uint2 eh = lookup_u64(__byte_perm(buf[1][word], tbl, sel));
         a0 = eg.x; a2 = eg.y; a1 = eh.x; a3 = eh.y;
       }
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb) {
-        uint2 b = make_uint2(a0, a1);
-        if (!(p.dbg & 4)) b = lds_u64(xb + nb * x_nb_stride + 32 * s);
-        if (!(p.dbg & 1)) mma_16816<F16>(acc[nb], a0, a1, a2, a3, b.x, b.y);
-        else acc[nb][0] += __uint_as_float(a0 ^ a1 ^ a2 ^ a3 ^ b.x ^ b.y);
+        if constexpr (s % 2 == 0) bfrag[nb] = lds_u128(xrow[nb] + pr_j * xstep[nb] + 32 * s);  // steps s, s + 1
+        if constexpr (s % 2 == 0) mma_16816<F16>(acc[0][nb], a0, a1, a2, a3, bfrag[nb].x, bfrag[nb].y);
+        else mma_16816<F16>(acc[1][nb], a0, a1, a2, a3, bfrag[nb].z, bfrag[nb].w);
       }
     });
   };
 
-  // after the iteration's __syncthreads: bias, epilogue, residual, store; then clear the slot
-  auto write_iteration = [&](int it) {
-    float* s = slots + static_cast<size_t>(it & 1) * p.G * (MR * 16);
-    const int total = p.G * MR * 16;
-    for (int idx = tid; idx < total; idx += kThreads) {
-      const int r = idx & 15;
-      const int m = (idx >> 4) % MR;
-      const int slot = idx / (MR * 16);
-      const float v = s[idx];
-      s[idx] = 0.0f;
-      const int64_t n = (static_cast<int64_t>(it) * p.G + slot) * 16 + r;
-      if (m < p.M && n < p.N) {
-        const float vb = v + (p.bias != nullptr ? load_as_float(p.bias, p.bias_dtype, n) : 0.0f);
-        const int64_t o = static_cast<int64_t>(m) * p.N + n;
-        const float res = p.residual != nullptr ? load_as_float(p.residual, p.y_dtype, o) : 0.0f;
-        store_from_float(p.y, p.y_dtype, o, finish_value(vb, p.epilogue, p.residual != nullptr, res));
-      }
+  for (int seq = 0; seq < total; ++seq) {
+    uint32_t buf[2][W];
+    if (fetch_unit(buf)) process(buf);
+    if (++pr_j == nch) {
+      pr_j = 0;
+      flush(pr_it);
+      end_iteration(pr_it);
+      ++pr_it;
     }
-  };
-
-  Cursor ld, pr;
-  ld.it = pr.it = it_begin;
-  ld.reset(warp, p.chunks);
-  pr.reset(warp, p.chunks);
-  static_for<0, PF>([&](auto qc) {
-    load_unit(ld, ring[decltype(qc)::value]);
-    ld.advance(p.upw, warp, p.chunks);
-  });
-  const int total = my_iters * p.upw;
-  for (int seq = 0; seq < total; seq += PF) {
-    static_for<0, PF>([&](auto qc) {
-      constexpr int q = decltype(qc)::value;
-      if (seq + q < total) {
-        process(pr, ring[q]);
-        load_unit(ld, ring[q]);
-        ld.advance(p.upw, warp, p.chunks);
-        if (pr.i == p.upw - 1) {  // the iteration ends here for every warp of the CTA
-          if (acc_slot >= 0) flush(pr.it);
-          __syncthreads();
-          write_iteration(pr.it);
-          if (pr.it + 1 < it_end) {
-            const int64_t ng = group_of_iteration(pr.it + 1);
-            if (ng != cur_group) {  // uniform over the CTA: nobody reads the table between the barriers
-              cur_group = ng;
-              build_table(ng);
-              __syncthreads();
-            }
-          }
-        }
-        pr.advance(p.upw, warp, p.chunks);
-      }
-    });
+  }
+  // Only after a wait gave up: copies of this warp may still be in flight; give each a last bounded
+  // chance to land before the CTA's shared memory is released.
+  if (*abort_flag != 0u && lane == 0) {
+    for (int q = 0; q < p.pf; ++q)
+      for (uint32_t poll = 0; poll < 1024u; ++poll)
+        if (mbar_try_wait(bars_w + q * 8, pr_phase) || mbar_try_wait(bars_w + q * 8, pr_phase ^ 1u)) break;
   }
 }
 
 struct Plan {
-  int G, chunks, units, upw, total_it, ipc, ctas, nb;
+  int G, wpr, cpw, chunks, total_it, ipc, ctas, nb, rows_low, pf;
+  uint32_t x_low, x_high, ring, bars, part, zero;
   size_t smem;
 };
 
 template <int BITS>
 bool make_plan(const dimq_wq_weight* w, int64_t M, int64_t N, int64_t K, Plan* out) {
-  const int nb = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
-  const int chunks = static_cast<int>(K / kChunkK);
-  const int64_t row_blocks = (N + 15) / 16;
-  double best = 1e30;
+  using C = Cfg<BITS>;
   Plan bp{};
-  for (int G = 1; G <= 8; G *= 2) {
-    if (w->groups > 1 && w->group_rows % (16 * G) != 0) continue;
-    const int64_t units = static_cast<int64_t>(G) * chunks;
-    if (units > (1 << 20)) continue;
-    const int upw = static_cast<int>((units + kWarps - 1) / kWarps);
-    const int64_t total_it = (row_blocks + G - 1) / G;
-    if (total_it > 0x3FFFFFFF) continue;
-    const int64_t ctas0 = total_it < kNumSMs ? total_it : kNumSMs;
-    const int64_t ipc = (total_it + ctas0 - 1) / ctas0;
-    const double cost = static_cast<double>(ipc) * (upw + 0.4);  // 0.4: barrier + write-back per iteration
-    if (cost < best) {
-      best = cost;
-      bp.G = G; bp.chunks = chunks; bp.units = static_cast<int>(units); bp.upw = upw;
-      bp.total_it = static_cast<int>(total_it); bp.ipc = static_cast<int>(ipc);
-      bp.ctas = static_cast<int>((total_it + ipc - 1) / ipc);
-    }
+  bp.nb = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
+  bp.chunks = static_cast<int>(K / kChunkK);
+  if (bp.chunks >= kWarps) {  // one row block at a time, every warp a run of consecutive chunks
+    bp.G = 1;
+    bp.cpw = (bp.chunks + kWarps - 1) / kWarps;
+    bp.wpr = (bp.chunks + bp.cpw - 1) / bp.cpw;
+  } else {  // several row blocks at a time, one chunk per warp
+    bp.cpw = 1;
+    bp.wpr = bp.chunks;
+    bp.G = kWarps / bp.chunks;
+    // all row blocks of an iteration use one codebook
+    while (bp.G > 1 && w->groups > 1 && w->group_rows % (16 * bp.G) != 0) --bp.G;
+    // a small problem is better spread over more CTAs
+    const int64_t row_blocks = (N + 15) / 16;
+    while (bp.G > 1 && (row_blocks + bp.G - 1) / bp.G < kNumSMs) --bp.G;
+    while (bp.G > 1 && w->groups > 1 && w->group_rows % (16 * bp.G) != 0) --bp.G;
   }
-  if (best >= 1e30) return false;
-  bp.nb = nb;
-  const size_t xs = static_cast<size_t>(K) + 16;
-  const size_t x_bytes = (static_cast<size_t>(8 * nb) * xs * 2 + 15) & ~size_t(15);
-  bp.smem = Cfg<BITS>::kTableBytes + x_bytes + sizeof(float) * (2 * bp.G * 8 * nb * 16 + 16);
-  if (bp.smem > kSmemLimit) return false;
+  const int64_t row_blocks = (N + 15) / 16;
+  const int64_t total_it = (row_blocks + bp.G - 1) / bp.G;
+  if (total_it > 0x3FFFFFF) return false;
+  const int64_t ctas0 = total_it < kNumSMs ? total_it : kNumSMs;
+  bp.ipc = static_cast<int>((total_it + ctas0 - 1) / ctas0);
+  bp.total_it = static_cast<int>(total_it);
+  bp.ctas = static_cast<int>((total_it + bp.ipc - 1) / bp.ipc);
+  // fixed layout (absolute shared addresses): codewords, mbarriers and the first activation rows below
+  // the table; the other activation rows, the partial sums and the rings above it
+  constexpr int kMaxPf = 8;
+  const size_t low = sizeof(float) * 16;  // codewords
+  bp.bars = static_cast<uint32_t>(kLowStart + low);
+  bp.zero = static_cast<uint32_t>((bp.bars + kWarps * kMaxPf * 8 + 16 + 127) & ~size_t(127));  // after the abort flag
+  const size_t low_end = bp.zero + 256;
+  if (low_end > C::kTableAddr) return false;
+  // row stride 2 K + 64 bytes: the eight lanes of a quarter-warp (two rows x four 16-byte slots) cover
+  // 128 consecutive bytes modulo the bank width
+  const size_t row = (static_cast<size_t>(K) + 32) * 2;
+  bp.x_low = static_cast<uint32_t>((low_end + 127) & ~size_t(127));
+  const size_t rows = static_cast<size_t>(M);
+  size_t rows_low = bp.x_low < C::kTableAddr ? (C::kTableAddr - bp.x_low) / row : 0;
+  if (rows_low > rows) rows_low = rows;
+  bp.rows_low = static_cast<int>(rows_low);
+  // rows above the table continue the same bank pattern (64 bytes per row modulo 128)
+  bp.x_high = C::kXAddr + static_cast<uint32_t>((rows_low % 2) * 64);
+  const size_t x_end = bp.x_high + (rows - rows_low) * row;
+  bp.part = static_cast<uint32_t>((x_end + 127) & ~size_t(127));
+  const size_t part_bytes = sizeof(float) * 2 * kWarps * 16 * 8 * bp.nb;
+  bp.ring = static_cast<uint32_t>((bp.part + part_bytes + 127) & ~size_t(127));
+  if (bp.ring + kWarps * C::kUnitBytes > kSmemWindow) return false;  // at least one slot per warp
+  size_t pf = (kSmemWindow - bp.ring) / (kWarps * C::kUnitBytes);
+  bp.pf = static_cast<int>(pf > kMaxPf ? kMaxPf : pf);
+  bp.smem = bp.ring + static_cast<size_t>(bp.pf) * kWarps * C::kUnitBytes;  // counted from shared address 0
   *out = bp;
   return true;
 }
@@ -420,20 +580,24 @@ bool plan_for(const dimq_wq_weight* w, int64_t M, int64_t N, int64_t K, Plan* pl
 }
 
 template <int BITS, int NB, bool F16>
-int launch_one(const MsParams& p, const Plan& plan, cudaStream_t st) {
+int launch_one(const CUtensorMap& wmap, MsParams& p, const Plan& plan, cudaStream_t st) {
   auto kern = linear_wq_mma_stream_kernel<BITS, NB, F16>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit);
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemWindow);
   if (e != cudaSuccess) return static_cast<int>(e);
-  kern<<<plan.ctas, kThreads, plan.smem, st>>>(p);
+  void* status = nullptr;
+  e = cudaGetSymbolAddress(&status, g_ms_status);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  p.status = static_cast<uint32_t*>(status);
+  kern<<<plan.ctas, kThreads, plan.smem, st>>>(wmap, p);
   return launch_status();
 }
 
 template <int BITS>
-int launch_bits(const MsParams& p, const Plan& plan, bool f16, cudaStream_t st) {
+int launch_bits(const CUtensorMap& wmap, MsParams& p, const Plan& plan, bool f16, cudaStream_t st) {
   switch (plan.nb) {
-    case 1: return f16 ? launch_one<BITS, 1, true>(p, plan, st) : launch_one<BITS, 1, false>(p, plan, st);
-    case 2: return f16 ? launch_one<BITS, 2, true>(p, plan, st) : launch_one<BITS, 2, false>(p, plan, st);
-    default: return f16 ? launch_one<BITS, 4, true>(p, plan, st) : launch_one<BITS, 4, false>(p, plan, st);
+    case 1: return f16 ? launch_one<BITS, 1, true>(wmap, p, plan, st) : launch_one<BITS, 1, false>(wmap, p, plan, st);
+    case 2: return f16 ? launch_one<BITS, 2, true>(wmap, p, plan, st) : launch_one<BITS, 2, false>(wmap, p, plan, st);
+    default: return f16 ? launch_one<BITS, 4, true>(wmap, p, plan, st) : launch_one<BITS, 4, false>(wmap, p, plan, st);
   }
 }
 
@@ -448,7 +612,7 @@ bool mma_stream_supported(const void* x, int x_dtype, const dimq_wq_weight* w, i
   if (w->bits != 2 && w->bits != 3 && w->bits != 4) return false;
   if (w->groups > 1 && w->group_rows % 16 != 0) return false;
   if (!aligned(x, 8) || !aligned(w->packed, 16)) return false;
-  if (N > (int64_t(1) << 34)) return false;
+  if (N > 0x3FFFFFFF) return false;
   Plan plan;
   return plan_for(w, M, N, K, &plan);
 }
@@ -464,15 +628,33 @@ int launch_linear_wq_mma_stream(const void* x, int x_dtype, const dimq_wq_weight
   p.group_rows = w->groups > 1 ? w->group_rows : (N + 15) / 16 * 16 + 16;
   p.bias = bias; p.bias_dtype = bias_dtype; p.residual = residual; p.y = y; p.y_dtype = y_dtype;
   p.M = static_cast<int>(M); p.N = N; p.K = K; p.epilogue = epilogue;
-  p.G = plan.G; p.chunks = plan.chunks; p.units = plan.units; p.upw = plan.upw; p.total_it = plan.total_it;
-  p.ipc = plan.ipc; p.xs = static_cast<int>(K) + 16;
-  { const char* e = getenv("DIMQ_B200_MS_DEBUG"); p.dbg = e ? atoi(e) : 0; }
+  p.G = plan.G; p.wpr = plan.wpr; p.cpw = plan.cpw; p.chunks = plan.chunks; p.total_it = plan.total_it;
+  p.ipc = plan.ipc; p.xs = static_cast<int>(K) + 32; p.rows_low = plan.rows_low; p.x_low = plan.x_low; p.x_high = plan.x_high;
+  p.pf = plan.pf; p.ring = plan.ring; p.bars = plan.bars; p.part = plan.part; p.zero = plan.zero;
+  // the packed index matrix as [N rows][K * bits / 8 bytes]; one box = one unit (16 rows x 128 k)
+  CUtensorMap wmap;
+  const uint64_t row_bytes = static_cast<uint64_t>(K) * w->bits / 8;
+  const uint64_t dims[2] = {row_bytes, static_cast<uint64_t>(N)};
+  const uint64_t strides[1] = {row_bytes};
+  const uint32_t box[2] = {static_cast<uint32_t>(kChunkK * w->bits / 8), 16u};
+  const int rc = encode_plain_tensor_map(&wmap, 1, 2, w->packed, dims, strides, box);
+  if (rc != DIMQ_OK) return rc;
   const bool f16 = x_dtype == DIMQ_F16;
   switch (w->bits) {
-    case 2: return launch_bits<2>(p, plan, f16, st);
-    case 3: return launch_bits<3>(p, plan, f16, st);
-    default: return launch_bits<4>(p, plan, f16, st);
+    case 2: return launch_bits<2>(wmap, p, plan, f16, st);
+    case 3: return launch_bits<3>(wmap, p, plan, f16, st);
+    default: return launch_bits<4>(wmap, p, plan, f16, st);
   }
+}
+
+// Status word of this kernel (non-zero: the shared-memory window did not start where the fixed layout
+// expects it and the launch did nothing); reading clears it.
+int read_ms_status(uint32_t* status) {
+  cudaError_t e = cudaMemcpyFromSymbol(status, g_ms_status, sizeof(uint32_t));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const uint32_t zero = 0;
+  e = cudaMemcpyToSymbol(g_ms_status, &zero, sizeof(uint32_t));
+  return e == cudaSuccess ? DIMQ_OK : static_cast<int>(e);
 }
 
 }  // namespace dimq

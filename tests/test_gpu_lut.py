@@ -280,8 +280,18 @@ def test_linear_wq_mma_stream(ops, bits, m, k, n, grp, mode):
     # fp16 operands: the codewords the kernel multiplies are the fp16 roundings of the codebook
     cbs = case["codebooks"].astype(np.float16).astype(np.float32) if x_dtype == torch.float16 else case["codebooks"]
     want = o.linear_wq(x.float().numpy(), case["packed"], cbs, bits, n, k, bias, case["group_rows"])
-    got = ops.dimq_linear_wq(x.cuda(), _cuda(case["packed"]), _cuda(case["codebooks"], cb_torch), _cuda(bias), n, k,
-                             bits=bits, group_rows=grp, algo="mma_stream")
+    args = (x.cuda(), _cuda(case["packed"]), _cuda(case["codebooks"], cb_torch), _cuda(bias), n, k)
+    # the two widest cases may not fit beside the lookup table (activation rows, per-warp partial sums
+    # and index rings share 227 KB): the kernel then refuses and the automatic choice takes another one
+    may_refuse = (m, k) in ((16, 4096), (32, 2048))
+    try:
+        got = ops.dimq_linear_wq(*args, bits=bits, group_rows=grp, algo="mma_stream")
+    except RuntimeError as err:
+        assert may_refuse and "does not support" in str(err), err
+        got = ops.dimq_linear_wq(*args, bits=bits, group_rows=grp)
+        _assert_close(got, want, "auto dispatch after refusal")
+        return
+    assert ops.last_device_status() == 0
     _assert_close(got, want, f"mma_stream bits={bits} {m}x{k}x{n} mode={mode}")
     np.testing.assert_allclose(got.cpu().numpy(), want, rtol=2e-4, atol=2e-4)
 
