@@ -40,7 +40,11 @@ WORKLOADS = {
                  "BN folded; 4-bit per-layer bf16 codebooks, 8-bit for the stem conv and the classifier, random init"),
 }
 FALLBACK_TFLOPS = 1590.0
+FALLBACK_HBM_GBS = 6650.0
 CPU_SAMPLE_IMAGES = 8
+
+
+NCU_DRAM_BYTES_PER_FLOP = 16.45e6 / 38.65e9
 
 
 def _peaks():
@@ -166,6 +170,59 @@ def cpu_baseline(ckpt, workload: str) -> dict:
             "sample": f"{passes} passes of {CPU_SAMPLE_IMAGES} images (fp32 PyTorch CPU, dequantised weights)"}
 
 
+def run_micro(args) -> None:
+    """One LUT GEMM shape, timed with CUDA events over a CUDA graph of back-to-back calls.
+
+    The single-kernel driver behind the per-kernel tables and the ncu captures under profiles/."""
+    import torch
+
+    from dimq_b200 import ops
+
+    ops.require_extension()
+    parts = args.micro.split(",")
+    m, k, n, bits = (int(v) for v in parts[:4])
+    algo = parts[4] if len(parts) > 4 and parts[4] not in ("", "auto") else None
+    index_bytes = n * k * bits // 8
+    copies = int(parts[5]) if len(parts) > 5 else max(1, min(64, (192 << 20) // max(index_bytes, 1) + 1))
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    x = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
+    packed = [torch.randint(0, 256, (index_bytes,), dtype=torch.uint8, device=dev) for _ in range(copies)]
+    groups = n // 128 if bits == 3 and n % 128 == 0 else 1
+    cb = (torch.randn(groups, 1 << bits, device=dev) * 0.02).sort(dim=1).values.to(torch.bfloat16)
+    kw = dict(bits=bits, group_rows=128 if groups > 1 else None, out_dtype=torch.bfloat16, algo=algo)
+    call = lambda pw: ops.dimq_linear_wq(x, pw, cb, None, n, k, **kw)
+    for pw in packed[:2]:
+        call(pw)
+    torch.cuda.synchronize()
+    per_graph = max(copies, 8)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(per_graph):
+            call(packed[i % copies])
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        graph.replay()
+    end.record()
+    torch.cuda.synchronize()
+    us = start.elapsed_time(end) * 1e3 / (args.steps * per_graph)
+    tc_peak, peak_kind = _peaks()
+    path = ROOT / "MEASURED_PEAKS.json"
+    hbm_peak = float(json.loads(path.read_text()).get("hbm_gbs", FALLBACK_HBM_GBS)) if path.exists() else FALLBACK_HBM_GBS
+    print(json.dumps({
+        "metric": "linear_wq_us_per_call", "value": us, "unit": "us", "higher_is_better": False,
+        "config": {"workload": f"lut_gemm_m{m}_k{k}_n{n}_w{bits}", "algo": algo or "auto", "weight_copies": copies,
+                   "l2": "weights rotated over more than 126 MB" if copies * index_bytes > (126 << 20) else "weights fit L2"},
+        "tflops": 2.0 * m * n * k / us / 1e6, "tflops_frac": 2.0 * m * n * k / us / 1e6 / tc_peak,
+        "index_gbs": index_bytes / us / 1e3, "index_gbs_frac": index_bytes / us / 1e3 / hbm_peak,
+        "peak_source": peak_kind, "dtype": "bf16", "data": "synthetic",
+    }), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -175,8 +232,15 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="vit_b16", choices=["vit_b16", "resnet18"],
                     help="vit_b16 is the headline line; resnet18 prints the same line for the ResNet-18 config")
+    ap.add_argument("--micro", default=None, metavar="M,K,N,BITS[,ALGO[,COPIES]]",
+                    help="time one weight-only LUT GEMM instead of a model (bf16 activations, bf16 codebook per "
+                         "128 rows at 3 bits, per layer otherwise); COPIES distinct weights are rotated so that "
+                         "indices come from HBM")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.micro is not None:
+        run_micro(args)
+        return
 
     if args.impl == "reference":
         run_reference(args)
@@ -335,7 +399,11 @@ def main() -> None:
         "roofline": {"kernel": "linear_wq_tc_kernel (tcgen05 LUT GEMM / implicit-GEMM conv)", "bound": "tensor", "achieved": achieved,
                      "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peak_kind,
                      "launches_timed": gemm_launches, "avg_launch_ms": gemm_ms / max(gemm_launches, 1),
-                     "flops_per_step": flops / roof_steps, "traffic": None},
+                     "flops_per_step": flops / roof_steps,
+                     # DRAM bytes per launch: the ncu capture of the M = 8192 fc1 case (16.45 MB for 38.65 GFLOP,
+                     # profiles/linear_wq_tc_kernel_m8192_k768_n3072_w3.md) scaled by the flops of an average launch
+                     "traffic": NCU_DRAM_BYTES_PER_FLOP * flops / max(gemm_launches, 1),
+                     "traffic_source": "ncu capture of a smaller launch, scaled by flops"},
     }
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(ckpt, args.workload)
