@@ -282,7 +282,11 @@ def main() -> None:
 
         # ---- CUDA graphs: one per resident input buffer, plus one reading a staging buffer (e2e) ----
         stream = torch.cuda.Stream(device=dev)
-        staging = torch.empty_like(dev_images[0])
+        # two staging buffers: the host->device copy of step i + 1 runs on its own stream under step i
+        staging = [torch.empty_like(dev_images[0]) for _ in range(2)]
+        copy_stream = torch.cuda.Stream(device=dev)
+        h2d_done = [torch.cuda.Event() for _ in range(2)]
+        compute_done = [torch.cuda.Event() for _ in range(2)]
         host_logits = torch.empty(B, 1000, dtype=torch.float32).pin_memory()
         graphs, outs = [], []
         with torch.cuda.stream(stream):
@@ -290,7 +294,7 @@ def main() -> None:
                 model(dev_images[0])
             stream.synchronize()
             launches_before = _lib.LAUNCH_COUNT[0]
-            for src in dev_images + [staging]:
+            for src in dev_images + staging:
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g, stream=stream):
                     out = model(src)
@@ -309,20 +313,28 @@ def main() -> None:
                 gather_logits(outs[i % n_bufs])
 
         def step_e2e(i: int) -> None:
-            staging.copy_(host_images[i % n_bufs], non_blocking=True)
-            graphs[n_bufs].replay()
+            b = i % 2
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(compute_done[b])  # the forward that last read this buffer
+                staging[b].copy_(host_images[i % n_bufs], non_blocking=True)
+                h2d_done[b].record(copy_stream)
+            stream.wait_event(h2d_done[b])
+            graphs[n_bufs + b].replay()
             if world > 1:
-                gather_logits(outs[n_bufs])
-            host_logits.copy_(outs[n_bufs], non_blocking=True)
+                gather_logits(outs[n_bufs + b])
+            host_logits.copy_(outs[n_bufs + b], non_blocking=True)
+            compute_done[b].record(stream)
 
         def run_timed(step_fn) -> float:
             with torch.cuda.stream(stream):
                 for i in range(args.warmup):
                     step_fn(i)
+                copy_stream.synchronize()
                 barrier()
                 start = torch.cuda.Event(enable_timing=True)
                 end = torch.cuda.Event(enable_timing=True)
                 start.record(stream)
+                copy_stream.wait_event(start)  # no copy of a timed step starts before the timed region
                 for i in range(args.steps):
                     step_fn(i)
                 end.record(stream)
