@@ -241,6 +241,19 @@ __device__ __forceinline__ void epi_issue_residual(const TmapSet& tmaps, const T
 // thread = feature (lane), r[j] = row / pixel j of the chunk.  The epilogue kind and the residual are
 // template parameters so that the 32 elements form straight-line code (a run-time switch inside the
 // loop serialises them: measured ~100 cycles per element).
+// GELU for 16-bit outputs: 0.5 v (1 + tanh(0.79788 (v + 0.044715 v^3))) with the hardware tanh.  It
+// differs from the erf form by at most 4.8e-4 (relative L2 2e-4 on N(0,1) inputs), an eighth of the
+// rounding error of the bf16 store that follows, and costs 6 instructions instead of 18; the erf
+// form stays for fp32 outputs.
+constexpr int kEpiGelu16 = 16;
+__device__ __forceinline__ float gelu_tanh(float v) {
+  const float u = v * fmaf(0.0356774081f, v * v, 0.7978845608f);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  const float h = 0.5f * v;
+  return fmaf(h, t, h);
+}
+
 template <int EPI, bool RES, typename RT>
 __device__ __forceinline__ void finish_chunk(uint32_t (&r)[32], float bias, const RT* res) {
 #pragma unroll
@@ -252,6 +265,7 @@ __device__ __forceinline__ void finish_chunk(uint32_t (&r)[32], float bias, cons
     } else {
       if (EPI == DIMQ_EPI_RELU) v = fmaxf(v, 0.0f);
       if (EPI == DIMQ_EPI_GELU) v = 0.5f * v * (1.0f + fast_erf(v * 0.70710678118654752440f));
+      if (EPI == kEpiGelu16) v = gelu_tanh(v);
       if (RES) v += to_float<RT>(res[j * 32]);
     }
     r[j] = __float_as_uint(v);
@@ -263,6 +277,7 @@ __device__ __forceinline__ void finish_chunk_epi(uint32_t (&r)[32], float bias, 
   switch (epilogue) {
     case DIMQ_EPI_RELU: finish_chunk<DIMQ_EPI_RELU, RES, RT>(r, bias, res); break;
     case DIMQ_EPI_GELU: finish_chunk<DIMQ_EPI_GELU, RES, RT>(r, bias, res); break;
+    case kEpiGelu16: finish_chunk<kEpiGelu16, RES, RT>(r, bias, res); break;
     case DIMQ_EPI_ADD_RELU: finish_chunk<DIMQ_EPI_ADD_RELU, RES, RT>(r, bias, res); break;
     default: finish_chunk<DIMQ_EPI_NONE, RES, RT>(r, bias, res); break;
   }
@@ -278,6 +293,7 @@ __device__ __forceinline__ void write_chunk(const uint32_t (&r)[32], unsigned ch
 // [32 rows][32 features] staging tile of one chunk; `res` is the residual tile in the same layout.
 __device__ __forceinline__ void stage_chunk(uint32_t (&r)[32], unsigned char* out, const unsigned char* res, int lane,
                                             float bias, int epilogue, int y_dtype) {
+  if (epilogue == DIMQ_EPI_GELU && y_dtype != DIMQ_F32) epilogue = kEpiGelu16;
   if (res == nullptr) finish_chunk_epi<false, float>(r, bias, nullptr, epilogue);
   else if (y_dtype == DIMQ_BF16) finish_chunk_epi<true, __nv_bfloat16>(r, bias, reinterpret_cast<const __nv_bfloat16*>(res) + lane, epilogue);
   else finish_chunk_epi<true, __half>(r, bias, reinterpret_cast<const __half*>(res) + lane, epilogue);
