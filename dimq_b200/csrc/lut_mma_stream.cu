@@ -39,7 +39,8 @@ int encode_plain_tensor_map(void* out, int elem_bytes, int rank, const void* bas
 namespace {
 
 constexpr int kWarps = 16;
-constexpr int kThreads = kWarps * 32;
+constexpr int kWriteWarps = 2;  // warps that only add the partial sums and write y, off the compute warps' path
+constexpr int kThreads = (kWarps + kWriteWarps) * 32;
 constexpr int kChunkK = 128;
 constexpr uint32_t kSmemWindow = 227 * 1024;  // dynamic shared memory a CTA may ask for
 constexpr uint32_t kLowStart = 1024;          // the dynamic window starts at or below this shared address
@@ -86,6 +87,7 @@ struct MsParams {
   uint32_t x_high; // shared address of row rows_low
   uint32_t zero;   // shared address of 256 zero bytes (the activations of MMA columns beyond M)
   int pf;          // ring slots per warp
+  int bw;          // units (k chunks) per TMA box and ring slot: 1, 2 or 4
   uint32_t part;   // shared address of the partial sums: [2][warp][16 rows][MR]
   uint32_t ring;   // shared address of the rings: [warp][pf][unit]
   uint32_t bars;   // shared address of the slots' mbarriers: [warp][pf]
@@ -239,15 +241,22 @@ linear_wq_mma_stream_kernel(const __grid_constant__ CUtensorMap wmap, const MsPa
   const int my_iters = it_end - it_begin;
   if (my_iters <= 0) return;
 
+  // the first group's codewords: the global load flies while the barriers are set up and the first
+  // copies are issued
+  const int64_t first_group = (static_cast<int64_t>(it_begin) * p.G * 16) / p.group_rows;
+  float first_cb = 0.0f;
+  if (tid < (1 << BITS) && tid < p.entries)
+    first_cb = load_as_float(p.codebooks, p.cb_dtype, first_group * p.entries + tid);
+
   // ---- this warp's share: row block `slot` of every iteration, k chunks [c0, c0 + nch) ----
   const int slot = warp / p.wpr;
   const int c0 = (warp - slot * p.wpr) * p.cpw;
-  const int nch = slot < p.G ? max(0, min(p.cpw, p.chunks - c0)) : 0;
+  const int nch = (warp < kWarps && slot < p.G) ? max(0, min(p.cpw, p.chunks - c0)) : 0;
 
 
   // ---- the warp's ring: p.pf slots of one unit each, one mbarrier per slot; lane 0 issues the copies ----
   constexpr int kChunkBytes = kChunkK * BITS / 8;  // per row
-  const uint32_t ring_w = p.ring + warp * p.pf * C::kUnitBytes;
+  const uint32_t ring_w = p.ring + warp * p.pf * p.bw * C::kUnitBytes;
   const uint32_t bars_w = p.bars + warp * p.pf * 8;
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(abs0 + p.bars + kWarps * p.pf * 8);
   const int total = my_iters * nch;
@@ -257,14 +266,17 @@ linear_wq_mma_stream_kernel(const __grid_constant__ CUtensorMap wmap, const MsPa
   uint32_t pr_phase = 0;
   bool seq_live = true;  // false once a wait of this warp gave up
 
-  // issue the copy of the next unit of the sequence (lane 0 only; the slot must be free)
+  // issue the copy of the next box of the sequence: p.bw consecutive chunks of the 16 rows (lane 0
+  // only; the slot must be free)
+  const uint32_t slot_bytes = p.bw * C::kUnitBytes;
   auto issue_unit = [&]() {
     const uint32_t bar = bars_w + ld_slot * 8;
-    mbar_expect_tx(bar, C::kUnitBytes);
-    tma_load_unit(ring_w + ld_slot * C::kUnitBytes, &wmap, bar, (c0 + ld_j) * kChunkBytes, ld_row0);
-    ++ld_seq;
+    mbar_expect_tx(bar, slot_bytes);
+    tma_load_unit(ring_w + ld_slot * slot_bytes, &wmap, bar, (c0 + ld_j) * kChunkBytes, ld_row0);
+    ld_seq += p.bw;
     if (++ld_slot == p.pf) ld_slot = 0;
-    if (++ld_j == nch) {
+    ld_j += p.bw;
+    if (ld_j == nch) {
       ld_j = 0;
       ld_row0 += p.G * 16;
     }
@@ -274,7 +286,7 @@ linear_wq_mma_stream_kernel(const __grid_constant__ CUtensorMap wmap, const MsPa
       for (int q = 0; q < p.pf; ++q) mbar_init(bars_w + q * 8, 1);
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
       // the first copies fly while the activations and the table are being set up
-      for (int q = 0; q < p.pf && ld_seq < total; ++q) issue_unit();
+      for (int q = 0; q < p.pf && ld_seq < total; ++q) issue_unit();  // ld_seq counts units
     }
     __syncwarp();
   }
@@ -299,9 +311,11 @@ linear_wq_mma_stream_kernel(const __grid_constant__ CUtensorMap wmap, const MsPa
   }
 
   // pair table of one codebook group, one copy per lane: word (entry * 32 + lane)
-  auto build_table = [&](int64_t group) {
-    if (tid < (1 << BITS))
-      cb_s[tid] = tid < p.entries ? load_as_float(p.codebooks, p.cb_dtype, group * p.entries + tid) : 0.0f;
+  auto build_table = [&](int64_t group, bool preloaded) {
+    if (tid < (1 << BITS)) {
+      if (preloaded) cb_s[tid] = first_cb;
+      else cb_s[tid] = tid < p.entries ? load_as_float(p.codebooks, p.cb_dtype, group * p.entries + tid) : 0.0f;
+    }
     __syncthreads();
     for (int wi = tid; wi < C::kTableEntries * 32; wi += kThreads) {
       const int e = wi >> 5;
@@ -318,8 +332,8 @@ linear_wq_mma_stream_kernel(const __grid_constant__ CUtensorMap wmap, const MsPa
   auto group_of_iteration = [&](int it) -> int64_t {
     return (static_cast<int64_t>(it) * p.G * 16) / p.group_rows;
   };
-  int64_t cur_group = group_of_iteration(it_begin);
-  build_table(cur_group);
+  int64_t cur_group = first_group;
+  build_table(cur_group, true);
   asm volatile("cp.async.wait_all;" ::: "memory");
   __syncthreads();
 
@@ -353,7 +367,7 @@ linear_wq_mma_stream_kernel(const __grid_constant__ CUtensorMap wmap, const MsPa
   auto write_iteration = [&](int it) {
     const float* base = part + static_cast<size_t>(it & 1) * kWarps * (16 * MR);
     const int total_out = p.G * MR * 16;
-    for (int idx = tid; idx < total_out; idx += kThreads) {
+    for (int idx = tid - kWarps * 32; idx < total_out; idx += kWriteWarps * 32) {
       const int r = idx & 15;
       const int m = (idx >> 4) % MR;
       const int sl = idx / (MR * 16);
@@ -370,21 +384,23 @@ linear_wq_mma_stream_kernel(const __grid_constant__ CUtensorMap wmap, const MsPa
     }
   };
 
-  // every warp of the CTA passes here once per iteration, in the same order
+  // Every warp of the CTA passes here once per iteration, in the same order.  The write-back warps read
+  // buffer it & 1 after this barrier and reach the next one only when they are done, so the compute
+  // warps cannot overwrite that buffer (iteration it + 2) before it has been read.
   auto end_iteration = [&](int it) {
     __syncthreads();
-    write_iteration(it);
+    if (warp >= kWarps) write_iteration(it);
     if (it + 1 < it_end) {
       const int64_t ng = group_of_iteration(it + 1);
       if (ng != cur_group) {  // uniform over the CTA: nobody reads the table between the barriers
         cur_group = ng;
-        build_table(ng);
+        build_table(ng, false);
         __syncthreads();
       }
     }
   };
 
-  if (nch == 0) {  // a warp without chunks only keeps the barriers and helps with the write-back
+  if (nch == 0) {  // the write-back warps, and compute warps without chunks: only the barriers
     for (int it = it_begin; it < it_end; ++it) end_iteration(it);
     return;
   }
@@ -402,26 +418,32 @@ linear_wq_mma_stream_kernel(const __grid_constant__ CUtensorMap wmap, const MsPa
     xstep[nb] = live ? kChunkK * 2 : 0;
   }
 
-  // Wait (bounded) for the slot of the next unit, copy the lane's indices out, refill the slot.
-  // Returns false when the unit has no data (a wait gave up here or elsewhere in the CTA).
+  // Unit `sub` of the current box: wait (bounded) for the box when it is its first unit, copy the lane's
+  // indices out, and re-arm the slot after its last unit.  Returns false when there is no data (a wait
+  // gave up here or elsewhere in the CTA).
+  int sub = 0;
+  bool box_ok = false;
+  const uint32_t row_pitch = p.bw * kChunkBytes;  // bytes between rows inside a slot
   auto fetch_unit = [&](uint32_t (&buf)[2][W]) -> bool {
-    const uint32_t bar = bars_w + pr_slot * 8;
-    bool ok = seq_live && mbar_test_wait(bar, pr_phase);  // usually the copy landed long ago
-    if (!ok && seq_live) {
-      for (uint32_t poll = 0; poll < kPollLimit; ++poll) {
-        if (mbar_try_wait(bar, pr_phase)) { ok = true; break; }
-        if ((poll & 63u) == 63u && *abort_flag != 0u) break;
-      }
-      if (!ok) {  // give up: no more copies are issued by this warp, the units left are skipped
-        *abort_flag = 1u;
-        atomicOr(p.status, 0x80000902u);
-        seq_live = false;
+    if (sub == 0) {
+      const uint32_t bar = bars_w + pr_slot * 8;
+      box_ok = seq_live && mbar_test_wait(bar, pr_phase);  // usually the copy landed long ago
+      if (!box_ok && seq_live) {
+        for (uint32_t poll = 0; poll < kPollLimit; ++poll) {
+          if (mbar_try_wait(bar, pr_phase)) { box_ok = true; break; }
+          if ((poll & 63u) == 63u && *abort_flag != 0u) break;
+        }
+        if (!box_ok) {  // give up: no more copies are issued by this warp, the units left are skipped
+          *abort_flag = 1u;
+          atomicOr(p.status, 0x80000902u);
+          seq_live = false;
+        }
       }
     }
-    const uint32_t src = ring_w + pr_slot * C::kUnitBytes + g * kChunkBytes + t * (4 * BITS);
+    const uint32_t src = ring_w + pr_slot * slot_bytes + g * row_pitch + sub * kChunkBytes + t * (4 * BITS);
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      const uint32_t a = src + h * 8 * kChunkBytes;
+      const uint32_t a = src + h * 8 * row_pitch;
       if constexpr (BITS == 4) {
         const uint4 q = lds_u128(a);
         buf[h][0] = q.x; buf[h][1] = q.y; buf[h][2] = q.z; buf[h][3] = q.w;
@@ -433,10 +455,13 @@ linear_wq_mma_stream_kernel(const __grid_constant__ CUtensorMap wmap, const MsPa
         for (int j = 0; j < W; ++j) buf[h][j] = lds_u32(a + 4 * j);
       }
     }
-    __syncwarp();  // every lane has its words: the slot may be overwritten
-    if (lane == 0 && ok && ld_seq < total) issue_unit();
-    if (++pr_slot == p.pf) { pr_slot = 0; pr_phase ^= 1u; }
-    return ok;
+    if (++sub == p.bw) {
+      sub = 0;
+      __syncwarp();  // every lane has its words of the last unit: the slot may be overwritten
+      if (lane == 0 && box_ok && ld_seq < total) issue_unit();
+      if (++pr_slot == p.pf) { pr_slot = 0; pr_phase ^= 1u; }
+    }
+    return box_ok;
   };
 
   // eight MMA steps over the 128 k of one unit
@@ -507,7 +532,7 @@ linear_wq_mma_stream_kernel(const __grid_constant__ CUtensorMap wmap, const MsPa
 }
 
 struct Plan {
-  int G, wpr, cpw, chunks, total_it, ipc, ctas, nb, rows_low, pf;
+  int G, wpr, cpw, chunks, total_it, ipc, ctas, nb, rows_low, pf, bw;
   uint32_t x_low, x_high, ring, bars, part, zero;
   size_t smem;
 };
@@ -562,10 +587,15 @@ bool make_plan(const dimq_wq_weight* w, int64_t M, int64_t N, int64_t K, Plan* o
   bp.part = static_cast<uint32_t>((x_end + 127) & ~size_t(127));
   const size_t part_bytes = sizeof(float) * 2 * kWarps * 16 * 8 * bp.nb;
   bp.ring = static_cast<uint32_t>((bp.part + part_bytes + 127) & ~size_t(127));
-  if (bp.ring + kWarps * C::kUnitBytes > kSmemWindow) return false;  // at least one slot per warp
-  size_t pf = (kSmemWindow - bp.ring) / (kWarps * C::kUnitBytes);
+  // units per TMA box: several consecutive chunks when every warp owns the same whole number of them
+  bp.bw = 1;
+  if (bp.chunks % bp.cpw == 0) bp.bw = bp.cpw % 4 == 0 ? 4 : (bp.cpw % 2 == 0 ? 2 : 1);
+  while (bp.bw > 1 && bp.ring + 2 * kWarps * bp.bw * C::kUnitBytes > kSmemWindow) bp.bw /= 2;
+  const size_t slot_bytes = static_cast<size_t>(bp.bw) * C::kUnitBytes;
+  if (bp.ring + kWarps * slot_bytes > kSmemWindow) return false;  // at least one slot per warp
+  size_t pf = (kSmemWindow - bp.ring) / (kWarps * slot_bytes);
   bp.pf = static_cast<int>(pf > kMaxPf ? kMaxPf : pf);
-  bp.smem = bp.ring + static_cast<size_t>(bp.pf) * kWarps * C::kUnitBytes;  // counted from shared address 0
+  bp.smem = bp.ring + static_cast<size_t>(bp.pf) * kWarps * slot_bytes;  // counted from shared address 0
   *out = bp;
   return true;
 }
@@ -630,13 +660,13 @@ int launch_linear_wq_mma_stream(const void* x, int x_dtype, const dimq_wq_weight
   p.M = static_cast<int>(M); p.N = N; p.K = K; p.epilogue = epilogue;
   p.G = plan.G; p.wpr = plan.wpr; p.cpw = plan.cpw; p.chunks = plan.chunks; p.total_it = plan.total_it;
   p.ipc = plan.ipc; p.xs = static_cast<int>(K) + 32; p.rows_low = plan.rows_low; p.x_low = plan.x_low; p.x_high = plan.x_high;
-  p.pf = plan.pf; p.ring = plan.ring; p.bars = plan.bars; p.part = plan.part; p.zero = plan.zero;
+  p.pf = plan.pf; p.bw = plan.bw; p.ring = plan.ring; p.bars = plan.bars; p.part = plan.part; p.zero = plan.zero;
   // the packed index matrix as [N rows][K * bits / 8 bytes]; one box = one unit (16 rows x 128 k)
   CUtensorMap wmap;
   const uint64_t row_bytes = static_cast<uint64_t>(K) * w->bits / 8;
   const uint64_t dims[2] = {row_bytes, static_cast<uint64_t>(N)};
   const uint64_t strides[1] = {row_bytes};
-  const uint32_t box[2] = {static_cast<uint32_t>(kChunkK * w->bits / 8), 16u};
+  const uint32_t box[2] = {static_cast<uint32_t>(plan.bw * kChunkK * w->bits / 8), 16u};
   const int rc = encode_plain_tensor_map(&wmap, 1, 2, w->packed, dims, strides, box);
   if (rc != DIMQ_OK) return rc;
   const bool f16 = x_dtype == DIMQ_F16;
