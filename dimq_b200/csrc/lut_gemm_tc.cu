@@ -78,7 +78,7 @@ struct TcParams {
   int epi_tma, epi_res;       // epi_res: the residual is fetched with TMA too
   int cbw, cbh;               // pixels of one 32-pixel chunk along w and h (conv)
   int rep;                    // 1: every 128-row tile lies in one codebook group -> replicated tables
-  int dbg;                    // diagnostics: 1 skip epilogue work, 2 skip dequant work, 4 skip MMAs
+  int dbg;                    // measurement only (DIMQ_B200_TC_DEBUG): 2 skip the TMEM stores of the dequantisation, 4 skip MMAs, 8 skip the activation copies, 16 skip the lookups
   unsigned long long* prof;   // optional per-CTA wait-cycle counters (diagnostics), else null
 };
 
@@ -594,9 +594,6 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kAccCol + as * kTileX;
       const int n_chunks = (p.tx + 31) / 32;
-#pragma unroll 1
-      if (p.dbg & 1) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(smem_u32(&hdr->d_empty[as])); }
-      else
       if (sub >= n_chunks) {   // fewer chunks than warps: nothing to read, release at once
         tc_fence_before();
         __syncwarp();
