@@ -17,7 +17,7 @@ namespace dimq {
 bool tc_supported(const void* x, int x_dtype, const dimq_wq_weight* w, int64_t M, int64_t N, int64_t K);
 int launch_linear_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
                         const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K, int epilogue,
-                        int precision, cudaStream_t st);
+                        int precision, cudaStream_t st, void* workspace = nullptr, int64_t workspace_bytes = 0);
 bool conv_tc_supported(const void* x, int x_dtype, const dimq_wq_weight* w, const dimq_conv_geom* g, int y_dtype);
 int launch_conv2d_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
                         const void* residual, void* y, int y_dtype, const dimq_conv_geom* g, int epilogue,

@@ -21,7 +21,8 @@ int launch_linear_wq_mma_stream(const void* x, int x_dtype, const dimq_wq_weight
 bool tc_supported(const void* x, int x_dtype, const dimq_wq_weight* w, int64_t M, int64_t N, int64_t K);
 int launch_linear_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
                         const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K, int epilogue,
-                        int precision, cudaStream_t st);
+                        int precision, cudaStream_t st, void* workspace = nullptr, int64_t workspace_bytes = 0);
+int tc_split_k(int64_t M, int64_t N, int64_t K);
 bool conv_tc_supported(const void* x, int x_dtype, const dimq_wq_weight* w, const dimq_conv_geom* g, int y_dtype);
 int launch_conv2d_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
                         const void* residual, void* y, int y_dtype, const dimq_conv_geom* g, int epilogue,
@@ -98,6 +99,34 @@ extern "C" int dimq_linear_wq(const void* x, int x_dtype, const dimq_wq_weight* 
     default:
       return DIMQ_ERR_UNSUPPORTED;
   }
+}
+
+extern "C" int dimq_linear_wq_workspace_bytes(const void* x, int x_dtype, const dimq_wq_weight* w, int64_t M, int64_t N,
+                                              int64_t K, int64_t* bytes) {
+  if (bytes == nullptr || w == nullptr) return DIMQ_ERR_NULL_POINTER;
+  *bytes = 0;
+  if (M <= 0 || N <= 0 || K <= 0) return DIMQ_OK;
+  if (check_wq_weight(w, N) != DIMQ_OK) return DIMQ_OK;
+  // only where the automatic choice would take the tcgen05 kernel and splitting K pays
+  if (mma_stream_supported(x, x_dtype, w, M, N, K) || stream_supported(w, M, N, K)) return DIMQ_OK;
+  if (!tc_supported(x, x_dtype, w, M, N, K)) return DIMQ_OK;
+  if (tc_split_k(M, N, K) > 1) *bytes = M * N * 4;
+  return DIMQ_OK;
+}
+
+extern "C" int dimq_linear_wq_ws(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
+                                 const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K,
+                                 int epilogue, void* workspace, int64_t workspace_bytes, void* stream) {
+  int64_t need = 0;
+  if (w != nullptr && workspace != nullptr && M > 0 && N > 0 && K > 0 && valid_dtype(x_dtype) && valid_dtype(y_dtype) &&
+      (bias == nullptr || valid_dtype(bias_dtype)) && epilogue >= DIMQ_EPI_NONE && epilogue <= DIMQ_EPI_ADD_RELU &&
+      x != nullptr && y != nullptr &&
+      dimq_linear_wq_workspace_bytes(x, x_dtype, w, M, N, K, &need) == DIMQ_OK && need > 0) {
+    if (workspace_bytes < need) return DIMQ_ERR_SCRATCH_TOO_SMALL;
+    return launch_linear_wq_tc(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, 0,
+                               static_cast<cudaStream_t>(stream), workspace, workspace_bytes);
+  }
+  return dimq_linear_wq(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, DIMQ_ALGO_AUTO, stream);
 }
 
 extern "C" int dimq_conv2d_wq(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias,

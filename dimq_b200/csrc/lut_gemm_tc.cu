@@ -78,6 +78,9 @@ struct TcParams {
   int epi_tma, epi_res;       // epi_res: the residual is fetched with TMA too
   int cbw, cbh;               // pixels of one 32-pixel chunk along w and h (conv)
   int rep;                    // 1: every 128-row tile lies in one codebook group -> replicated tables
+  int ksplit;                 // K is cut into this many slices, one tile per (slice, n block, m block);
+                              // > 1: partial sums are added into `ws` instead of being stored
+  float* ws;                  // [M][N] fp32 workspace of the split-K mode (zeroed by the launcher)
   int dbg;                    // measurement only (DIMQ_B200_TC_DEBUG): 2 skip the TMEM stores of the dequantisation, 4 skip MMAs, 8 skip the activation copies, 16 skip the lookups
   unsigned long long* prof;   // optional per-CTA wait-cycle counters (diagnostics), else null
 };
@@ -381,8 +384,9 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
-  const int num_tiles = p.m_tiles * p.n_tiles;
-  const int k_blocks = static_cast<int>(p.K / kBlockK);
+  // tile t = (k slice * n_tiles + n block) * m_tiles + m block; one slice unless split-K is on
+  const int num_tiles = p.m_tiles * p.n_tiles * p.ksplit;
+  const int k_blocks = static_cast<int>(p.K / kBlockK) / p.ksplit;
   constexpr int kWStageCols = SPLIT ? kBlockK : kBlockK / 2;   // TMEM columns per weight stage
   constexpr uint32_t kWStagesUsed = SPLIT ? kWStages / 2 : kWStages;
 
@@ -448,6 +452,7 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
       const long long t_begin = clock64();
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         const int m_blk = t % p.m_tiles;
+        const int k0 = ((t / p.m_tiles) / p.n_tiles) * k_blocks;  // first k block of this tile's slice
         int ow0 = 0, oh0 = 0, b0 = 0, tap = 0, cb = 0;
         if (p.conv) {
           ow0 = (m_blk % p.tiles_w) * p.tw;
@@ -462,7 +467,7 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
             mbar_arrive(full);
           } else if (!p.conv) {
             mbar_arrive_expect_tx(full, p.x_stage_bytes);
-            tma_load_2d(dst, &tmaps.m[0], full, kb * kBlockK, m_blk * p.tx);
+            tma_load_2d(dst, &tmaps.m[0], full, (k0 + kb) * kBlockK, m_blk * p.tx);
           } else {
             // tap (kh, kw), channels [64 cb, 64 cb + 64): input pixel = s * out + tap offset.  With
             // stride 2 the input is addressed through one tensor map per (row, column) parity, so the
@@ -584,7 +589,7 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
     unsigned long long w_df = 0, t_ewait = 0, t_estage = 0;
     const long long t_begin = clock64();
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-      const int m_blk = t % p.m_tiles, n_blk = t / p.m_tiles;
+      const int m_blk = t % p.m_tiles, n_blk = (t / p.m_tiles) % p.n_tiles;
       const int64_t n = static_cast<int64_t>(n_blk) * kTileW + quarter * 32 + lane;
       const int64_t m0 = static_cast<int64_t>(m_blk) * p.tx;
       const bool n_ok = n < p.N;
@@ -663,7 +668,13 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
           const int64_t m_first = m0 + c * 32;
           const int64_t rows64 = p.M - m_first;
           const int rows = rows64 >= 32 ? 32 : static_cast<int>(rows64);
-          if (n_ok && rows > 0) {
+          if (n_ok && rows > 0 && p.ksplit > 1) {
+            // split-K: this tile holds the sum over one K slice only
+            float* wsp = p.ws + m_first * p.N + n;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < rows) atomicAdd(wsp + j * p.N, __uint_as_float(r[j]));
+          } else if (n_ok && rows > 0) {
             const int64_t off = m_first * p.N + n;
             if (p.y_dtype == DIMQ_BF16) store_chunk_t<__nv_bfloat16>(r, p.y, p.residual, off, p.N, rows, bias, p.epilogue);
             else if (p.y_dtype == DIMQ_F16) store_chunk_t<__half>(r, p.y, p.residual, off, p.N, rows, bias, p.epilogue);
@@ -708,7 +719,7 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
     uint32_t* my_rep = rep_tables + grp * kRepWords;
     const int gt = (dw & 3) * 32 + lane;            // thread index inside the group, 0..127
     auto row_of = [&](int t) -> int {
-      int row = (t / p.m_tiles) * kTileW + row_in_tile;
+      int row = ((t / p.m_tiles) % p.n_tiles) * kTileW + row_in_tile;
       return row >= n_rows ? n_rows - 1 : row;
     };
     auto advance = [&](int& t, int& kb, int steps) {
@@ -727,7 +738,8 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
     auto prefetch_next = [&]() {
       if (pf_j < n_own) {
         if (pf_tile != pf_row_tile) {
-          pf_row = p.packed + static_cast<int64_t>(row_of(pf_tile)) * row_bytes;
+          pf_row = p.packed + static_cast<int64_t>(row_of(pf_tile)) * row_bytes +
+                   static_cast<int64_t>((pf_tile / p.m_tiles) / p.n_tiles) * k_blocks * (8 * BITS);
           pf_row_tile = pf_tile;
         }
         issue_unit<BITS>(ring_u32 + pf_slot * kRingStride, pf_row + pf_kb * (8 * BITS));
@@ -765,7 +777,7 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
         if (rep) {
           // all 128 rows of the tile share codebook group g: (re)build this warp group's replicated
           // table, entry e copied kRep times so that lane l reads copy (l mod kRep) in its own bank
-          const int g0 = ((t / p.m_tiles) * kTileW) / group_rows;
+          const int g0 = (((t / p.m_tiles) % p.n_tiles) * kTileW) / group_rows;
           if (g0 != cur_group) {
             bar_sync(1 + grp, 128);
             const uint32_t* src = table + g0 * per_group;
@@ -986,7 +998,8 @@ int finish_launch(const TmapSet& tmaps, TcParams& p, const dimq_wq_weight* w, co
   if (const char* env = getenv("DIMQ_B200_TC_DEBUG")) p.dbg = atoi(env);
   if (const char* env = getenv("DIMQ_B200_PROFILE_PTR")) p.prof = reinterpret_cast<unsigned long long*>(strtoull(env, nullptr, 0));
   p.n_tiles = static_cast<int>((p.N + kTileW - 1) / kTileW);
-  const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
+  if (p.ksplit < 1) p.ksplit = 1;
+  const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.ksplit;
   if (tiles >= 0x7FFFFFFF) return DIMQ_ERR_TOO_LARGE;
   const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
 
@@ -1021,9 +1034,44 @@ int finish_launch(const TmapSet& tmaps, TcParams& p, const dimq_wq_weight* w, co
 
 }  // namespace
 
+// Split-K factor for a GEMM whose tiles would leave most SMs idle while each CTA walks a long K:
+// a power of two that divides the k blocks, leaves at least four k blocks per slice and does not
+// create more tiles than SMs.  1 = do not split.
+int tc_split_k(int64_t M, int64_t N, int64_t K) {
+  int tx = kTileX;
+  {
+    double best = -1.0;
+    for (int c = 32; c <= kTileX; c += 32) {
+      const double covered = static_cast<double>((M + c - 1) / c) * c;
+      const double score = static_cast<double>(M) / covered * c / (c > 96 ? c : 96);
+      if (score >= best) { best = score; tx = c; }
+    }
+  }
+  const int64_t tiles = ((M + tx - 1) / tx) * ((N + kTileW - 1) / kTileW);
+  const int64_t kb = K / kBlockK;
+  int s = 1;
+  while (s < 16 && tiles * (s * 2) <= kNumSMs && kb % (s * 2) == 0 && kb / (s * 2) >= 4) s *= 2;
+  return s >= 4 ? s : 1;  // a two-way split does not pay for the zeroing and the finishing kernel
+}
+
+namespace {
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+splitk_finish_kernel(const float* __restrict__ ws, const void* __restrict__ bias, int bias_dtype,
+                     const T* __restrict__ residual, T* __restrict__ y, int64_t total, int64_t N, int epilogue) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= total) return;
+  const float v = ws[i] + (bias != nullptr ? load_as_float(bias, bias_dtype, i % N) : 0.0f);
+  const float res = residual != nullptr ? to_float<T>(residual[i]) : 0.0f;
+  y[i] = from_float<T>(finish_value(v, epilogue, residual != nullptr, res));
+}
+
+}  // namespace
+
 int launch_linear_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
                         const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K, int epilogue,
-                        int precision, cudaStream_t st) {
+                        int precision, cudaStream_t st, void* workspace = nullptr, int64_t workspace_bytes = 0) {
   if (!tc_supported(x, x_dtype, w, M, N, K)) return DIMQ_ERR_UNSUPPORTED;
   EncodeTiledFn encode = get_encode_tiled();
   if (encode == nullptr) return DIMQ_ERR_DRIVER;
@@ -1054,6 +1102,32 @@ int launch_linear_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, con
   p.K = K;
   p.tx = tx_best;
   p.m_tiles = static_cast<int>((M + tx_best - 1) / tx_best);
+  const int ksplit = workspace != nullptr ? tc_split_k(M, N, K) : 1;
+  if (ksplit > 1) {
+    // partial sums of the K slices meet in the caller's fp32 workspace; a second small kernel applies
+    // bias / epilogue / residual and writes y
+    if (workspace_bytes < M * N * 4) return DIMQ_ERR_SCRATCH_TOO_SMALL;
+    if (!aligned(workspace, 16)) return DIMQ_ERR_ALIGNMENT;
+    cudaError_t e = cudaMemsetAsync(workspace, 0, static_cast<size_t>(M) * N * 4, st);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    p.ksplit = ksplit;
+    p.ws = static_cast<float*>(workspace);
+    int rc = finish_launch(tmaps, p, w, w->packed, x_dtype, nullptr, 0, nullptr, y, y_dtype, DIMQ_EPI_NONE, precision, st);
+    if (rc != DIMQ_OK) return rc;
+    const int64_t total = M * N;
+    const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+    if (y_dtype == DIMQ_F32)
+      splitk_finish_kernel<float><<<blocks, 256, 0, st>>>(p.ws, bias, bias_dtype, static_cast<const float*>(residual),
+                                                          static_cast<float*>(y), total, N, epilogue);
+    else if (y_dtype == DIMQ_F16)
+      splitk_finish_kernel<__half><<<blocks, 256, 0, st>>>(p.ws, bias, bias_dtype, static_cast<const __half*>(residual),
+                                                           static_cast<__half*>(y), total, N, epilogue);
+    else
+      splitk_finish_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(p.ws, bias, bias_dtype,
+                                                                  static_cast<const __nv_bfloat16*>(residual),
+                                                                  static_cast<__nv_bfloat16*>(y), total, N, epilogue);
+    return launch_status();
+  }
   if (epi_tma_possible(y, y_dtype, residual, N)) {
     const cuuint64_t odims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M)};
     const cuuint32_t obox[2] = {32, 32};

@@ -510,6 +510,23 @@ def dimq_linear_wq(x: torch.Tensor, packed_weight: torch.Tensor, codebooks: torc
         if residual.dtype != out_dtype or residual.numel() != y.numel():
             raise RuntimeError("residual must match the output shape and dtype")
         res = residual.contiguous()
+    if algo is None:
+        # shapes that would fill only a few SMs with long-K tiles get a workspace: the kernel splits K
+        need = C.c_int64(0)
+        _lib.lib().dimq_linear_wq_workspace_bytes(_lib.ptr(xc), _lib.dtype_code(xc, "x"), C.byref(w), C.c_int64(m),
+                                                  C.c_int64(out_features), C.c_int64(in_features), C.byref(need))
+        if need.value > 0:
+            ws = torch.empty(need.value, dtype=torch.uint8, device=xc.device)
+            with torch.cuda.device(xc.device):
+                st = _lib.lib().dimq_linear_wq_ws(_lib.ptr(xc), _lib.dtype_code(xc, "x"), C.byref(w), _lib.ptr(b), b_dt,
+                                                  _lib.ptr(res), _lib.ptr(y), _lib.dtype_code(y, "y"), C.c_int64(m),
+                                                  C.c_int64(out_features), C.c_int64(in_features),
+                                                  _EPILOGUES[epilogue], _lib.ptr(ws), C.c_int64(need.value),
+                                                  _lib.stream_ptr(xc.device))
+            _lib.check(st, "linear_wq_ws")
+            _lib.LAUNCH_COUNT[0] += 1  # the GEMM and the kernel that finishes the sums
+            del keep
+            return y.view(*x.shape[:-1], out_features)
     with torch.cuda.device(xc.device):
         st = _lib.lib().dimq_linear_wq(_lib.ptr(xc), _lib.dtype_code(xc, "x"), C.byref(w), _lib.ptr(b), b_dt,
                                        _lib.ptr(res), _lib.ptr(y), _lib.dtype_code(y, "y"), C.c_int64(m),

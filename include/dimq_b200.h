@@ -192,6 +192,19 @@ DIMQ_API int dimq_conv2d_wq_static(const void* x, int x_dtype, const dimq_wq_wei
                                    int bias_dtype, const void* residual, void* y, int y_dtype,
                                    const dimq_conv_geom* geom, int epilogue, void* stream);
 
+/* dimq_linear_wq with a caller-owned fp32 workspace, for shapes whose tiles would occupy only a few
+ * SMs while each walks a long K (a few hundred activation rows against a wide-K weight): the tcgen05
+ * kernel then cuts K into slices (split-K), adds the partial sums into the workspace and a second
+ * small kernel applies bias / epilogue / residual.  dimq_linear_wq_workspace_bytes reports M*N*4 when
+ * that path would be taken and 0 otherwise (then this call is dimq_linear_wq with DIMQ_ALGO_AUTO and
+ * the workspace is not touched).  The sum over slices uses float atomics: the result can differ in
+ * the last bits from run to run.  No counterpart in the reference. */
+DIMQ_API int dimq_linear_wq_workspace_bytes(const void* x, int x_dtype, const dimq_wq_weight* w, int64_t M, int64_t N,
+                                            int64_t K, int64_t* bytes);
+DIMQ_API int dimq_linear_wq_ws(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
+                               const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K,
+                               int epilogue, void* workspace, int64_t workspace_bytes, void* stream);
+
 /* ---- W4A4 product-table ops on the tensor cores ------------------------- */
 
 /* Same operation as dimq_linear_lut / dimq_conv2d_lut (csrc/dimq_gemm_lut.cu:58-117,

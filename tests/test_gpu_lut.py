@@ -398,6 +398,48 @@ def test_linear_wq_tcgen05_dtypes_epilogues(ops, x_dtype, y_dtype):
         assert max_abs <= tol * 3 and rel <= (5e-3 if y_dtype == torch.bfloat16 else REL_L2), (epi, max_abs, rel)
 
 
+@pytest.mark.parametrize("y_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("m,k,n,bits,grp", [(64, 4096, 1024, 4, None), (256, 4096, 1024, 3, 128), (100, 2048, 384, 2, None),
+                                            (200, 1024, 130, 4, None)])
+def test_linear_wq_split_k(ops, m, k, n, bits, grp, y_dtype):
+    """Few output tiles and a long K: the automatic choice hands the tcgen05 kernel a workspace and it
+    splits K; bias, epilogue and residual are applied by the finishing kernel."""
+    import ctypes as C
+
+    from dimq_b200 import _lib
+
+    case = make_weight(n, k, bits, seed=bits + m, group_rows=grp, cb_dtype="bf16")
+    rng = np.random.default_rng(m + n)
+    x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(torch.bfloat16)
+    bias = rng.standard_normal(n).astype(np.float32)
+    res = torch.from_numpy(rng.standard_normal((m, n)).astype(np.float32)).to(y_dtype)
+    lin = o.linear_wq(x.float().numpy(), case["packed"], case["codebooks"], bits, n, k, bias, case["group_rows"])
+    xc, pw, cb = x.cuda(), _cuda(case["packed"]), _cuda(case["codebooks"], torch.bfloat16)
+    w, keep = ops._wq_weight(pw, cb, bits, n, n * k, grp)
+    need = C.c_int64(0)
+    assert _lib.lib().dimq_linear_wq_workspace_bytes(_lib.ptr(xc), 2, C.byref(w), C.c_int64(m), C.c_int64(n),
+                                                     C.c_int64(k), C.byref(need)) == 0
+    assert need.value == m * n * 4, "this shape is expected to take the split-K path"
+    before = _lib.LAUNCH_COUNT[0]
+    got = ops.dimq_linear_wq(xc, pw, cb, _cuda(bias), n, k, bits=bits, group_rows=grp, out_dtype=y_dtype)
+    assert _lib.LAUNCH_COUNT[0] - before == 2
+    assert ops.last_device_status() == 0
+    max_abs, rel = o.parity_metrics(got.float().cpu().numpy(), lin)
+    assert max_abs <= (3e-2 if y_dtype == torch.bfloat16 else MAX_ABS) and rel <= (5e-3 if y_dtype == torch.bfloat16 else REL_L2), (max_abs, rel)
+    # the same numbers as the unsplit kernel up to the order of the fp32 additions
+    ref = ops.dimq_linear_wq(xc, pw, cb, _cuda(bias), n, k, bits=bits, group_rows=grp, out_dtype=torch.float32,
+                             algo="tcgen05")
+    got32 = ops.dimq_linear_wq(xc, pw, cb, _cuda(bias), n, k, bits=bits, group_rows=grp, out_dtype=torch.float32)
+    assert float((got32 - ref).abs().max()) <= 1e-3
+    # epilogue and residual in the finishing kernel
+    want = np.maximum(lin + res.float().numpy(), 0)
+    got = ops.dimq_linear_wq(xc, pw, cb, _cuda(bias), n, k, bits=bits, group_rows=grp, out_dtype=y_dtype,
+                             epilogue="add_relu", residual=res.cuda())
+    max_abs, rel = o.parity_metrics(got.float().cpu().numpy(), want)
+    assert rel <= (5e-3 if y_dtype == torch.bfloat16 else REL_L2), (max_abs, rel)
+    del keep
+
+
 @pytest.mark.parametrize("bits", [2, 3, 4])
 @pytest.mark.parametrize("k,n", [(1024, 4096), (4096, 1024)])
 @pytest.mark.parametrize("m", [1, 4, 16, 64, 256, 4096])
