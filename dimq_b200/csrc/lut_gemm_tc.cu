@@ -1051,7 +1051,8 @@ int tc_split_k(int64_t M, int64_t N, int64_t K) {
   const int64_t kb = K / kBlockK;
   int s = 1;
   while (s < 16 && tiles * (s * 2) <= kNumSMs && kb % (s * 2) == 0 && kb / (s * 2) >= 4) s *= 2;
-  return s >= 4 ? s : 1;  // a two-way split does not pay for the zeroing and the finishing kernel
+  // a two-way split pays for the zeroing and the finishing kernel only when K is long
+  return (s >= 4 || (s == 2 && kb >= 32)) ? s : 1;
 }
 
 namespace {
