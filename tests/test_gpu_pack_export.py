@@ -136,6 +136,42 @@ def test_hard_quantize_adversarial(ops, golden, book):
     assert np.array_equal(idx.cpu().numpy(), golden[f"hq_adv_{book}_idx"])
 
 
+@pytest.mark.parametrize("entries", [1, 2, 3, 5, 8, 12, 16, 37, 200, 256])
+@pytest.mark.parametrize("kind", ["normal", "dups", "tiny", "huge", "zeros", "grid"])
+def test_hard_quantize_sorted_codebook_search(ops, entries, kind):
+    """Sorted finite codebooks take the bisection path; it must give the scan's answer bit for bit:
+    duplicates, exact midpoints, weights equal to codewords, denormal and overflowing distances,
+    signed zeros, non-finite weights, codeword counts that are not powers of two."""
+    from oracle import c_oracle
+
+    rng = np.random.default_rng(entries * 7 + len(kind))
+    if kind == "normal":
+        cb = np.sort(rng.standard_normal(entries).astype(np.float32) * 0.05)
+    elif kind == "dups":
+        cb = np.sort(rng.choice(np.array([-0.5, -0.25, 0.0, 0.25, 0.5], np.float32), entries))
+    elif kind == "tiny":
+        cb = np.sort((rng.integers(-20, 20, entries) * np.float32(1e-44)).astype(np.float32))  # denormals
+    elif kind == "huge":
+        cb = np.sort((rng.standard_normal(entries) * 1e38).astype(np.float32))
+        cb = np.clip(cb, -3.0e38, 3.0e38)
+    elif kind == "zeros":
+        cb = np.sort(np.concatenate([np.full(entries // 2, -0.0, np.float32), np.zeros(entries - entries // 2, np.float32)]))
+    else:
+        cb = (np.arange(entries, dtype=np.float32) - entries // 2) * np.float32(0.125)
+    cb = cb.astype(np.float32)
+    mids = (cb[:-1] + cb[1:]) / 2 if entries > 1 else cb
+    special = np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 3.4e38, -3.4e38, 1e-45, -1e-45], np.float32)
+    scale = np.float32(max(float(np.abs(cb).max()), 1e-3) * 1.5)
+    w = np.concatenate([cb, mids, np.nextafter(mids, np.float32(np.inf)), np.nextafter(mids, np.float32(-np.inf)),
+                        special, (rng.standard_normal(4096) * scale).astype(np.float32)]).astype(np.float32)
+    w = np.resize(w, (w.size + 7) // 8 * 8).reshape(-1, 8)
+    want = c_oracle.hard_quantize(w, cb[None, :], w.shape[0])
+    idx, _ = ops.hard_quantize(_cuda(w), _cuda(cb))
+    got = idx.cpu().numpy()
+    bad = np.argwhere(got != want)
+    assert bad.size == 0, (kind, entries, w[tuple(bad[0])], got[tuple(bad[0])], want[tuple(bad[0])], cb)
+
+
 def test_hard_quantize_reference_unit_case_and_wrapper(ops, golden):
     from dimq_b200.export import hard_quantize_weight
 
