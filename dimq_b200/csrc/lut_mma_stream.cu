@@ -1,30 +1,34 @@
 // Small-M weight-only LUT GEMM for 16-bit activations (M <= 32): the index-streaming regime.
 //
-// The packed indices are read from HBM exactly once: TMA box copies (16 rows x 128 k per unit) land in
-// a per-warp ring in shared memory, several units ahead of the arithmetic.  (A first version loaded
-// the indices with per-lane vector loads into a register ring; with the shared-memory carve-out this
-// kernel needs, the few loads the L1 could keep in flight capped it near 1.5 TB/s whatever the
-// arithmetic did.  Bulk copies do not pass through L1.)  The work per weight is one table lookup for every TWO weights (four at 2 bits) and
-// a share of a warp-level mma.sync, which stands in for the M fused multiply-adds per weight that a
-// SIMT kernel cannot issue fast enough beyond M = 2.  The tensor pipe is nowhere near busy here: the
-// kernel is bound by HBM and by shared-memory lookups, so the warp-level MMA is the right tool and
-// the tcgen05 path (which would need the weights staged as operands) is not.
+// The packed indices are read from HBM exactly once: TMA box copies (16 rows x 128..512 k) land in a
+// per-warp ring in shared memory, several boxes ahead of the arithmetic; lane 0 of the warp re-arms a
+// slot as soon as the warp has copied its words out of it.  The work per weight is one table lookup
+// for every TWO weights (four at 2 bits) and a share of a warp-level mma.sync, which stands in for the
+// M fused multiply-adds per weight that a SIMT kernel cannot issue fast enough beyond M = 2.  The
+// tensor pipe is nowhere near busy here: the kernel is bound by the index stream, the shared-memory
+// lookups and instruction issue, so the warp-level MMA is the right tool and the tcgen05 path (which
+// would need the weights staged as operands) is not.
 //
 // Work unit: 16 output rows x 128 k.  Lane (g = lane / 4, t = lane % 4) of a warp takes, for rows g
 // and g + 8 of the block, the 32 consecutive indices k = 32 t .. 32 t + 31 of the chunk (16 B at
-// 4 bits, 12 B at 3 bits, 8 B at 2 bits) out of the unit's ring slot.  Because a dot
-// product does not care about the order of k, MMA step s (of 8) takes from every lane its indices
-// 4 s .. 4 s + 3: the A fragment registers a0/a2 (row g) and a1/a3 (row g + 8) each hold two
-// k-adjacent codewords, which is exactly one entry of a PAIR table indexed by the two packed indices
-// (one byte of a 4-bit stream, six bits of a 3-bit stream; at 2 bits one byte gives a0 and a2
-// together).  The pair table is stored once per lane ([entry][lane]), so a lookup never has a bank
-// conflict whatever the indices are.  The matching B fragment is x[m = g][32 t + 4 s .. + 3]: one
-// 8-byte read of the activations, staged in shared memory in an order ([chunk][s][t][4]) and with a
-// row stride (2 K + 32 bytes) that put the 16 lanes of a half-warp on distinct banks.
+// 4 bits, 12 B at 3 bits, 8 B at 2 bits) out of the unit's ring slot.  Because a dot product does not
+// care about the order of k, MMA step s (of 8) takes from every lane its indices 4 s .. 4 s + 3: the
+// A fragment registers a0/a2 (row g) and a1/a3 (row g + 8) each hold two k-adjacent codewords, which
+// is exactly one entry of a PAIR table indexed by the two packed indices (one byte of a 4-bit stream,
+// six bits of a 3-bit stream; at 2 bits one byte gives a0 and a2 together).  The pair table is stored
+// once per lane ([entry][lane]), so a lookup never has a bank conflict whatever the indices are, and
+// it sits on a boundary of its own size, so a lookup address is (index bits masked in place) | base.
+// The matching B fragments of two steps are x[m = g][32 t + 8 (s / 2) .. + 7]: one 16-byte read of the
+// activations, staged in shared memory in [chunk][s / 2][t][8] order with a row stride of 2 K + 64
+// bytes, which puts the eight lanes of a quarter-warp on distinct banks; MMA columns beyond M read a
+// chunk of zeros.
 //
-// A CTA (16 warps) works on G row blocks at a time and deals their (block, chunk) units round-robin
-// to its warps; partial sums meet in a double-buffered shared-memory accumulator with one
-// __syncthreads per iteration, after which bias / epilogue / residual are applied and y is stored.
+// A CTA has 16 compute warps and 2 write-back warps.  It works on G row blocks at a time (G > 1 only
+// when K has fewer than 16 chunks); every compute warp owns a fixed run of k chunks of one of them,
+// so a unit costs a pointer increment.  The partial sums of a row block's warps go to per-warp
+// buffers (double-buffered); after one __syncthreads per iteration the write-back warps add them,
+// apply bias / epilogue / residual and store y while the compute warps are already on the next row
+// blocks.  Every wait on a ring slot is bounded; a warp that gives up sets a flag and a status word.
 #include <cuda.h>
 
 #include <cstdlib>

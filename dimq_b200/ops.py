@@ -141,8 +141,9 @@ _UNSUPPORTED = -7
 
 def _a4_workspace(x_numel: int, conv_weight_numel: int, device: torch.device) -> torch.Tensor:
     need = C.c_int64(0)
-    _lib.check(_lib.lib().dimq_a4_workspace_bytes(C.c_int64(x_numel), C.c_int64(conv_weight_numel), C.byref(need)),
-               "last_device_status")
+    st = _lib.lib().dimq_a4_workspace_bytes(C.c_int64(x_numel), C.c_int64(conv_weight_numel), C.byref(need))
+    if st != 0:
+        raise RuntimeError(f"dimq_b200.a4_workspace_bytes failed (status {st})")
     return torch.empty(need.value, dtype=torch.uint8, device=device)
 
 
