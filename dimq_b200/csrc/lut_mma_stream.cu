@@ -321,15 +321,24 @@ linear_wq_mma_stream_kernel(const __grid_constant__ CUtensorMap wmap, const MsPa
       else cb_s[tid] = tid < p.entries ? load_as_float(p.codebooks, p.cb_dtype, group * p.entries + tid) : 0.0f;
     }
     __syncthreads();
-    for (int wi = tid; wi < C::kTableEntries * 32; wi += kThreads) {
-      const int e = wi >> 5;
-      if constexpr (BITS == 2) {
+    // 16 bytes per store: four lanes' copies of an entry (two at 2 bits, where an entry is 8 bytes)
+    uint4* table4 = reinterpret_cast<uint4*>(table);
+    if constexpr (BITS == 2) {
+#pragma unroll 2
+      for (int wi = tid; wi < C::kTableEntries * 16; wi += kThreads) {
+        const int e = wi >> 4;
         uint32_t h[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) h[j] = to_operand<F16>(cb_s[(e >> (2 * j)) & 3]);
-        reinterpret_cast<uint2*>(table)[wi] = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
-      } else {
-        table[wi] = to_operand<F16>(cb_s[e & ((1 << BITS) - 1)]) | (to_operand<F16>(cb_s[e >> BITS]) << 16);
+        const uint32_t a = h[0] | (h[1] << 16), b = h[2] | (h[3] << 16);
+        table4[wi] = make_uint4(a, b, a, b);
+      }
+    } else {
+#pragma unroll 2
+      for (int wi = tid; wi < C::kTableEntries * 8; wi += kThreads) {
+        const int e = wi >> 3;
+        const uint32_t v = to_operand<F16>(cb_s[e & ((1 << BITS) - 1)]) | (to_operand<F16>(cb_s[e >> BITS]) << 16);
+        table4[wi] = make_uint4(v, v, v, v);
       }
     }
   };
