@@ -229,9 +229,10 @@ hard_quantize_kernel(const T* __restrict__ w, int64_t n, int64_t cols, const flo
   const int64_t last = (base + 7 < n ? base + 7 : n - 1);
   const int64_t g_last = (last / cols) / group_rows;
   uint32_t r[8];
-  // (measured: the bisection's dependent shared-memory reads lose against the plain scan up to 16
-  // codewords and win 3.6x at 256)
-  if (g_first == g_last && use_smem && entries > 16 && sorted_s[g_first]) {
+  // From 9 to 16 codewords the position of w is counted with one comparison per codeword (the
+  // codeword is a broadcast read shared by the thread's eight weights); above, by bisection; up to 8
+  // codewords the plain scan below is faster (measured).
+  if (g_first == g_last && use_smem && entries > 8 && sorted_s[g_first]) {
     // Sorted finite codebook.  d(k) = fl(fl(w - c[k])^2) does not increase up to the last c[k] < w and
     // does not decrease from the first c[k] >= w on (rounding is monotone), so the minimum is at one of
     // the two entries around w; equal distances form a contiguous run, and the scan's "first minimum"
@@ -239,15 +240,28 @@ hard_quantize_kernel(const T* __restrict__ w, int64_t n, int64_t cols, const flo
     // finite codeword: index 0, as the scan gives.
     const float* cb = cb_s + g_first * entries;
     const int top = 1 << (31 - __clz(entries));
+    int below[8];  // number of codewords below the weight
+#pragma unroll
+    for (int i = 0; i < 8; ++i) below[i] = 0;
+    if (entries <= 16) {
+#pragma unroll 4
+      for (int k = 0; k < entries; ++k) {
+        const float c = cb[k];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) below[i] += c < f[i] ? 1 : 0;
+      }
+    }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const float wv = f[i];
       uint32_t bi = 0u;
       if (isfinite(wv)) {
-        int pos = 0;  // number of codewords below wv
-        for (int step = top; step > 0; step >>= 1) {
-          const int q = pos + step;
-          if (q <= entries && cb[q - 1] < wv) pos = q;
+        int pos = below[i];
+        if (entries > 16) {
+          for (int step = top; step > 0; step >>= 1) {
+            const int q = pos + step;
+            if (q <= entries && cb[q - 1] < wv) pos = q;
+          }
         }
         const int lo = pos > 0 ? pos - 1 : 0;
         const int hi = pos < entries ? pos : entries - 1;
