@@ -162,6 +162,88 @@ im2col_kernel(const T* __restrict__ x, T* __restrict__ cols, dimq_conv_geom g, i
   reinterpret_cast<uint4*>(cols)[i] = out;
 }
 
+// The same matrix through a shared-memory patch, persistent blocks.  Block (kp / 8, pixels per
+// chunk); a block walks over output rows (b, oh) and, inside a row, over chunks of pixels: it loads the
+// input window of the chunk ([C][KH][win_w], read along w, zeros outside the image), then every
+// thread gathers its eight columns from the patch and writes 16 bytes.  Everything that needs a
+// division (column -> patch offset, patch element -> (channel, kernel row, column)) is worked out once
+// per block / thread, outside the loops.
+constexpr int kPatchPerThread = 4;
+constexpr int kPixelGroups = 1;  // pixel groups (of blockDim.y pixels) per chunk; more per barrier pair measured slower
+template <typename T>
+__global__ void __launch_bounds__(kAuxThreads)
+im2col_patch_kernel(const T* __restrict__ x, T* __restrict__ cols, dimq_conv_geom g, int kp, int win_w) {
+  extern __shared__ int col_tbl[];  // [kp] patch offset of column k (or -1), then the patch
+  T* patch = reinterpret_cast<T*>(col_tbl + kp);
+  const int C = g.in_channels, KH = g.kernel_h, KW = g.kernel_w, k_real = KH * KW * C;
+  const int threads = blockDim.x * blockDim.y;
+  const int tid = threadIdx.y * blockDim.x + threadIdx.x;
+  for (int k = tid; k < kp; k += threads) {
+    int off = -1;
+    if (k < k_real) {
+      const int c = k % C, tap = k / C;
+      off = (c * KH + tap / KW) * win_w + (tap % KW) * g.dilation_w;
+    }
+    col_tbl[k] = off;
+  }
+  // this thread's patch elements: idx = tid + i * threads -> (channel, kernel row, column j)
+  const int patch_elems = C * KH * win_w;
+  int p_dh[kPatchPerThread], p_j[kPatchPerThread];
+  int64_t p_off[kPatchPerThread];
+#pragma unroll
+  for (int i = 0; i < kPatchPerThread; ++i) {
+    const int idx = tid + i * threads;
+    p_dh[i] = -1;
+    p_j[i] = 0;
+    p_off[i] = 0;
+    if (idx < patch_elems) {
+      const int r = idx / win_w, j = idx - r * win_w;
+      const int c = r / KH, kh = r - c * KH;
+      p_dh[i] = kh * g.dilation_h;
+      p_j[i] = j;
+      p_off[i] = c * g.x_stride[1] + static_cast<int64_t>(p_dh[i]) * g.x_stride[2] + j * g.x_stride[3];
+    }
+  }
+  const int px = blockDim.y * kPixelGroups, v = threadIdx.x;
+  const int vec = kp / 8;
+  const int64_t n_rows = static_cast<int64_t>(g.batch) * g.out_h;
+  for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
+    const int b = static_cast<int>(row / g.out_h), oh = static_cast<int>(row - static_cast<int64_t>(b) * g.out_h);
+    const int ih0 = oh * g.stride_h - g.pad_h;
+    const T* xr = x + static_cast<int64_t>(b) * g.x_stride[0] + static_cast<int64_t>(ih0) * g.x_stride[2];
+    for (int ow0 = 0; ow0 < g.out_w; ow0 += px) {
+      const int iw0 = ow0 * g.stride_w - g.pad_w;
+      __syncthreads();  // the previous chunk's gathers are done (and, the first time, the table is written)
+#pragma unroll
+      for (int i = 0; i < kPatchPerThread; ++i) {
+        if (p_dh[i] >= 0) {
+          const int ih = ih0 + p_dh[i], iw = iw0 + p_j[i];
+          T val = from_float<T>(0.0f);
+          if (ih >= 0 && ih < g.in_h && iw >= 0 && iw < g.in_w) val = xr[p_off[i] + static_cast<int64_t>(iw0) * g.x_stride[3]];
+          patch[tid + i * threads] = val;
+        }
+      }
+      __syncthreads();
+#pragma unroll
+      for (int r = 0; r < kPixelGroups; ++r) {
+        const int pl = threadIdx.y + r * blockDim.y;  // pixel inside the chunk
+        const int ow = ow0 + pl;
+        if (ow < g.out_w) {
+          const int shift = pl * g.stride_w;
+          uint4 out;
+          T* o = reinterpret_cast<T*>(&out);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int off = col_tbl[v * 8 + e];
+            o[e] = off >= 0 ? patch[off + shift] : from_float<T>(0.0f);
+          }
+          reinterpret_cast<uint4*>(cols)[(row * g.out_w + ow) * vec + v] = out;
+        }
+      }
+    }
+  }
+}
+
 // y[b][oh][ow][c] = max over the window of x[b][ih][iw][c], NHWC 16-bit, 8 channels per thread.
 template <typename T>
 __global__ void __launch_bounds__(kAuxThreads)
@@ -218,6 +300,31 @@ extern "C" int dimq_im2col(const void* x, int dtype, const dimq_conv_geom* geom,
   const int64_t blocks = (total + kAuxThreads - 1) / kAuxThreads;
   if (blocks > 0x7FFFFFFFll) return DIMQ_ERR_TOO_LARGE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  {
+    // shared-memory patch variant when the launch geometry can carry the output position and the
+    // window of a block's pixels is small
+    const int vec = static_cast<int>(padded_k / 8);
+    if (vec <= kAuxThreads) {
+      const int px = kAuxThreads / vec;
+      const int64_t win_w = static_cast<int64_t>(px * kPixelGroups - 1) * g.stride_w + static_cast<int64_t>(g.kernel_w - 1) * g.dilation_w + 1;
+      const int64_t patch_elems = static_cast<int64_t>(g.in_channels) * g.kernel_h * win_w;
+      if (patch_elems <= static_cast<int64_t>(kPatchPerThread) * vec * px) {
+        const int64_t n_rows = static_cast<int64_t>(g.batch) * g.out_h;
+        const int64_t want = static_cast<int64_t>(kNumSMs) * 8;
+        const dim3 block(vec, px), grid(static_cast<unsigned>(n_rows < want ? n_rows : want));
+        const size_t smem = padded_k * sizeof(int) + static_cast<size_t>(patch_elems) * 2;
+        if (dtype == DIMQ_BF16)
+          im2col_patch_kernel<__nv_bfloat16><<<grid, block, smem, st>>>(static_cast<const __nv_bfloat16*>(x),
+                                                                        static_cast<__nv_bfloat16*>(cols), g,
+                                                                        static_cast<int>(padded_k), static_cast<int>(win_w));
+        else
+          im2col_patch_kernel<__half><<<grid, block, smem, st>>>(static_cast<const __half*>(x),
+                                                                 static_cast<__half*>(cols), g,
+                                                                 static_cast<int>(padded_k), static_cast<int>(win_w));
+        return launch_status();
+      }
+    }
+  }
   if (dtype == DIMQ_BF16)
     im2col_kernel<__nv_bfloat16><<<(unsigned)blocks, kAuxThreads, padded_k * sizeof(int), st>>>(
         static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(cols), g, static_cast<int>(padded_k));
