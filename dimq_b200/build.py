@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import os
 import shutil
+import sys
 import subprocess
 from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
@@ -37,17 +38,28 @@ def _stale() -> bool:
     return newest > LIB.stat().st_mtime
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every kernel source and link the shared library (no-op when up to date)."""
+def build(force: bool = False, verbose: bool = False, diag: bool = False) -> Path:
+    """Compile every kernel source and link the shared library (no-op when up to date).
+
+    ``diag=True`` builds ``libdimq_b200_diag.so`` instead: the same library with
+    ``-DDIMQ_B200_DIAG`` (per-role cycle counters and role-skipping switches of the
+    tcgen05 kernel, set through ``dimq_diag_configure``).  Nothing in the package
+    loads that file; it is for kernel development.
+    """
+    if diag:
+        return _build(PKG / "libdimq_b200_diag.so", PKG / "build_diag", ["-DDIMQ_B200_DIAG"], verbose)
     if not force and not _stale():
         return LIB
+    return _build(LIB, PKG / "build", [], verbose)
+
+
+def _build(lib: Path, objdir: Path, extra: list[str], verbose: bool) -> Path:
     nvcc = _nvcc()
-    objdir = PKG / "build"
     objdir.mkdir(exist_ok=True)
 
     def compile_one(src: str) -> Path:
         obj = objdir / (src + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-c", str(CSRC / src), "-o", str(obj)]
+        cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", str(CSRC / src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         res = subprocess.run(cmd, capture_output=True, text=True)
@@ -59,12 +71,12 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
         objs = list(pool.map(compile_one, SOURCES))
-    cmd = [nvcc, "-shared", "-o", str(LIB), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"]
+    cmd = [nvcc, "-shared", "-o", str(lib), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
-    print(build(force=True, verbose=bool(os.environ.get("DIMQ_BUILD_VERBOSE"))))
+    print(build(force=True, verbose=bool(os.environ.get("DIMQ_BUILD_VERBOSE")), diag="--diag" in sys.argv))

@@ -33,6 +33,15 @@ int read_ms_status(uint32_t* status);
 
 using namespace dimq;
 
+#ifdef DIMQ_B200_DIAG
+namespace dimq { void diag_configure(int dbg, int rep, unsigned long long* prof, int64_t prof_words); }
+// Diagnostics build only (not declared in the public header).
+extern "C" __attribute__((visibility("default"))) int dimq_diag_configure(int dbg, int rep, void* prof, int64_t prof_words) {
+  diag_configure(dbg, rep, static_cast<unsigned long long*>(prof), prof_words);
+  return DIMQ_OK;
+}
+#endif
+
 extern "C" int dimq_version(void) { return 100; }
 
 extern "C" const char* dimq_status_string(int status) {
@@ -94,8 +103,10 @@ extern "C" int dimq_linear_wq(const void* x, int x_dtype, const dimq_wq_weight* 
       return launch_linear_wq_mma_stream(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, st);
     case DIMQ_ALGO_TCGEN05:
       return launch_linear_wq_tc(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, 0, st);
-    case DIMQ_ALGO_TCGEN05 + 100:  // codewords rounded to the activations' 16-bit format, never split (measurement only)
+#ifdef DIMQ_B200_DIAG
+    case DIMQ_ALGO_TCGEN05 + 100:  // codewords rounded to the activations' 16-bit format, never split
       return launch_linear_wq_tc(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, 1, st);
+#endif
     default:
       return DIMQ_ERR_UNSUPPORTED;
   }

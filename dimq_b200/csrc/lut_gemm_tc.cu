@@ -16,9 +16,14 @@
 // column = activation row m, so each epilogue warp store writes 32 consecutive n
 // of one m (a 128-byte segment in fp32).
 //
-// Warp roles (448 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM
-// allocator, warps 2-5 epilogue, warps 6-13 dequantisation.  Persistent grid:
-// one CTA per SM walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...
+// Warp roles (576 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM
+// allocator, warps 2-9 epilogue (two per TMEM lane quarter), warps 10-17
+// dequantisation (two groups of four).  Persistent grid: one CTA per SM walks
+// tiles blockIdx.x, blockIdx.x + gridDim.x, ...
+//
+// Building with -DDIMQ_B200_DIAG adds per-role cycle counters and role-skipping
+// switches (set through dimq_diag_configure, an entry point that exists only in
+// that build); the default build has neither.
 #include <cstdlib>
 #include <cstring>
 
@@ -81,8 +86,10 @@ struct TcParams {
   int ksplit;                 // K is cut into this many slices, one tile per (slice, n block, m block);
                               // > 1: partial sums are added into `ws` instead of being stored
   float* ws;                  // [M][N] fp32 workspace of the split-K mode (zeroed by the launcher)
-  int dbg;                    // measurement only (DIMQ_B200_TC_DEBUG): 2 skip the TMEM stores of the dequantisation, 4 skip MMAs, 8 skip the activation copies, 16 skip the lookups
-  unsigned long long* prof;   // optional per-CTA wait-cycle counters (diagnostics), else null
+#ifdef DIMQ_B200_DIAG
+  int dbg;                    // 2 skip the TMEM stores of the dequantisation, 4 skip MMAs, 8 skip the activation copies, 16 skip the lookups
+  unsigned long long* prof;   // per-CTA cycle counters, 32 words per CTA, or null
+#endif
 };
 
 struct TmapSet {
@@ -101,14 +108,24 @@ struct SharedHeader {
 };
 constexpr int kHeaderBytes = 512;
 
-// Diagnostics: cycles spent inside one bounded wait, accumulated per role when p.prof is set.
+#ifdef DIMQ_B200_DIAG
+// cycles spent inside one bounded wait, accumulated per role when p.prof is set
 #define DIMQ_TIMED(acc, expr)                                   \
   [&]() {                                                        \
-    const long long t0_ = p.prof ? clock64() : 0;                \
+    const long long t0_ = DIMQ_PROF_ON ? clock64() : 0;                \
     const bool ok_ = (expr);                                     \
     if (p.prof) acc += static_cast<unsigned long long>(clock64() - t0_); \
     return ok_;                                                  \
   }()
+#define DIMQ_DBG(bit) ((p.dbg & (bit)) != 0)
+#define DIMQ_PROF_ON (p.prof != nullptr)
+#define DIMQ_PROF_STORE(i, v) do { if (p.prof) p.prof[blockIdx.x * 32 + (i)] = (v); } while (0)
+#else
+#define DIMQ_TIMED(acc, expr) (expr)
+#define DIMQ_DBG(bit) false
+#define DIMQ_PROF_ON false
+#define DIMQ_PROF_STORE(i, v) do { } while (0)
+#endif
 
 template <int BITS>
 __device__ __forceinline__ void load_unit(const uint8_t* p, uint32_t (&w)[BITS]) {
@@ -444,7 +461,8 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
 
   if (warp == 0) {
     // ===================== TMA producer =====================
-    if (lane == 0) {
+    // The whole warp walks the loop; one elected lane issues the copies (see elect_one).
+    {
       uint32_t stage = 0, phase = 0;
       uint32_t issued = 0;
       bool ok = true;
@@ -460,14 +478,16 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
           b0 = (m_blk / (p.tiles_w * p.tiles_h)) * p.tb;
         }
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!DIMQ_TIMED(w_xe, mbar_wait(smem_u32(&hdr->x_empty[stage]), phase ^ 1u, abort_flag, 0x100u | stage))) { ok = false; break; }
+          if (!__all_sync(0xFFFFFFFFu, DIMQ_TIMED(w_xe, mbar_wait(smem_u32(&hdr->x_empty[stage]), phase ^ 1u, abort_flag, 0x100u | stage)))) { ok = false; break; }
           const uint32_t full = smem_u32(&hdr->x_full[stage]);
           const uint32_t dst = smem_u32(x_stage + stage * p.x_stage_bytes);
-          if (p.dbg & 8) {
-            mbar_arrive(full);
+          if (DIMQ_DBG(8)) {
+            if (elect_one()) mbar_arrive(full);
           } else if (!p.conv) {
-            mbar_arrive_expect_tx(full, p.x_stage_bytes);
-            tma_load_2d(dst, &tmaps.m[0], full, (k0 + kb) * kBlockK, m_blk * p.tx);
+            if (elect_one()) {
+              mbar_arrive_expect_tx(full, p.x_stage_bytes);
+              tma_load_2d(dst, &tmaps.m[0], full, (k0 + kb) * kBlockK, m_blk * p.tx);
+            }
           } else {
             // tap (kh, kw), channels [64 cb, 64 cb + 64): input pixel = s * out + tap offset.  With
             // stride 2 the input is addressed through one tensor map per (row, column) parity, so the
@@ -481,16 +501,22 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
               hy = oh0 + ((dy - py) >> 1);
               wx = ow0 + ((dx - px) >> 1);
             }
-            mbar_arrive_expect_tx(full, p.x_stage_bytes);
-            tma_load_4d(dst, &tmaps.m[map], full, cb * kBlockK, wx, hy, b0);
+            if (elect_one()) {
+              mbar_arrive_expect_tx(full, p.x_stage_bytes);
+              tma_load_4d(dst, &tmaps.m[map], full, cb * kBlockK, wx, hy, b0);
+            }
             if (++cb == p.c_blocks) { cb = 0; ++tap; }
           }
+          __syncwarp();
           ++issued;
           if (++stage == n_xs) { stage = 0; phase ^= 1u; }
         }
       }
-      if (p.prof) { p.prof[blockIdx.x * 16 + 0] = w_xe; p.prof[blockIdx.x * 16 + 1] = clock64() - t_begin; }
-      if (!ok) {
+      if (lane == 0) {
+        DIMQ_PROF_STORE(0, w_xe);
+        DIMQ_PROF_STORE(1, clock64() - t_begin);
+      }
+      if (!ok && lane == 0) {
         // Gave up: wait (bounded) for the copies still in flight so that no TMA write
         // lands in shared memory after this CTA has exited.
         const uint32_t n_back = issued < n_xs ? issued : n_xs;
@@ -501,10 +527,13 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
             if (mbar_try_wait(smem_u32(&hdr->x_full[s]), ph)) break;
         }
       }
+      __syncwarp();
     }
   } else if (warp == 1) {
     // ===================== MMA issuer =====================
-    if (lane == 0) {
+    // The whole warp walks the loop and polls the barriers; one elected lane issues the MMAs and
+    // the commits (see elect_one).
+    {
       uint32_t xs = 0, xph = 0, ws = 0, wph = 0, as = 0, aph = 0;
       bool ok = true;
       unsigned long long w_de = 0, w_xf = 0, w_wf = 0, t_cm = 0, t_fe = 0, t_mm = 0;
@@ -512,15 +541,14 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
       const uint64_t desc0 = make_smem_desc_sw128(smem_u32(x_stage));
       const uint32_t a0 = tmem_base + kWCol;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        if (!DIMQ_TIMED(w_de, mbar_wait(smem_u32(&hdr->d_empty[as]), aph ^ 1u, abort_flag, 0x200u | as))) { ok = false; break; }
+        if (!__all_sync(0xFFFFFFFFu, DIMQ_TIMED(w_de, mbar_wait(smem_u32(&hdr->d_empty[as]), aph ^ 1u, abort_flag, 0x200u | as)))) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + kAccCol + as * kTileX;
-        // k blocks are issued two at a time: the four barrier polls of a pair overlap, which halves the
-        // time this thread spends waiting per MMA (its latency, not the tensor pipe, bounds the loop)
+        // k blocks are issued two at a time: the four barrier polls of a pair overlap
         auto issue_block = [&](int kb, uint32_t xs_, uint32_t ws_) {
           const uint64_t b_desc = desc0 + static_cast<uint64_t>(xs_ * (p.x_stage_bytes >> 4));
           const uint32_t a_tmem = a0 + ws_ * kWStageCols;
-          if (!(p.dbg & 4)) {
+          if (!DIMQ_DBG(4)) {
             // advance 16 k: 32 bytes inside the swizzled row (encoded >> 4), 8 TMEM columns
             if (kb == 0) mma_f16_ts(d_tmem, a_tmem, b_desc, p.idesc, 0u);
             else mma_f16_ts_acc(d_tmem, a_tmem, b_desc, p.idesc);
@@ -540,18 +568,21 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
           uint32_t xs1 = xs + 1, xph1 = xph, ws1 = ws + 1, wph1 = wph;
           if (xs1 == n_xs) { xs1 = 0; xph1 ^= 1u; }
           if (ws1 == kWStagesUsed) { ws1 = 0; wph1 ^= 1u; }
-          const long long tq0 = p.prof ? clock64() : 0;
+          const long long tq0 = DIMQ_PROF_ON ? clock64() : 0;
           const bool got = two ? mbar_wait4(smem_u32(&hdr->x_full[xs]), xph, smem_u32(&hdr->w_full[ws]), wph,
                                             smem_u32(&hdr->x_full[xs1]), xph1, smem_u32(&hdr->w_full[ws1]), wph1,
                                             abort_flag, 0x300u | xs)
                                : mbar_wait2(smem_u32(&hdr->x_full[xs]), xph, smem_u32(&hdr->w_full[ws]), wph,
                                             abort_flag, 0x300u | xs);
-          if (!got) { ok = false; break; }
+          if (!__all_sync(0xFFFFFFFFu, got)) { ok = false; break; }
           tc_fence_after();
-          const long long tq1 = p.prof ? clock64() : 0;
-          issue_block(kb, xs, ws);
-          if (two) issue_block(kb + 1, xs1, ws1);
-          if (p.prof) { w_xf += tq1 - tq0; t_mm += clock64() - tq1; }
+          const long long tq1 = DIMQ_PROF_ON ? clock64() : 0;
+          if (elect_one()) {
+            issue_block(kb, xs, ws);
+            if (two) issue_block(kb + 1, xs1, ws1);
+          }
+          __syncwarp();
+          if (DIMQ_PROF_ON) { w_xf += tq1 - tq0; t_mm += clock64() - tq1; }
           const int nb = two ? 2 : 1;
           for (int i = 0; i < nb; ++i) {
             if (++xs == n_xs) { xs = 0; xph ^= 1u; }
@@ -560,13 +591,14 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
           kb += nb;
         }
         if (!ok) break;
-        mma_commit(smem_u32(&hdr->d_full[as]));
+        if (elect_one()) mma_commit(smem_u32(&hdr->d_full[as]));
+        __syncwarp();
         if (++as == kAccStages) { as = 0; aph ^= 1u; }
       }
-      if (p.prof) {
-        p.prof[blockIdx.x * 16 + 2] = w_de; p.prof[blockIdx.x * 16 + 3] = w_xf; p.prof[blockIdx.x * 16 + 4] = w_wf;
-        p.prof[blockIdx.x * 16 + 5] = clock64() - t_begin;
-        p.prof[blockIdx.x * 16 + 11] = t_cm; p.prof[blockIdx.x * 16 + 12] = t_fe; p.prof[blockIdx.x * 16 + 13] = t_mm;
+      if (lane == 0) {
+        DIMQ_PROF_STORE(2, w_de); DIMQ_PROF_STORE(3, w_xf); DIMQ_PROF_STORE(4, w_wf);
+        DIMQ_PROF_STORE(5, clock64() - t_begin);
+        DIMQ_PROF_STORE(11, t_cm); DIMQ_PROF_STORE(12, t_fe); DIMQ_PROF_STORE(13, t_mm);
       }
     }
   } else if (warp < 2 + kNumEpilogueWarps) {
@@ -578,11 +610,13 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
     unsigned char* my_res = my_out + epi_out_bytes;
     uint32_t res_ph[2] = {0u, 0u};
     int res_buf = 0;
-    if (p.epi_tma && p.epi_res && lane == 0) {
+    if (p.epi_tma && p.epi_res) {
       // residual tile of this warp's first chunk
       const int t0 = blockIdx.x;
-      if (t0 < num_tiles && sub < (p.tx + 31) / 32 && (t0 / p.m_tiles) * kTileW + quarter * 32 < p.N)
-        epi_issue_residual(tmaps, p, hdr, my_res, ew, 0, t0, sub, quarter);
+      if (t0 < num_tiles && sub < (p.tx + 31) / 32 && (t0 / p.m_tiles) * kTileW + quarter * 32 < p.N) {
+        if (elect_one()) epi_issue_residual(tmaps, p, hdr, my_res, ew, 0, t0, sub, quarter);
+      }
+      __syncwarp();
     }
     uint32_t as = 0, aph = 0;
     bool ok = true;
@@ -624,8 +658,8 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
           const bool has_next = t_next < num_tiles && c_next < n_chunks &&
                                 (t_next / p.m_tiles) * kTileW + quarter * 32 < p.N;
           if (p.epi_res) {
-            if (lane == 0) {
-              if (has_next) epi_issue_residual(tmaps, p, hdr, my_res + (res_buf ^ 1) * epi_out_bytes, ew, res_buf ^ 1, t_next, c_next, quarter);
+            if (has_next) {
+              if (elect_one()) epi_issue_residual(tmaps, p, hdr, my_res + (res_buf ^ 1) * epi_out_bytes, ew, res_buf ^ 1, t_next, c_next, quarter);
             }
             uint32_t got = 0;
             if (lane == 0) got = mbar_wait(smem_u32(&hdr->r_full[ew][res_buf]), res_ph[res_buf], abort_flag, 0x700u | ew) ? 1u : 0u;
@@ -633,21 +667,23 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
             res_ph[res_buf] ^= 1u;
           }
           // the previous store of this warp must have finished reading the staging tile
-          const long long te0 = p.prof ? clock64() : 0;
-          if (lane == 0) tma_store_wait_read();
+          const long long te0 = DIMQ_PROF_ON ? clock64() : 0;
+          if (elect_one()) tma_store_wait_read();
           __syncwarp();
-          const long long te1 = p.prof ? clock64() : 0;
+          const long long te1 = DIMQ_PROF_ON ? clock64() : 0;
           const unsigned char* res_tile = my_res + res_buf * epi_out_bytes;
           stage_chunk(r, my_out, p.epi_res ? res_tile : nullptr, lane, bias, p.epilogue, p.y_dtype);
           fence_proxy_async_smem();
           __syncwarp();
-          if (p.prof) { const long long te2 = clock64(); t_ewait += te1 - te0; t_estage += te2 - te1; }
-          if (lane == 0) {
+          if (DIMQ_PROF_ON) { const long long te2 = clock64(); t_ewait += te1 - te0; t_estage += te2 - te1; }
+          {
             int c0, c1, c2, c3;
             epi_coords(p, t, c, quarter, c0, c1, c2, c3);
-            if (p.conv) tma_store_4d(&tmaps.y, smem_u32(my_out), c0, c1, c2, c3);
-            else tma_store_2d(&tmaps.y, smem_u32(my_out), c0, c1);
-            tma_store_commit();
+            if (elect_one()) {
+              if (p.conv) tma_store_4d(&tmaps.y, smem_u32(my_out), c0, c1, c2, c3);
+              else tma_store_2d(&tmaps.y, smem_u32(my_out), c0, c1);
+              tma_store_commit();
+            }
           }
           if (p.epi_res) res_buf ^= 1;
         }
@@ -688,8 +724,14 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
       }
       if (++as == kAccStages) { as = 0; aph ^= 1u; }
     }
-    if (p.epi_tma && lane == 0) tma_store_wait_all();
-    if (p.prof && warp == 2 && lane == 0) { p.prof[blockIdx.x * 16 + 14] = t_ewait; p.prof[blockIdx.x * 16 + 15] = t_estage; p.prof[blockIdx.x * 16 + 6] = w_df; p.prof[blockIdx.x * 16 + 7] = clock64() - t_begin; }
+    __syncwarp();
+    if (p.epi_tma) {
+      if (elect_one()) tma_store_wait_all();
+    }
+    if (warp == 2 && lane == 0) {
+      DIMQ_PROF_STORE(14, t_ewait); DIMQ_PROF_STORE(15, t_estage); DIMQ_PROF_STORE(6, w_df);
+      DIMQ_PROF_STORE(7, clock64() - t_begin);
+    }
   } else {
     // ===================== dequantisation =====================
     // 8 warps in 2 groups of 4 (one warp per TMEM lane quarter).  Group g dequantises stages
@@ -752,7 +794,7 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
 #pragma unroll
     for (int s0 = 0; s0 < kIdxPrefetch - 1; ++s0) prefetch_next();
     int slot = 0;
-    unsigned long long w_we = 0, w_cp = 0;
+    unsigned long long w_we = 0, w_cp = 0, t_look = 0, t_st = 0, t_arr = 0;
     const long long t_begin = clock64();
     // activation slot and parity of k block (it - kWStagesUsed) for this group's first waiting stage
     uint32_t rel_slot, rel_par;
@@ -795,13 +837,14 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
         }
       }
       prefetch_next();
-      { const long long t0_ = p.prof ? clock64() : 0; cp_async_wait<kIdxPrefetch - 1>(); if (p.prof) w_cp += clock64() - t0_; }
+      { const long long t0_ = DIMQ_PROF_ON ? clock64() : 0; cp_async_wait<kIdxPrefetch - 1>(); if (DIMQ_PROF_ON) w_cp += clock64() - t0_; }
+      const long long tl0 = DIMQ_PROF_ON ? clock64() : 0;
       uint32_t cur[2 * BITS];
       read_unit<BITS>(my_ring + slot * kRingStride, cur);
       if (++slot == kIdxPrefetch) slot = 0;
       uint32_t out[32];
       uint32_t out_lo[SPLIT ? 32 : 1];
-      if (p.dbg & 16) {   // diagnostics: no lookups
+      if (DIMQ_DBG(16)) {   // diagnostics: no lookups
 #pragma unroll
         for (int q = 0; q < 32; ++q) { out[q] = cur[q % (2 * BITS)]; if (SPLIT) out_lo[SPLIT ? q : 0] = 0u; }
       } else
@@ -835,6 +878,7 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
           out[q] = lo | (hi << 16);
         }
       }
+      if (DIMQ_PROF_ON) t_look += clock64() - tl0;
       // tcgen05.st is warp-collective: the whole warp proceeds or the whole warp gives up
       // weight slot ws was last read by k block (it - kWStagesUsed): wait for its commit, which was
       // signalled on the activation slot of that k block
@@ -844,8 +888,9 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
         if (rel_slot >= n_xs) { rel_slot -= n_xs; rel_par ^= 1u; }
       }
       tc_fence_after();
+      const long long ts0 = DIMQ_PROF_ON ? clock64() : 0;
       const uint32_t w_tmem = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kWCol + ws * kWStageCols;
-      if (!(p.dbg & 2)) {
+      if (!DIMQ_DBG(2)) {
         tmem_st32(w_tmem, out);
         if (SPLIT) {
           uint32_t lo32[32];
@@ -856,12 +901,17 @@ linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
       }
       // one arrival per warp: per-thread arrivals on one mbarrier serialise in shared memory
       tmem_st_wait();
+      const long long ts1 = DIMQ_PROF_ON ? clock64() : 0;
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&hdr->w_full[ws]));
+      if (DIMQ_PROF_ON) { t_st += ts1 - ts0; t_arr += clock64() - ts1; }
       advance(t, kb, kGroups);
     }
-    if (p.prof && dq_tid == 0) { p.prof[blockIdx.x * 16 + 8] = w_we; p.prof[blockIdx.x * 16 + 9] = w_cp; p.prof[blockIdx.x * 16 + 10] = clock64() - t_begin; }
+    if (dq_tid == 0) {
+      DIMQ_PROF_STORE(8, w_we); DIMQ_PROF_STORE(9, w_cp); DIMQ_PROF_STORE(10, clock64() - t_begin);
+      DIMQ_PROF_STORE(16, t_look); DIMQ_PROF_STORE(17, t_st); DIMQ_PROF_STORE(18, t_arr);
+    }
   }
 
   // ---- teardown -----------------------------------------------------------------
@@ -934,11 +984,29 @@ bool tc_supported(const void* x, int x_dtype, const dimq_wq_weight* w, int64_t M
   return tiles < 0x7FFFFFFF;
 }
 
+#ifdef DIMQ_B200_DIAG
+// Diagnostics build only: role-skipping switches, replicated-table switch and the buffer of per-CTA
+// cycle counters (32 words per CTA; ignored unless it holds at least 148 * 32 words).
+static int g_diag_dbg = 0, g_diag_rep = 0;
+static unsigned long long* g_diag_prof = nullptr;
+static int64_t g_diag_prof_words = 0;
+void diag_configure(int dbg, int rep, unsigned long long* prof, int64_t prof_words) {
+  g_diag_dbg = dbg;
+  g_diag_rep = rep;
+  g_diag_prof = prof;
+  g_diag_prof_words = prof != nullptr ? prof_words : 0;
+}
+#endif
+
 namespace {
 
 bool epi_tma_enabled() {
-  const char* env = getenv("DIMQ_B200_TC_EPI");
-  return env == nullptr || atoi(env) != 0;
+  // read once per process: DIMQ_B200_TC_EPI=0 selects the direct-store epilogue
+  static const bool enabled = [] {
+    const char* env = getenv("DIMQ_B200_TC_EPI");
+    return env == nullptr || atoi(env) != 0;
+  }();
+  return enabled;
 }
 
 CUtensorMapDataType tmap_dtype(int dtype) {
@@ -993,10 +1061,10 @@ int finish_launch(const TmapSet& tmaps, TcParams& p, const dimq_wq_weight* w, co
   p.w_fmt = w_fmt;
   p.idesc = tc::make_idesc_f16(w_fmt, w_fmt, kTileW, p.tx);
   p.x_stage_bytes = static_cast<uint32_t>(p.tx) * kBlockK * 2;
-  p.prof = nullptr;
-  p.dbg = 0;
-  if (const char* env = getenv("DIMQ_B200_TC_DEBUG")) p.dbg = atoi(env);
-  if (const char* env = getenv("DIMQ_B200_PROFILE_PTR")) p.prof = reinterpret_cast<unsigned long long*>(strtoull(env, nullptr, 0));
+#ifdef DIMQ_B200_DIAG
+  p.dbg = g_diag_dbg;
+  p.prof = g_diag_prof_words >= static_cast<int64_t>(kNumSMs) * 32 ? g_diag_prof : nullptr;
+#endif
   p.n_tiles = static_cast<int>((p.N + kTileW - 1) / kTileW);
   if (p.ksplit < 1) p.ksplit = 1;
   const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.ksplit;
@@ -1005,7 +1073,9 @@ int finish_launch(const TmapSet& tmaps, TcParams& p, const dimq_wq_weight* w, co
 
   const bool pair = w->bits != 8 && table_bytes(w->bits, w->groups, true, split) <= (size_t)kMaxTableBytes;
   p.rep = 0;
-  if (const char* env = getenv("DIMQ_B200_TC_REP")) p.rep = (atoi(env) != 0 && (w->groups == 1 || w->group_rows % kTileW == 0)) ? 1 : 0;
+#ifdef DIMQ_B200_DIAG
+  p.rep = (g_diag_rep != 0 && (w->groups == 1 || w->group_rows % kTileW == 0)) ? 1 : 0;
+#endif
   const size_t epi_bytes = p.epi_tma ? static_cast<size_t>(kNumEpilogueWarps) * 32 * 32 * (y_dtype == DIMQ_F32 ? 4 : 2) * (p.epi_res ? 3 : 1) : 0;
   const size_t fixed = 1024 + kHeaderBytes + epi_bytes + static_cast<size_t>(kIdxPrefetch) * kNumDequantWarps * 32 * (w->bits == 8 ? 64 : 32) +
                        (p.rep ? static_cast<size_t>(kNumDequantGroups) * kRepWords * 4 : 0) +
@@ -1023,10 +1093,14 @@ int finish_launch(const TmapSet& tmaps, TcParams& p, const dimq_wq_weight* w, co
     return split ? launch_tc<B, false, true>(tmaps, p, smem, grid, st)                              \
                  : launch_tc<B, false, false>(tmaps, p, smem, grid, st);
   switch (w->bits) {
+#ifdef DIMQ_B200_DIAG_BITS   // diagnostics build: instantiate one index width only (shorter compile)
+    DIMQ_TC_CASE(DIMQ_B200_DIAG_BITS)
+#else
     DIMQ_TC_CASE(2)
     DIMQ_TC_CASE(3)
     DIMQ_TC_CASE(4)
     DIMQ_TC_CASE(8)
+#endif
     default: return DIMQ_ERR_BAD_BITS;
   }
 #undef DIMQ_TC_CASE

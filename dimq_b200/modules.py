@@ -105,13 +105,19 @@ class DIMQConv2d(_PackedBase):
         self.padding = _pair(padding)
         self.dilation = _pair(dilation)
         self.groups = int(groups)
-        self._khwc = None  # indices re-ordered for the tensor-core conv, built on first use on the GPU
+        # indices re-ordered for the tensor-core conv: built on first use on the GPU and rebuilt
+        # whenever the packed_weight buffer is replaced, moved or written in place
+        self._khwc = None
+        self._khwc_key = None
 
     def _prepacked(self) -> torch.Tensor | None:
         if self.groups != 1 or self.weight_shape[1] % 64 != 0:
             return None
-        if self._khwc is None or self._khwc.device != self.packed_weight.device:
-            self._khwc = ops.conv_prepack(self.packed_weight, self.weight_shape, self.bits)
+        pw = self.packed_weight
+        key = (pw.data_ptr(), pw._version, pw.device)
+        if self._khwc is None or self._khwc_key != key:
+            self._khwc = ops.conv_prepack(pw, self.weight_shape, self.bits)
+            self._khwc_key = key
         return self._khwc
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:

@@ -22,7 +22,7 @@ from ._lib import ALGO_AUTO, ALGO_GENERIC, ALGO_STREAM, ALGO_TCGEN05, EPI_GELU, 
 
 _EPILOGUES = {None: EPI_NONE, "none": EPI_NONE, "relu": EPI_RELU, "gelu": EPI_GELU, "add_relu": _lib.EPI_ADD_RELU}
 _ALGOS = {None: ALGO_AUTO, "auto": ALGO_AUTO, "generic": ALGO_GENERIC, "stream": ALGO_STREAM,
-          "tcgen05": ALGO_TCGEN05, "tcgen05_bf16w": ALGO_TCGEN05 + 100, "mma_stream": 4}
+          "tcgen05": ALGO_TCGEN05, "mma_stream": 4}
 
 
 def is_available() -> bool:
