@@ -28,7 +28,8 @@ EXPORTED_SYMBOLS = (
     "dimq_conv_out_size", "dimq_conv2d_lut", "dimq_hard_quantize", "dimq_linear_wq", "dimq_conv2d_wq",
     "dimq_last_device_status", "dimq_add_layer_norm", "dimq_conv_prepack", "dimq_conv2d_wq_static", "dimq_im2col", "dimq_max_pool_nhwc",
     "dimq_a4_workspace_bytes", "dimq_linear_lut_tc", "dimq_conv2d_lut_tc",
-    "dimq_linear_wq_workspace_bytes", "dimq_linear_wq_ws",
+    "dimq_linear_wq_workspace_bytes", "dimq_linear_wq_ws", "dimq_expand_workspace_bytes", "dimq_linear_wq_expand",
+    "dimq_conv2d_wq_workspace_bytes", "dimq_conv2d_wq_ws", "dimq_conv2d_wq_expand",
 )
 
 

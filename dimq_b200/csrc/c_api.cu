@@ -27,6 +27,19 @@ bool conv_tc_supported(const void* x, int x_dtype, const dimq_wq_weight* w, cons
 int launch_conv2d_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
                         const void* residual, void* y, int y_dtype, const dimq_conv_geom* g, int epilogue,
                         cudaStream_t st);
+bool dense_pays(int64_t rows);
+bool dense_supported(const void* x, int x_dtype, const dimq_wq_weight* w, const void* y, int y_dtype,
+                     const void* residual, int64_t M, int64_t N, int64_t K);
+int64_t dense_workspace_bytes(int x_dtype, const dimq_wq_weight* w, int64_t N, int64_t K);
+int launch_linear_wq_dense(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
+                           const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K, int epilogue,
+                           void* workspace, int64_t workspace_bytes, cudaStream_t st);
+bool conv_dense_supported(const void* x, int x_dtype, const dimq_wq_weight* w, const dimq_conv_geom* g, const void* y,
+                          int y_dtype, const void* residual);
+int64_t conv_dense_workspace_bytes(int x_dtype, const dimq_wq_weight* w, const dimq_conv_geom* g);
+int launch_conv2d_wq_dense(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
+                           const void* residual, void* y, int y_dtype, const dimq_conv_geom* g, int epilogue,
+                           void* workspace, int64_t workspace_bytes, cudaStream_t st);
 int read_device_status(uint32_t* status);
 int read_ms_status(uint32_t* status);
 }  // namespace dimq
@@ -118,8 +131,14 @@ extern "C" int dimq_linear_wq_workspace_bytes(const void* x, int x_dtype, const 
   *bytes = 0;
   if (M <= 0 || N <= 0 || K <= 0) return DIMQ_OK;
   if (check_wq_weight(w, N) != DIMQ_OK) return DIMQ_OK;
-  // only where the automatic choice would take the tcgen05 kernel and splitting K pays
   if (mma_stream_supported(x, x_dtype, w, M, N, K) || stream_supported(w, M, N, K)) return DIMQ_OK;
+  // many activation rows: the expanded 16-bit weight (the output is taken to be as wide as it may get
+  // - 16-bit - and aligned; dimq_linear_wq_ws checks the real one and falls back if it does not fit)
+  if (dense_pays(M) && (N * 2) % 16 == 0 && dense_supported(x, x_dtype, w, x, x_dtype, nullptr, M, N, K)) {
+    *bytes = dense_workspace_bytes(x_dtype, w, N, K);
+    return DIMQ_OK;
+  }
+  // else only where the automatic choice would take the tcgen05 kernel and splitting K pays
   if (!tc_supported(x, x_dtype, w, M, N, K)) return DIMQ_OK;
   if (tc_split_k(M, N, K) > 1) *bytes = M * N * 4;
   return DIMQ_OK;
@@ -134,8 +153,14 @@ extern "C" int dimq_linear_wq_ws(const void* x, int x_dtype, const dimq_wq_weigh
       x != nullptr && y != nullptr &&
       dimq_linear_wq_workspace_bytes(x, x_dtype, w, M, N, K, &need) == DIMQ_OK && need > 0) {
     if (workspace_bytes < need) return DIMQ_ERR_SCRATCH_TOO_SMALL;
-    return launch_linear_wq_tc(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, 0,
-                               static_cast<cudaStream_t>(stream), workspace, workspace_bytes);
+    if (dense_pays(M)) {
+      if (dense_supported(x, x_dtype, w, y, y_dtype, residual, M, N, K))
+        return launch_linear_wq_dense(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue,
+                                      workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+    } else {
+      return launch_linear_wq_tc(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, 0,
+                                 static_cast<cudaStream_t>(stream), workspace, workspace_bytes);
+    }
   }
   return dimq_linear_wq(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, DIMQ_ALGO_AUTO, stream);
 }
@@ -162,4 +187,87 @@ extern "C" int dimq_conv2d_wq(const void* x, int x_dtype, const dimq_wq_weight* 
   if (algo != DIMQ_ALGO_GENERIC) return DIMQ_ERR_UNSUPPORTED;
   return launch_conv2d_direct(false, x, x_dtype, w, 1.0f, 0, bias, bias_dtype, residual, y, y_dtype, &g, epilogue,
                               static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dimq_expand_workspace_bytes(int x_dtype, const dimq_wq_weight* w, int64_t rows, int64_t row_len,
+                                           int64_t* bytes) {
+  if (bytes == nullptr || w == nullptr) return DIMQ_ERR_NULL_POINTER;
+  if (rows < 0 || row_len < 0) return DIMQ_ERR_BAD_SIZE;
+  *bytes = dense_workspace_bytes(x_dtype, w, rows, row_len);
+  return DIMQ_OK;
+}
+
+extern "C" int dimq_linear_wq_expand(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias,
+                                     int bias_dtype, const void* residual, void* y, int y_dtype, int64_t M, int64_t N,
+                                     int64_t K, int epilogue, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (M < 0 || N <= 0 || K <= 0) return DIMQ_ERR_BAD_SIZE;
+  if (!valid_dtype(x_dtype) || !valid_dtype(y_dtype)) return DIMQ_ERR_BAD_DTYPE;
+  if (bias != nullptr && !valid_dtype(bias_dtype)) return DIMQ_ERR_BAD_DTYPE;
+  if (epilogue < DIMQ_EPI_NONE || epilogue > DIMQ_EPI_ADD_RELU) return DIMQ_ERR_UNSUPPORTED;
+  const int rc = check_wq_weight(w, N);
+  if (rc != DIMQ_OK) return rc;
+  if (M == 0) return DIMQ_OK;
+  if (x == nullptr || y == nullptr) return DIMQ_ERR_NULL_POINTER;
+  return launch_linear_wq_dense(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, workspace,
+                                workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dimq_conv2d_wq_workspace_bytes(const void* x, int x_dtype, const dimq_wq_weight* w,
+                                              const dimq_conv_geom* geom, int64_t* bytes) {
+  if (bytes == nullptr || w == nullptr || geom == nullptr) return DIMQ_ERR_NULL_POINTER;
+  *bytes = 0;
+  dimq_conv_geom g = *geom;
+  if (dimq_conv_out_size(&g) != DIMQ_OK || check_wq_weight(w, g.out_channels) != DIMQ_OK) return DIMQ_OK;
+  if (!dense_pays(static_cast<int64_t>(g.batch) * g.out_h * g.out_w)) return DIMQ_OK;
+  if ((static_cast<int64_t>(g.out_channels) * 2) % 16 != 0) return DIMQ_OK;
+  if (conv_dense_supported(x, x_dtype, w, &g, x, x_dtype, nullptr)) *bytes = conv_dense_workspace_bytes(x_dtype, w, &g);
+  return DIMQ_OK;
+}
+
+static int conv_wq_checks(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
+                          void* y, int y_dtype, const dimq_conv_geom* geom, int epilogue, dimq_conv_geom* g, bool* empty) {
+  if (geom == nullptr) return DIMQ_ERR_NULL_POINTER;
+  *g = *geom;
+  int rc = dimq_conv_out_size(g);
+  if (rc != DIMQ_OK) return rc;
+  if (g->out_h != geom->out_h || g->out_w != geom->out_w) return DIMQ_ERR_BAD_SHAPE;
+  if (!valid_dtype(x_dtype) || !valid_dtype(y_dtype)) return DIMQ_ERR_BAD_DTYPE;
+  if (bias != nullptr && !valid_dtype(bias_dtype)) return DIMQ_ERR_BAD_DTYPE;
+  if (epilogue < DIMQ_EPI_NONE || epilogue > DIMQ_EPI_ADD_RELU) return DIMQ_ERR_UNSUPPORTED;
+  rc = check_wq_weight(w, g->out_channels);
+  if (rc != DIMQ_OK) return rc;
+  *empty = static_cast<int64_t>(g->batch) * g->out_channels * g->out_h * g->out_w == 0;
+  if (!*empty && (x == nullptr || y == nullptr)) return DIMQ_ERR_NULL_POINTER;
+  return DIMQ_OK;
+}
+
+extern "C" int dimq_conv2d_wq_expand(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias,
+                                     int bias_dtype, const void* residual, void* y, int y_dtype,
+                                     const dimq_conv_geom* geom, int epilogue, void* workspace, int64_t workspace_bytes,
+                                     void* stream) {
+  dimq_conv_geom g;
+  bool empty = false;
+  const int rc = conv_wq_checks(x, x_dtype, w, bias, bias_dtype, y, y_dtype, geom, epilogue, &g, &empty);
+  if (rc != DIMQ_OK) return rc;
+  if (empty) return DIMQ_OK;
+  return launch_conv2d_wq_dense(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, &g, epilogue, workspace,
+                                workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dimq_conv2d_wq_ws(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
+                                 const void* residual, void* y, int y_dtype, const dimq_conv_geom* geom, int epilogue,
+                                 void* workspace, int64_t workspace_bytes, void* stream) {
+  dimq_conv_geom g;
+  bool empty = false;
+  const int rc = conv_wq_checks(x, x_dtype, w, bias, bias_dtype, y, y_dtype, geom, epilogue, &g, &empty);
+  if (rc != DIMQ_OK) return rc;
+  if (empty) return DIMQ_OK;
+  int64_t need = 0;
+  if (workspace != nullptr && dimq_conv2d_wq_workspace_bytes(x, x_dtype, w, geom, &need) == DIMQ_OK && need > 0 &&
+      conv_dense_supported(x, x_dtype, w, &g, y, y_dtype, residual)) {
+    if (workspace_bytes < need) return DIMQ_ERR_SCRATCH_TOO_SMALL;
+    return launch_conv2d_wq_dense(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, &g, epilogue, workspace,
+                                  workspace_bytes, static_cast<cudaStream_t>(stream));
+  }
+  return dimq_conv2d_wq(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, geom, epilogue, DIMQ_ALGO_AUTO, stream);
 }

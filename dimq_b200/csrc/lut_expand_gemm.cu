@@ -1,0 +1,782 @@
+// Weight-only LUT GEMM / implicit-GEMM convolution for LARGE M in two steps.
+//
+//   1. lut_expand_kernel: every packed index is looked up ONCE and the codeword is written, in the
+//      activations' 16-bit format, to a caller-owned scratch matrix W16[N][K] (a few MB: it stays in
+//      the 126 MB L2).
+//   2. lut_dense_tc_kernel: y = x * W16^T on the 5th-generation tensor cores.  Both operands are staged
+//      by TMA (128-byte swizzle, no multicast) and read by tcgen05.mma from shared memory; fp32
+//      accumulators live in tensor memory, double-buffered so that the epilogue of a tile overlaps the
+//      main loop of the next.
+//
+// Why not look up inside the GEMM pipeline (lut_gemm_tc.cu does): there every CTA tile repeats the
+// lookups of its 128 weight rows, i.e. the N*K lookups are done M/192 times - 131 times for the
+// ViT-B/16 batch (M = 25 216) - and the lookup rate, not the tensor pipe, bounds the kernel (measured:
+// 1 560 cycles per 64-k block against 384 cycles of MMA).  Here the lookups cost N*K once (~1 % of the
+// GEMM's time) and the main loop is a plain two-operand TMA -> MMA pipeline.
+//
+// Tile: 128 activation rows (UMMA M, one TMEM lane each) x up to 256 weight rows (UMMA N = 256 is the
+// shape whose four MMAs per 64-k block run at the tensor pipe's full rate: measured 589 cycles per
+// block, commit included, against 512 ideal; N = 192 needs 573 cycles for 3/4 of the work).
+// Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2-9 epilogue
+// (two per TMEM lane quarter, alternating 32-column chunks).  Persistent grid, one CTA per SM.
+// The accumulator is y-oriented (lane = output row m, column = output feature n): an epilogue thread
+// holds 32 consecutive features of one row, adds bias / activation / residual, writes them as 16-byte
+// vectors into a swizzled staging tile and one TMA store per 32 x 32 chunk writes y.
+#include <cstring>
+
+#include "tc_common.cuh"
+
+namespace dimq {
+namespace {
+
+using namespace tc;
+
+constexpr int kBM = 128;         // activation rows (output pixels) per tile
+constexpr int kBK = 64;          // k per pipeline stage: 128 bytes of 16-bit elements
+constexpr int kMaxStages = 8;
+constexpr int kAccStages = 2;
+constexpr int kAccCols = 256;    // TMEM columns per accumulator buffer
+constexpr int kTmemCols = 512;
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = (2 + kEpiWarps) * 32;
+constexpr uint32_t kABytes = kBM * kBK * 2;   // 16 KB
+constexpr int kHeaderBytes = 1024;
+constexpr int kBiasBytes = kEpiWarps * 128;
+constexpr size_t kSmemMax = 227 * 1024;
+
+struct DenseParams {
+  const void* bias;
+  int bias_dtype;
+  const void* residual;     // same element type and layout as y, or null
+  int y_dtype;
+  int64_t M, N;             // output rows (GEMM) / pixels (conv), output features
+  int k_blocks;             // 64-k blocks of one pass over the reduction
+  int passes;               // 2 when the scratch carries hi and lo terms of every codeword side by side
+  int bn;                   // weight rows per tile: 64, 128 or 256
+  int m_tiles, n_tiles;
+  int stages;
+  uint32_t b_bytes;         // bn * 128
+  uint32_t idesc;
+  int epilogue;
+  // implicit-GEMM convolution: rows are output pixels, a tile is a tw x th x tb box of (ow, oh, batch)
+  int conv;
+  int tw, th, tb, tiles_w, tiles_h;
+  int OW, OH, Bn;
+  int stride, pad_h, pad_w, dil_h, dil_w, KW, c_blocks;
+};
+
+struct DenseMaps {
+  CUtensorMap a[4];   // activations; conv: one map per (row, column) parity of a stride-2 input
+  CUtensorMap b;      // expanded weights [N][passes * K]
+  CUtensorMap y;      // output, boxes of 32 features x 32 rows / pixels
+};
+
+struct DenseHeader {
+  uint64_t full[kMaxStages], empty[kMaxStages];
+  uint64_t d_full[kAccStages], d_empty[kAccStages];
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+};
+static_assert(sizeof(DenseHeader) <= kHeaderBytes, "header");
+
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ float gelu_tanh16(float v) {
+  const float u = v * fmaf(0.0356774081f, v * v, 0.7978845608f);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  const float h = 0.5f * v;
+  return fmaf(h, t, h);
+}
+
+constexpr int kEpiGelu16 = 16;   // GELU for 16-bit outputs: tanh form on the hardware tanh (see lut_gemm_tc.cu)
+
+// 32 accumulators of one output row (+ bias) -> activation / residual, in place.
+template <int EPI, bool RES>
+__device__ __forceinline__ void finish_row(float (&v)[32], const float* __restrict__ bias_s, const float (&res)[32]) {
+#pragma unroll
+  for (int j4 = 0; j4 < 8; ++j4) {
+    const float4 b = *reinterpret_cast<const float4*>(bias_s + 4 * j4);   // same address for all lanes: broadcast
+    v[4 * j4] += b.x; v[4 * j4 + 1] += b.y; v[4 * j4 + 2] += b.z; v[4 * j4 + 3] += b.w;
+  }
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    float x = v[j];
+    if (EPI == DIMQ_EPI_ADD_RELU) {
+      if (RES) x += res[j];
+      x = fmaxf(x, 0.0f);
+    } else {
+      if (EPI == DIMQ_EPI_RELU) x = fmaxf(x, 0.0f);
+      if (EPI == DIMQ_EPI_GELU) x = 0.5f * x * (1.0f + fast_erf(x * 0.70710678118654752440f));
+      if (EPI == kEpiGelu16) x = gelu_tanh16(x);
+      if (RES) x += res[j];
+    }
+    v[j] = x;
+  }
+}
+
+template <bool RES>
+__device__ __forceinline__ void finish_row_epi(float (&v)[32], const float* bias_s, const float (&res)[32], int epilogue) {
+  switch (epilogue) {
+    case DIMQ_EPI_RELU: finish_row<DIMQ_EPI_RELU, RES>(v, bias_s, res); break;
+    case DIMQ_EPI_GELU: finish_row<DIMQ_EPI_GELU, RES>(v, bias_s, res); break;
+    case kEpiGelu16: finish_row<kEpiGelu16, RES>(v, bias_s, res); break;
+    case DIMQ_EPI_ADD_RELU: finish_row<DIMQ_EPI_ADD_RELU, RES>(v, bias_s, res); break;
+    default: finish_row<DIMQ_EPI_NONE, RES>(v, bias_s, res); break;
+  }
+}
+
+__device__ __forceinline__ uint32_t pack16(float lo, float hi, int y_dtype) {
+  if (y_dtype == DIMQ_BF16) {
+    const __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&t);
+  }
+  const __half2 t = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&t);
+}
+
+// 32 residual values of one row: `p` points at the first of them (16-byte aligned), `valid` of them exist
+// (a multiple of 8 for 16-bit elements, of 4 for fp32: the row pitch is a multiple of 16 bytes).
+template <int ES>
+__device__ __forceinline__ void load_residual(const void* p, int y_dtype, int valid, float (&res)[32]) {
+  if (ES == 2) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint4 q = make_uint4(0u, 0u, 0u, 0u);
+      if (8 * c + 8 <= valid) q = __ldg(reinterpret_cast<const uint4*>(p) + c);
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (y_dtype == DIMQ_BF16) {
+          const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+          res[8 * c + 2 * i] = f.x; res[8 * c + 2 * i + 1] = f.y;
+        } else {
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+          res[8 * c + 2 * i] = f.x; res[8 * c + 2 * i + 1] = f.y;
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (4 * c + 4 <= valid) q = __ldg(reinterpret_cast<const float4*>(p) + c);
+      res[4 * c] = q.x; res[4 * c + 1] = q.y; res[4 * c + 2] = q.z; res[4 * c + 3] = q.w;
+    }
+  }
+}
+
+// ES = bytes per output element (2: bf16 / fp16, 4: fp32)
+template <int ES>
+__global__ void __launch_bounds__(kThreads, 1)
+lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // [stages: A 16 KB | B bn*128 B (all 1024-aligned)] [header] [bias slices] [staging tiles]
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t stage_bytes = kABytes + p.b_bytes;
+  const uint32_t n_st = static_cast<uint32_t>(p.stages);
+  DenseHeader* hdr = reinterpret_cast<DenseHeader*>(smem + n_st * stage_bytes);
+  float* bias_area = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(hdr) + kHeaderBytes);
+  unsigned char* staging = reinterpret_cast<unsigned char*>(bias_area) + kBiasBytes;   // 1024-aligned
+  constexpr uint32_t kStagingBytes = 32u * 32u * ES;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int num_tiles = p.m_tiles * p.n_tiles;
+  const int total_kb = p.k_blocks * p.passes;
+
+  if (tid == 0) {
+    for (int s = 0; s < kMaxStages; ++s) { mbar_init(smem_u32(&hdr->full[s]), 1); mbar_init(smem_u32(&hdr->empty[s]), 1); }
+    for (int s = 0; s < kAccStages; ++s) { mbar_init(smem_u32(&hdr->d_full[s]), 1); mbar_init(smem_u32(&hdr->d_empty[s]), kEpiWarps); }
+    hdr->abort_flag = 0u;
+    fence_barrier_init();
+    prefetch_tensormap(&maps.a[0]);
+    prefetch_tensormap(&maps.b);
+    prefetch_tensormap(&maps.y);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&hdr->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = hdr->tmem_base;
+  volatile uint32_t* abort_flag = &hdr->abort_flag;
+
+  if (warp == 0) {
+    // ===================== TMA producer (whole warp loops, one elected lane issues) =====================
+    uint32_t stage = 0, phase = 0, issued = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      const int n_blk = t % p.n_tiles, m_blk = t / p.n_tiles;
+      int ow0 = 0, oh0 = 0, b0 = 0;
+      if (p.conv) {
+        ow0 = (m_blk % p.tiles_w) * p.tw;
+        oh0 = ((m_blk / p.tiles_w) % p.tiles_h) * p.th;
+        b0 = (m_blk / (p.tiles_w * p.tiles_h)) * p.tb;
+      }
+      for (int pass = 0; pass < p.passes && ok; ++pass) {
+        int tap = 0, cb = 0;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->empty[stage]), phase ^ 1u, abort_flag, 0x1100u | stage))) { ok = false; break; }
+          const uint32_t full = smem_u32(&hdr->full[stage]);
+          const uint32_t dst_a = smem_u32(smem + stage * stage_bytes);
+          const uint32_t dst_b = dst_a + kABytes;
+          const int kcol_b = (pass * p.k_blocks + kb) * kBK;
+          if (!p.conv) {
+            if (elect_one()) {
+              mbar_arrive_expect_tx(full, stage_bytes);
+              tma_load_2d(dst_a, &maps.a[0], full, kb * kBK, m_blk * kBM);
+              tma_load_2d(dst_b, &maps.b, full, kcol_b, n_blk * p.bn);
+            }
+          } else {
+            // tap (kh, kw), channels [64 cb, 64 cb + 64): input pixel = stride * out + tap offset.  With
+            // stride 2 the input is addressed through one tensor map per (row, column) parity, so the box
+            // stays dense; taps that fall outside the image read the zero fill.
+            const int kh = tap / p.KW, kw = tap - kh * p.KW;
+            const int dy = kh * p.dil_h - p.pad_h, dx = kw * p.dil_w - p.pad_w;
+            int map = 0, hy = oh0 + dy, wx = ow0 + dx;
+            if (p.stride == 2) {
+              const int py = dy & 1, px = dx & 1;
+              map = py * 2 + px;
+              hy = oh0 + ((dy - py) >> 1);
+              wx = ow0 + ((dx - px) >> 1);
+            }
+            if (elect_one()) {
+              mbar_arrive_expect_tx(full, stage_bytes);
+              tma_load_4d(dst_a, &maps.a[map], full, cb * kBK, wx, hy, b0);
+              tma_load_2d(dst_b, &maps.b, full, kcol_b, n_blk * p.bn);
+            }
+            if (++cb == p.c_blocks) { cb = 0; ++tap; }
+          }
+          __syncwarp();
+          ++issued;
+          if (++stage == n_st) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+    if (!ok && lane == 0) {
+      // gave up: wait (bounded) for the copies still in flight so that none lands after the CTA has exited
+      const uint32_t n_back = issued < n_st ? issued : n_st;
+      uint32_t s = stage, ph = phase;
+      for (uint32_t i = 0; i < n_back; ++i) {
+        if (s == 0) { s = n_st - 1; ph ^= 1u; } else { --s; }
+        for (uint32_t it = 0; it < kSpinLimit; ++it)
+          if (mbar_try_wait(smem_u32(&hdr->full[s]), ph)) break;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ===================== MMA issuer (whole warp loops, one elected lane issues) =====================
+    uint32_t stage = 0, phase = 0, as = 0, aph = 0;
+    bool ok = true;
+    const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem));
+    const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(smem + kABytes));
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->d_empty[as]), aph ^ 1u, abort_flag, 0x1200u | as))) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + as * kAccCols;
+      for (int kb = 0; kb < total_kb; ++kb) {
+        if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->full[stage]), phase, abort_flag, 0x1300u | stage))) { ok = false; break; }
+        tc_fence_after();
+        if (elect_one()) {
+          const uint64_t off = static_cast<uint64_t>(stage * (stage_bytes >> 4));
+          const uint64_t a_desc = a_desc0 + off, b_desc = b_desc0 + off;
+#pragma unroll
+          for (int j = 0; j < kBK / 16; ++j)   // 16 k = 32 bytes inside the swizzled row (encoded >> 4)
+            mma_f16_ss(d_tmem, a_desc + static_cast<uint64_t>(2 * j), b_desc + static_cast<uint64_t>(2 * j), p.idesc,
+                       (kb | j) ? 1u : 0u);
+          mma_commit(smem_u32(&hdr->empty[stage]));   // frees the stage when these MMAs have read it
+        }
+        __syncwarp();
+        if (++stage == n_st) { stage = 0; phase ^= 1u; }
+      }
+      if (!ok) break;
+      if (elect_one()) mma_commit(smem_u32(&hdr->d_full[as]));
+      __syncwarp();
+      if (++as == kAccStages) { as = 0; aph ^= 1u; }
+    }
+  } else {
+    // ===================== epilogue =====================
+    const int quarter = warp & 3;          // TMEM lanes [32 quarter, 32 quarter + 32) = rows of the tile
+    const int sub = (warp - 2) >> 2;       // which of the two warps of this quarter: chunks sub, sub + 2, ...
+    const int ew = warp - 2;
+    float* my_bias = bias_area + ew * 32;
+    unsigned char* my_out = staging + ew * kStagingBytes;
+    const int n_chunks = p.bn / 32;
+    uint32_t as = 0, aph = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      const int n_blk = t % p.n_tiles, m_blk = t / p.n_tiles;
+      // where this thread's output row lives (for the residual); the store itself goes through TMA
+      int64_t row_off = -1;    // element offset of [row][0] in y, or -1 when the row is outside the tensor
+      int c1 = 0, c2 = 0, c3 = 0;   // TMA store coordinates of this warp's 32 rows
+      if (!p.conv) {
+        const int64_t row = static_cast<int64_t>(m_blk) * kBM + quarter * 32 + lane;
+        if (row < p.M) row_off = row * p.N;
+        c1 = m_blk * kBM + quarter * 32;
+      } else {
+        const int pj = quarter * 32 + lane;
+        const int ww = pj % p.tw, hh = (pj / p.tw) % p.th, bb = pj / (p.tw * p.th);
+        const int ow = (m_blk % p.tiles_w) * p.tw + ww;
+        const int oh = ((m_blk / p.tiles_w) % p.tiles_h) * p.th + hh;
+        const int ob = (m_blk / (p.tiles_w * p.tiles_h)) * p.tb + bb;
+        if (ob < p.Bn && oh < p.OH && ow < p.OW)
+          row_off = ((static_cast<int64_t>(ob) * p.OH + oh) * p.OW + ow) * p.N;
+        const int p0 = quarter * 32;         // all tile dimensions are powers of two: 32 pixels form a box
+        c1 = (m_blk % p.tiles_w) * p.tw + p0 % p.tw;
+        c2 = ((m_blk / p.tiles_w) % p.tiles_h) * p.th + (p0 / p.tw) % p.th;
+        c3 = (m_blk / (p.tiles_w * p.tiles_h)) * p.tb + p0 / (p.tw * p.th);
+      }
+      // tcgen05.ld is warp-collective: the whole warp proceeds or the whole warp gives up
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->d_full[as]), aph, abort_flag, 0x1500u | as))) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * kAccCols;
+      if (sub >= n_chunks) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&hdr->d_empty[as]));
+      }
+      for (int c = sub; c < n_chunks; c += 2) {
+        const int64_t n_first = static_cast<int64_t>(n_blk) * p.bn + c * 32;
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld32(d_tmem + c * 32, r);
+        // bias slice of this chunk, one feature per lane, while the load is in flight
+        const float bj = (p.bias != nullptr && n_first + lane < p.N) ? load_as_float(p.bias, p.bias_dtype, n_first + lane) : 0.0f;
+        my_bias[lane] = bj;
+        tmem_ld_wait();
+        if (c + 2 >= n_chunks) {
+          // every column this warp reads of the buffer is in registers: hand it back to the MMA warp
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&hdr->d_empty[as]));
+        }
+        __syncwarp();
+        if (n_first >= p.N) continue;        // chunk beyond the last feature (warp-uniform)
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        float res[32];
+        const int64_t left = p.N - n_first;
+        const int valid = left >= 32 ? 32 : static_cast<int>(left);
+        if (p.residual != nullptr) {
+          if (row_off >= 0)
+            load_residual<ES>(static_cast<const char*>(p.residual) + (row_off + n_first) * ES, p.y_dtype, valid, res);
+          else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) res[j] = 0.0f;
+          }
+          finish_row_epi<true>(v, my_bias, res, (p.epilogue == DIMQ_EPI_GELU && ES == 2) ? kEpiGelu16 : p.epilogue);
+        } else {
+          finish_row_epi<false>(v, my_bias, res, (p.epilogue == DIMQ_EPI_GELU && ES == 2) ? kEpiGelu16 : p.epilogue);
+        }
+        // the previous store of this warp must have finished reading the staging tile
+        if (elect_one()) tma_store_wait_read();
+        __syncwarp();
+        if (ES == 2) {
+          // [32 rows][64 bytes], 64-byte swizzle: 16-byte piece j of row r sits at piece j ^ ((r >> 1) & 3)
+          unsigned char* row_ptr = my_out + lane * 64;
+          const int sw = (lane >> 1) & 3;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 q;
+            q.x = pack16(v[8 * j], v[8 * j + 1], p.y_dtype);
+            q.y = pack16(v[8 * j + 2], v[8 * j + 3], p.y_dtype);
+            q.z = pack16(v[8 * j + 4], v[8 * j + 5], p.y_dtype);
+            q.w = pack16(v[8 * j + 6], v[8 * j + 7], p.y_dtype);
+            *reinterpret_cast<uint4*>(row_ptr + ((j ^ sw) << 4)) = q;
+          }
+        } else {
+          // [32 rows][128 bytes], 128-byte swizzle: piece j of row r sits at piece j ^ (r & 7)
+          unsigned char* row_ptr = my_out + lane * 128;
+          const int sw = lane & 7;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<float4*>(row_ptr + ((j ^ sw) << 4)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (elect_one()) {
+          if (p.conv) tma_store_4d(&maps.y, smem_u32(my_out), static_cast<int>(n_first), c1, c2, c3);
+          else tma_store_2d(&maps.y, smem_u32(my_out), static_cast<int>(n_first), c1);
+          tma_store_commit();
+        }
+      }
+      if (++as == kAccStages) { as = 0; aph ^= 1u; }
+    }
+    __syncwarp();
+    if (elect_one()) tma_store_wait_all();
+    __syncwarp();
+  }
+
+  // ---- teardown -----------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- step 1: expand the index stream to 16-bit codewords ---------------------------------------
+// One thread = 32 consecutive indices of one row (4 * BITS bytes, 4-byte aligned because K % 64 == 0).
+// out[row][k] (row pitch passes * K) = codeword in `fmt` (0 fp16, 1 bf16); with passes == 2 the bf16
+// remainder c - bf16(c) goes to out[row][K + k], so that hi + lo carries the codeword to ~2^-17.
+template <int BITS>
+__global__ void __launch_bounds__(256)
+lut_expand_kernel(const uint8_t* __restrict__ packed, const void* __restrict__ codebooks, int cb_dtype, int entries,
+                  int64_t group_rows, int64_t rows, int64_t K, int fmt, int passes, uint16_t* __restrict__ out) {
+  const int64_t units_per_row = K / 32;
+  const int64_t u = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (u >= rows * units_per_row) return;
+  const int64_t row = u / units_per_row;
+  const int64_t k0 = (u - row * units_per_row) * 32;
+  const uint32_t* src = reinterpret_cast<const uint32_t*>(packed + (row * K + k0) * BITS / 8);
+  uint32_t w[BITS];
+#pragma unroll
+  for (int i = 0; i < BITS; ++i) w[i] = __ldg(src + i);
+  const int64_t cb0 = (row / group_rows) * entries;
+  uint16_t hi[32], lo[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int bit = i * BITS, word = bit >> 5, sh = bit & 31;
+    uint32_t idx = w[word] >> sh;
+    if (sh + BITS > 32) idx |= w[word + 1 < BITS ? word + 1 : word] << (32 - sh);
+    idx &= (1u << BITS) - 1u;
+    const float c = idx < static_cast<uint32_t>(entries) ? load_as_float(codebooks, cb_dtype, cb0 + idx) : 0.0f;
+    if (fmt == 0) {
+      hi[i] = __half_as_ushort(__float2half_rn(c));
+      lo[i] = 0;
+    } else {
+      const __nv_bfloat16 h = __float2bfloat16_rn(c);
+      hi[i] = __bfloat16_as_ushort(h);
+      lo[i] = __bfloat16_as_ushort(__float2bfloat16_rn(c - __bfloat162float(h)));
+    }
+  }
+  uint16_t* dst = out + row * (K * passes) + k0;
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    uint4 q;
+    q.x = hi[8 * v] | (static_cast<uint32_t>(hi[8 * v + 1]) << 16);
+    q.y = hi[8 * v + 2] | (static_cast<uint32_t>(hi[8 * v + 3]) << 16);
+    q.z = hi[8 * v + 4] | (static_cast<uint32_t>(hi[8 * v + 5]) << 16);
+    q.w = hi[8 * v + 6] | (static_cast<uint32_t>(hi[8 * v + 7]) << 16);
+    reinterpret_cast<uint4*>(dst)[v] = q;
+  }
+  if (passes == 2) {
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      uint4 q;
+      q.x = lo[8 * v] | (static_cast<uint32_t>(lo[8 * v + 1]) << 16);
+      q.y = lo[8 * v + 2] | (static_cast<uint32_t>(lo[8 * v + 3]) << 16);
+      q.z = lo[8 * v + 4] | (static_cast<uint32_t>(lo[8 * v + 5]) << 16);
+      q.w = lo[8 * v + 6] | (static_cast<uint32_t>(lo[8 * v + 7]) << 16);
+      reinterpret_cast<uint4*>(dst + K)[v] = q;
+    }
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      return reinterpret_cast<EncodeTiledFn>(sym);
+    return static_cast<EncodeTiledFn>(nullptr);
+  }();
+  return fn;
+}
+
+CUtensorMapDataType map_dtype(int dtype) {
+  return dtype == DIMQ_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                           : (dtype == DIMQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+}
+
+// Weight rows per tile: the candidate that needs the fewest cycles for the whole problem under a
+// simple model - waves of tiles over the SMs times the measured cycles of a 64-k block (four MMAs and
+// a commit: ~590 at N = 256, ~450 at N = 128, ~430 at N = 64: below N = 256 the per-instruction floor
+// of about 106 cycles shows).
+int choose_bn(int64_t m_tiles, int64_t N) {
+  const int cand[3] = {256, 128, 64};
+  const double cycles[3] = {590.0, 450.0, 430.0};
+  int best = 256;
+  double best_cost = -1.0;
+  for (int i = 0; i < 3; ++i) {
+    const int64_t tiles = m_tiles * ((N + cand[i] - 1) / cand[i]);
+    const double cost = static_cast<double>((tiles + kNumSMs - 1) / kNumSMs) * cycles[i];
+    if (best_cost < 0.0 || cost < best_cost) { best_cost = cost; best = cand[i]; }
+  }
+  return best;
+}
+
+int expand(const dimq_wq_weight* w, const uint8_t* packed, int64_t rows, int64_t K, int fmt, int passes, void* scratch,
+           cudaStream_t st) {
+  const int64_t units = rows * (K / 32);
+  const unsigned blocks = static_cast<unsigned>((units + 255) / 256);
+  uint16_t* out = static_cast<uint16_t*>(scratch);
+#define DIMQ_EXPAND_CASE(B)                                                                                     \
+  case B:                                                                                                       \
+    lut_expand_kernel<B><<<blocks, 256, 0, st>>>(packed, w->codebooks, w->cb_dtype, w->entries, w->group_rows,  \
+                                                 rows, K, fmt, passes, out);                                    \
+    break;
+  switch (w->bits) {
+    DIMQ_EXPAND_CASE(2)
+    DIMQ_EXPAND_CASE(3)
+    DIMQ_EXPAND_CASE(4)
+    DIMQ_EXPAND_CASE(8)
+    default: return DIMQ_ERR_BAD_BITS;
+  }
+#undef DIMQ_EXPAND_CASE
+  return launch_status();
+}
+
+// Shared tail of the GEMM and the convolution launchers: weight map, shared-memory budget, launch.
+int launch_dense(DenseMaps& maps, DenseParams& p, const void* scratch, int64_t K, int x_dtype, const void* bias,
+                 int bias_dtype, const void* residual, int y_dtype, int epilogue, cudaStream_t st) {
+  EncodeTiledFn encode = encode_tiled();
+  if (encode == nullptr) return DIMQ_ERR_DRIVER;
+  p.bias = bias;
+  p.bias_dtype = bias_dtype;
+  p.residual = residual;
+  p.y_dtype = y_dtype;
+  p.epilogue = epilogue;
+  p.k_blocks = static_cast<int>(K / kBK);
+  p.b_bytes = static_cast<uint32_t>(p.bn) * kBK * 2;
+  const int fmt = x_dtype == DIMQ_BF16 ? 1 : 0;
+  p.idesc = tc::make_idesc_f16(fmt, fmt, kBM, p.bn);
+  const cuuint64_t bdims[2] = {static_cast<cuuint64_t>(K * p.passes), static_cast<cuuint64_t>(p.N)};
+  const cuuint64_t bstr[1] = {static_cast<cuuint64_t>(K * p.passes) * 2};
+  const cuuint32_t bbox[2] = {kBK, static_cast<cuuint32_t>(p.bn)};
+  const cuuint32_t estr[2] = {1, 1};
+  if (encode(&maps.b, fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+             const_cast<void*>(scratch), bdims, bstr, bbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return DIMQ_ERR_DRIVER;
+  const int es = y_dtype == DIMQ_F32 ? 4 : 2;
+  const size_t fixed = 1024 + kHeaderBytes + kBiasBytes + static_cast<size_t>(kEpiWarps) * 32 * 32 * es;
+  const size_t stage_bytes = kABytes + p.b_bytes;
+  int stages = static_cast<int>((kSmemMax - fixed) / stage_bytes);
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 3) return DIMQ_ERR_UNSUPPORTED;
+  p.stages = stages;
+  const size_t smem = fixed + stages * stage_bytes;
+  const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
+  if (tiles >= 0x7FFFFFFF) return DIMQ_ERR_TOO_LARGE;
+  const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
+  cudaError_t e;
+  if (es == 2) {
+    e = cudaFuncSetAttribute(lut_dense_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    lut_dense_tc_kernel<2><<<grid, kThreads, smem, st>>>(maps, p);
+  } else {
+    e = cudaFuncSetAttribute(lut_dense_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    lut_dense_tc_kernel<4><<<grid, kThreads, smem, st>>>(maps, p);
+  }
+  return launch_status();
+}
+
+bool out_map(EncodeTiledFn encode, CUtensorMap* m, const void* base, int dtype, int rank, const cuuint64_t* dims,
+             const cuuint32_t* box) {
+  const cuuint64_t es = dtype == DIMQ_F32 ? 4 : 2;
+  cuuint64_t strides[3];
+  cuuint64_t acc = dims[0] * es;
+  for (int i = 0; i < rank - 1; ++i) { strides[i] = acc; acc *= dims[i + 1]; }
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  return encode(m, map_dtype(dtype), rank, const_cast<void*>(base), dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, es == 4 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// hi + lo split of the codewords: bf16 activations with a codebook that is not stored in bf16
+int passes_for(int x_dtype, const dimq_wq_weight* w) { return (x_dtype == DIMQ_BF16 && w->cb_dtype != DIMQ_BF16) ? 2 : 1; }
+
+}  // namespace
+
+// ---- GEMM ----------------------------------------------------------------------------------------
+
+// Smallest M for which expanding the weight first pays (below it the in-pipeline kernel or its split-K
+// form runs: the expansion and the second launch cost a few microseconds).
+constexpr int64_t kDenseMinRows = 1024;
+
+bool dense_pays(int64_t rows) { return rows >= kDenseMinRows; }
+
+bool dense_supported(const void* x, int x_dtype, const dimq_wq_weight* w, const void* y, int y_dtype,
+                     const void* residual, int64_t M, int64_t N, int64_t K) {
+  if (x_dtype != DIMQ_BF16 && x_dtype != DIMQ_F16) return false;
+  if (y_dtype != x_dtype && y_dtype != DIMQ_F32) return false;
+  if (M < 1 || N < 1 || K < kBK || K % kBK != 0) return false;
+  if (M > 0x7FFFFFFF / 2 || N > 0x7FFFFFFF / 2) return false;
+  const int64_t es = y_dtype == DIMQ_F32 ? 4 : 2;
+  if (!aligned(x, 16) || !aligned(w->packed, 4) || !aligned(y, 16) || (N * es) % 16 != 0) return false;
+  if (residual != nullptr && !aligned(residual, 16)) return false;
+  return w->bits == 2 || w->bits == 3 || w->bits == 4 || w->bits == 8;
+}
+
+int64_t dense_workspace_bytes(int x_dtype, const dimq_wq_weight* w, int64_t N, int64_t K) {
+  return N * K * 2 * passes_for(x_dtype, w);
+}
+
+int launch_linear_wq_dense(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
+                           const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K, int epilogue,
+                           void* workspace, int64_t workspace_bytes, cudaStream_t st) {
+  if (!dense_supported(x, x_dtype, w, y, y_dtype, residual, M, N, K)) return DIMQ_ERR_UNSUPPORTED;
+  if (workspace == nullptr || workspace_bytes < dense_workspace_bytes(x_dtype, w, N, K)) return DIMQ_ERR_SCRATCH_TOO_SMALL;
+  if (!aligned(workspace, 16)) return DIMQ_ERR_ALIGNMENT;
+  EncodeTiledFn encode = encode_tiled();
+  if (encode == nullptr) return DIMQ_ERR_DRIVER;
+  DenseParams p;
+  memset(&p, 0, sizeof(p));
+  DenseMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  p.M = M;
+  p.N = N;
+  p.passes = passes_for(x_dtype, w);
+  p.m_tiles = static_cast<int>((M + kBM - 1) / kBM);
+  p.bn = choose_bn(p.m_tiles, N);
+  p.n_tiles = static_cast<int>((N + p.bn - 1) / p.bn);
+  const CUtensorMapDataType dt = x_dtype == DIMQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const cuuint64_t adims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
+  const cuuint64_t astr[1] = {static_cast<cuuint64_t>(K) * 2};
+  const cuuint32_t abox[2] = {kBK, kBM};
+  const cuuint32_t estr[2] = {1, 1};
+  if (encode(&maps.a[0], dt, 2, const_cast<void*>(x), adims, astr, abox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return DIMQ_ERR_DRIVER;
+  const cuuint64_t odims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M)};
+  const cuuint32_t obox[2] = {32, 32};
+  if (!out_map(encode, &maps.y, y, y_dtype, 2, odims, obox)) return DIMQ_ERR_DRIVER;
+  int rc = expand(w, w->packed, N, K, x_dtype == DIMQ_BF16 ? 1 : 0, p.passes, workspace, st);
+  if (rc != DIMQ_OK) return rc;
+  return launch_dense(maps, p, workspace, K, x_dtype, bias, bias_dtype, residual, y_dtype, epilogue, st);
+}
+
+// ---- implicit-GEMM convolution ------------------------------------------------------------------------
+
+bool conv_dense_supported(const void* x, int x_dtype, const dimq_wq_weight* w, const dimq_conv_geom* g, const void* y,
+                          int y_dtype, const void* residual) {
+  if (w->packed_khwc == nullptr) return false;
+  if (x_dtype != DIMQ_BF16 && x_dtype != DIMQ_F16) return false;
+  if (y_dtype != x_dtype && y_dtype != DIMQ_F32) return false;
+  if (g->groups != 1 || g->in_channels % kBK != 0) return false;
+  if (g->stride_h != g->stride_w || (g->stride_h != 1 && g->stride_h != 2)) return false;
+  if (g->stride_h == 2 && (g->in_w < 2 || g->in_h < 2)) return false;   // a parity plane would be empty
+  const int64_t C = g->in_channels, W = g->in_w, H = g->in_h;
+  if (g->x_stride[1] != 1 || g->x_stride[3] != C || g->x_stride[2] != W * C || g->x_stride[0] != H * W * C) return false;
+  const int64_t OC = g->out_channels, OW = g->out_w, OH = g->out_h;
+  if (g->y_stride[1] != 1 || g->y_stride[3] != OC || g->y_stride[2] != OW * OC || g->y_stride[0] != OH * OW * OC) return false;
+  const int64_t es = y_dtype == DIMQ_F32 ? 4 : 2;
+  if (!aligned(x, 16) || !aligned(w->packed_khwc, 4) || !aligned(y, 16) || (OC * es) % 16 != 0) return false;
+  if (residual != nullptr && !aligned(residual, 16)) return false;
+  return g->batch >= 1 && OW >= 1 && OH >= 1;
+}
+
+int64_t conv_dense_workspace_bytes(int x_dtype, const dimq_wq_weight* w, const dimq_conv_geom* g) {
+  return static_cast<int64_t>(g->out_channels) * g->kernel_h * g->kernel_w * g->in_channels * 2 * passes_for(x_dtype, w);
+}
+
+int launch_conv2d_wq_dense(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
+                           const void* residual, void* y, int y_dtype, const dimq_conv_geom* g, int epilogue,
+                           void* workspace, int64_t workspace_bytes, cudaStream_t st) {
+  if (!conv_dense_supported(x, x_dtype, w, g, y, y_dtype, residual)) return DIMQ_ERR_UNSUPPORTED;
+  if (workspace == nullptr || workspace_bytes < conv_dense_workspace_bytes(x_dtype, w, g)) return DIMQ_ERR_SCRATCH_TOO_SMALL;
+  if (!aligned(workspace, 16)) return DIMQ_ERR_ALIGNMENT;
+  EncodeTiledFn encode = encode_tiled();
+  if (encode == nullptr) return DIMQ_ERR_DRIVER;
+  const int OW = g->out_w, OH = g->out_h, B = g->batch;
+  // Tile = tw x th x tb output pixels with tw * th * tb = 128, so every factor is a power of two and
+  // any 32 consecutive tile pixels form a box (the TMA store of the epilogue needs that).  Prefer the
+  // shape that wastes the fewest rows on positions outside the image, then the widest.
+  int best_tw = 0, best_th = 0, best_tb = 0;
+  double best_score = -1.0;
+  for (int tw = 1; tw <= kBM; tw *= 2) {
+    for (int th = 1; tw * th <= kBM; th *= 2) {
+      const int tb = kBM / (tw * th);
+      const double covered = static_cast<double>((OW + tw - 1) / tw) * tw * ((OH + th - 1) / th) * th * ((B + tb - 1) / tb) * tb;
+      const double score = static_cast<double>(OW) * OH * B / covered + 1e-4 * tw + 1e-6 * th;
+      if (score > best_score) { best_score = score; best_tw = tw; best_th = th; best_tb = tb; }
+    }
+  }
+  DenseParams p;
+  memset(&p, 0, sizeof(p));
+  DenseMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  p.conv = 1;
+  p.tw = best_tw;
+  p.th = best_th;
+  p.tb = best_tb;
+  p.tiles_w = (OW + best_tw - 1) / best_tw;
+  p.tiles_h = (OH + best_th - 1) / best_th;
+  const int64_t m_tiles = static_cast<int64_t>(p.tiles_w) * p.tiles_h * ((B + best_tb - 1) / best_tb);
+  if (m_tiles >= 0x7FFFFFFF) return DIMQ_ERR_TOO_LARGE;
+  p.m_tiles = static_cast<int>(m_tiles);
+  p.OW = OW;
+  p.OH = OH;
+  p.Bn = B;
+  p.stride = g->stride_h;
+  p.pad_h = g->pad_h;
+  p.pad_w = g->pad_w;
+  p.dil_h = g->dilation_h;
+  p.dil_w = g->dilation_w;
+  p.KW = g->kernel_w;
+  p.c_blocks = g->in_channels / kBK;
+  p.M = static_cast<int64_t>(B) * OH * OW;
+  p.N = g->out_channels;
+  p.passes = passes_for(x_dtype, w);
+  p.bn = choose_bn(p.m_tiles, p.N);
+  p.n_tiles = static_cast<int>((p.N + p.bn - 1) / p.bn);
+  const int64_t K = static_cast<int64_t>(g->kernel_h) * g->kernel_w * g->in_channels;
+
+  const int s = g->stride_h;
+  const int64_t C = g->in_channels, W = g->in_w, H = g->in_h;
+  const CUtensorMapDataType dt = x_dtype == DIMQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  for (int py = 0; py < s; ++py) {
+    for (int px = 0; px < s; ++px) {
+      const int64_t Wp = (W - px + s - 1) / s, Hp = (H - py + s - 1) / s;
+      const cuuint64_t dims[4] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(Wp), static_cast<cuuint64_t>(Hp),
+                                  static_cast<cuuint64_t>(B)};
+      const cuuint64_t strides[3] = {static_cast<cuuint64_t>(s * C * 2), static_cast<cuuint64_t>(s * W * C * 2),
+                                     static_cast<cuuint64_t>(H * W * C * 2)};
+      const cuuint32_t box[4] = {kBK, static_cast<cuuint32_t>(best_tw), static_cast<cuuint32_t>(best_th),
+                                 static_cast<cuuint32_t>(best_tb)};
+      const cuuint32_t estr[4] = {1, 1, 1, 1};
+      void* base = const_cast<char*>(static_cast<const char*>(x)) + (py * W + px) * C * 2;
+      if (encode(&maps.a[py * s + px], dt, 4, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return DIMQ_ERR_DRIVER;
+    }
+  }
+  const int cbw = best_tw < 32 ? best_tw : 32;
+  const int cbh = best_th < 32 / cbw ? best_th : 32 / cbw;
+  const int cbb = 32 / (cbw * cbh);
+  const cuuint64_t odims[4] = {static_cast<cuuint64_t>(g->out_channels), static_cast<cuuint64_t>(OW),
+                               static_cast<cuuint64_t>(OH), static_cast<cuuint64_t>(B)};
+  const cuuint32_t obox[4] = {32, static_cast<cuuint32_t>(cbw), static_cast<cuuint32_t>(cbh), static_cast<cuuint32_t>(cbb)};
+  if (!out_map(encode, &maps.y, y, y_dtype, 4, odims, obox)) return DIMQ_ERR_DRIVER;
+  int rc = expand(w, w->packed_khwc, p.N, K, x_dtype == DIMQ_BF16 ? 1 : 0, p.passes, workspace, st);
+  if (rc != DIMQ_OK) return rc;
+  return launch_dense(maps, p, workspace, K, x_dtype, bias, bias_dtype, residual, y_dtype, epilogue, st);
+}
+
+}  // namespace dimq

@@ -1221,6 +1221,9 @@ bool conv_tc_supported(const void* x, int x_dtype, const dimq_wq_weight* w, cons
   if (y_dtype != x_dtype && y_dtype != DIMQ_F32) return false;
   if (g->groups != 1 || g->in_channels % kBlockK != 0) return false;
   if (g->stride_h != g->stride_w || (g->stride_h != 1 && g->stride_h != 2)) return false;
+  // stride 2 reads the input through one tensor map per (row, column) parity; a one-pixel-wide or
+  // one-pixel-high input has an empty parity plane, which no tensor map can describe
+  if (g->stride_h == 2 && (g->in_w < 2 || g->in_h < 2)) return false;
   // channels_last storage of both tensors
   const int64_t C = g->in_channels, W = g->in_w, H = g->in_h;
   if (g->x_stride[1] != 1 || g->x_stride[3] != C || g->x_stride[2] != W * C || g->x_stride[0] != H * W * C) return false;
@@ -1303,7 +1306,7 @@ int launch_conv2d_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, con
     for (int px = 0; px < s; ++px) {
       const int64_t Wp = (W - px + s - 1) / s, Hp = (H - py + s - 1) / s;
       CUtensorMap* m = &tmaps.m[py * s + px];
-      if (Wp <= 0 || Hp <= 0) { *m = tmaps.m[0]; continue; }   // parity without pixels: every tap there is padding
+      if (Wp <= 0 || Hp <= 0) return DIMQ_ERR_UNSUPPORTED;   // excluded by conv_tc_supported
       const cuuint64_t dims[4] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(Wp), static_cast<cuuint64_t>(Hp),
                                   static_cast<cuuint64_t>(B)};
       const cuuint64_t strides[3] = {static_cast<cuuint64_t>(s * C * 2), static_cast<cuuint64_t>(s * W * C * 2),

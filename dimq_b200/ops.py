@@ -22,7 +22,7 @@ from ._lib import ALGO_AUTO, ALGO_GENERIC, ALGO_STREAM, ALGO_TCGEN05, EPI_GELU, 
 
 _EPILOGUES = {None: EPI_NONE, "none": EPI_NONE, "relu": EPI_RELU, "gelu": EPI_GELU, "add_relu": _lib.EPI_ADD_RELU}
 _ALGOS = {None: ALGO_AUTO, "auto": ALGO_AUTO, "generic": ALGO_GENERIC, "stream": ALGO_STREAM,
-          "tcgen05": ALGO_TCGEN05, "mma_stream": 4}
+          "tcgen05": ALGO_TCGEN05, "mma_stream": 4, "expand": 5}
 
 
 def is_available() -> bool:
@@ -511,8 +511,27 @@ def dimq_linear_wq(x: torch.Tensor, packed_weight: torch.Tensor, codebooks: torc
         if residual.dtype != out_dtype or residual.numel() != y.numel():
             raise RuntimeError("residual must match the output shape and dtype")
         res = residual.contiguous()
+    if algo == "expand":
+        # always the two-step form: expand the indices to a 16-bit weight in scratch, then the dense
+        # TMA + tcgen05 GEMM
+        need = C.c_int64(0)
+        _lib.check(_lib.lib().dimq_expand_workspace_bytes(_lib.dtype_code(xc, "x"), C.byref(w), C.c_int64(out_features),
+                                                          C.c_int64(in_features), C.byref(need)), "expand_workspace_bytes")
+        ws = torch.empty(max(need.value, 16), dtype=torch.uint8, device=xc.device)
+        with torch.cuda.device(xc.device):
+            st = _lib.lib().dimq_linear_wq_expand(_lib.ptr(xc), _lib.dtype_code(xc, "x"), C.byref(w), _lib.ptr(b), b_dt,
+                                                  _lib.ptr(res), _lib.ptr(y), _lib.dtype_code(y, "y"), C.c_int64(m),
+                                                  C.c_int64(out_features), C.c_int64(in_features),
+                                                  _EPILOGUES[epilogue], _lib.ptr(ws), C.c_int64(ws.numel()),
+                                                  _lib.stream_ptr(xc.device))
+        _lib.check(st, "linear_wq_expand")
+        _lib.LAUNCH_COUNT[0] += 1  # the expansion and the GEMM
+        del keep
+        return y.view(*x.shape[:-1], out_features)
     if algo is None:
-        # shapes that would fill only a few SMs with long-K tiles get a workspace: the kernel splits K
+        # Two shapes get scratch memory: many activation rows (the indices are expanded once to a
+        # 16-bit weight and a dense tensor-core GEMM follows) and a few hundred rows against a long K
+        # (the kernel splits K and sums partial tiles there).
         need = C.c_int64(0)
         _lib.lib().dimq_linear_wq_workspace_bytes(_lib.ptr(xc), _lib.dtype_code(xc, "x"), C.byref(w), C.c_int64(m),
                                                   C.c_int64(out_features), C.c_int64(in_features), C.byref(need))
@@ -525,7 +544,7 @@ def dimq_linear_wq(x: torch.Tensor, packed_weight: torch.Tensor, codebooks: torc
                                                   _EPILOGUES[epilogue], _lib.ptr(ws), C.c_int64(need.value),
                                                   _lib.stream_ptr(xc.device))
             _lib.check(st, "linear_wq_ws")
-            _lib.LAUNCH_COUNT[0] += 1  # the GEMM and the kernel that finishes the sums
+            _lib.LAUNCH_COUNT[0] += 1  # two kernels: expansion + GEMM, or GEMM + the kernel that finishes the sums
             del keep
             return y.view(*x.shape[:-1], out_features)
     with torch.cuda.device(xc.device):
@@ -571,6 +590,31 @@ def dimq_conv2d_wq(x: torch.Tensor, packed_weight: torch.Tensor, codebooks: torc
         if residual.dtype != out_dtype or residual.shape != y.shape or residual.stride() != y.stride():
             raise RuntimeError("residual must match the output shape, dtype and memory format")
         res = residual
+    if algo in (None, "expand") and packed_khwc is not None:
+        # many output pixels: expand the re-ordered indices once to a 16-bit weight in scratch and run
+        # the dense implicit-GEMM kernel ("expand" forces that form at any size)
+        need = C.c_int64(0)
+        if algo == "expand":
+            numel_k = numel // g.out_channels
+            _lib.check(_lib.lib().dimq_expand_workspace_bytes(_lib.dtype_code(xc, "x"), C.byref(w),
+                                                              C.c_int64(g.out_channels), C.c_int64(numel_k),
+                                                              C.byref(need)), "expand_workspace_bytes")
+        else:
+            _lib.lib().dimq_conv2d_wq_workspace_bytes(_lib.ptr(xc), _lib.dtype_code(xc, "x"), C.byref(w), C.byref(g),
+                                                      C.byref(need))
+        if need.value > 0:
+            ws = torch.empty(need.value, dtype=torch.uint8, device=x.device)
+            fn = _lib.lib().dimq_conv2d_wq_expand if algo == "expand" else _lib.lib().dimq_conv2d_wq_ws
+            with torch.cuda.device(x.device):
+                st = fn(_lib.ptr(xc), _lib.dtype_code(xc, "x"), C.byref(w), _lib.ptr(b), b_dt, _lib.ptr(res), _lib.ptr(y),
+                        _lib.dtype_code(y, "y"), C.byref(g), _EPILOGUES[epilogue], _lib.ptr(ws), C.c_int64(need.value),
+                        _lib.stream_ptr(x.device))
+            _lib.check(st, "conv2d_wq_ws")
+            _lib.LAUNCH_COUNT[0] += 1  # the expansion and the convolution
+            del keep
+            return y
+    if algo == "expand":
+        raise RuntimeError("conv2d_wq: algo='expand' needs packed_khwc (see conv_prepack)")
     with torch.cuda.device(x.device):
         st = _lib.lib().dimq_conv2d_wq(_lib.ptr(xc), _lib.dtype_code(xc, "x"), C.byref(w), _lib.ptr(b), b_dt,
                                        _lib.ptr(res), _lib.ptr(y), _lib.dtype_code(y, "y"), C.byref(g),

@@ -192,18 +192,51 @@ DIMQ_API int dimq_conv2d_wq_static(const void* x, int x_dtype, const dimq_wq_wei
                                    int bias_dtype, const void* residual, void* y, int y_dtype,
                                    const dimq_conv_geom* geom, int epilogue, void* stream);
 
-/* dimq_linear_wq with a caller-owned fp32 workspace, for shapes whose tiles would occupy only a few
- * SMs while each walks a long K (a few hundred activation rows against a wide-K weight): the tcgen05
- * kernel then cuts K into slices (split-K), adds the partial sums into the workspace and a second
- * small kernel applies bias / epilogue / residual.  dimq_linear_wq_workspace_bytes reports M*N*4 when
- * that path would be taken and 0 otherwise (then this call is dimq_linear_wq with DIMQ_ALGO_AUTO and
- * the workspace is not touched).  The sum over slices uses float atomics: the result can differ in
- * the last bits from run to run.  No counterpart in the reference. */
+/* dimq_linear_wq with caller-owned scratch memory, which two regimes use:
+ *  - many activation rows (M >= 1024, 16-bit x, K a multiple of 64, 16-byte aligned y rows): the
+ *    indices are expanded ONCE per call into a 16-bit weight matrix in the workspace (N*K*2 bytes; twice
+ *    that when bf16 activations meet a codebook that is not stored in bf16 and every codeword is carried
+ *    as a hi + lo pair) and a dense TMA + tcgen05 GEMM runs over it.  Looking the indices up inside the
+ *    GEMM pipeline instead repeats the N*K lookups once per 192 activation rows.
+ *  - a few hundred activation rows against a long K, whose tiles would occupy only a few SMs: the
+ *    in-pipeline tcgen05 kernel cuts K into slices (split-K), adds the partial sums into the workspace
+ *    (M*N*4 bytes, float atomics: the last bits can differ from run to run) and a second small kernel
+ *    applies bias / epilogue / residual.
+ * dimq_linear_wq_workspace_bytes reports the bytes of the regime that applies and 0 otherwise (then
+ * dimq_linear_wq_ws is dimq_linear_wq with DIMQ_ALGO_AUTO and the workspace is not touched).  The
+ * workspace must be 16-byte aligned; its contents after the call are unspecified.  The reference has no
+ * counterpart: it dequantises the whole weight per call (dimq_backend/reference.py:47-56) or reads
+ * nibbles in its innermost loop (csrc/dimq_gemm_lut.cu:45-49). */
 DIMQ_API int dimq_linear_wq_workspace_bytes(const void* x, int x_dtype, const dimq_wq_weight* w, int64_t M, int64_t N,
                                             int64_t K, int64_t* bytes);
 DIMQ_API int dimq_linear_wq_ws(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
                                const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K,
                                int epilogue, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* The same for dimq_conv2d_wq: with w->packed_khwc, channels_last 16-bit x and y, groups 1, input
+ * channels a multiple of 64, stride 1 or 2 and at least 1024 output pixels, the re-ordered indices are
+ * expanded once into the workspace (OC*KH*KW*IC*2 bytes, doubled for hi + lo pairs as above) and the
+ * dense implicit-GEMM kernel runs; otherwise dimq_conv2d_wq_workspace_bytes reports 0 and
+ * dimq_conv2d_wq_ws is dimq_conv2d_wq with DIMQ_ALGO_AUTO. */
+DIMQ_API int dimq_conv2d_wq_workspace_bytes(const void* x, int x_dtype, const dimq_wq_weight* w,
+                                            const dimq_conv_geom* geom, int64_t* bytes);
+DIMQ_API int dimq_conv2d_wq_ws(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
+                               const void* residual, void* y, int y_dtype, const dimq_conv_geom* geom, int epilogue,
+                               void* workspace, int64_t workspace_bytes, void* stream);
+
+/* The expand-then-GEMM form requested explicitly, at any M (DIMQ_ERR_UNSUPPORTED where it cannot run:
+ * see the conditions above, without the row threshold).  dimq_expand_workspace_bytes gives the scratch
+ * size for `rows` weight rows of `row_len` indices each (linear: N rows of K; convolution: OC rows of
+ * KH*KW*IC).  No counterpart in the reference. */
+DIMQ_API int dimq_expand_workspace_bytes(int x_dtype, const dimq_wq_weight* w, int64_t rows, int64_t row_len,
+                                         int64_t* bytes);
+DIMQ_API int dimq_linear_wq_expand(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias,
+                                   int bias_dtype, const void* residual, void* y, int y_dtype, int64_t M, int64_t N,
+                                   int64_t K, int epilogue, void* workspace, int64_t workspace_bytes, void* stream);
+DIMQ_API int dimq_conv2d_wq_expand(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias,
+                                   int bias_dtype, const void* residual, void* y, int y_dtype,
+                                   const dimq_conv_geom* geom, int epilogue, void* workspace, int64_t workspace_bytes,
+                                   void* stream);
 
 /* ---- W4A4 product-table ops on the tensor cores ------------------------- */
 
