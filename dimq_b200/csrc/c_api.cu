@@ -42,6 +42,8 @@ int launch_conv2d_wq_dense(const void* x, int x_dtype, const dimq_wq_weight* w, 
                            void* workspace, int64_t workspace_bytes, cudaStream_t st);
 int read_device_status(uint32_t* status);
 int read_ms_status(uint32_t* status);
+int read_dense_status(uint32_t* status);
+int launch_bounded_wait_selftest(uint32_t polls, uint32_t* result, cudaStream_t st);
 }  // namespace dimq
 
 using namespace dimq;
@@ -80,13 +82,21 @@ extern "C" const char* dimq_status_string(int status) {
 
 extern "C" int dimq_last_device_status(uint32_t* status) {
   if (status == nullptr) return DIMQ_ERR_NULL_POINTER;
-  uint32_t tc = 0, ms = 0;
+  uint32_t tc = 0, ms = 0, dense = 0;
   int rc = read_device_status(&tc);
   if (rc != DIMQ_OK) return rc;
   rc = read_ms_status(&ms);
   if (rc != DIMQ_OK) return rc;
-  *status = tc | ms;
+  rc = read_dense_status(&dense);
+  if (rc != DIMQ_OK) return rc;
+  *status = tc | ms | dense;
   return DIMQ_OK;
+}
+
+extern "C" int dimq_selftest_bounded_wait(uint32_t polls, uint32_t* result, void* stream) {
+  if (result == nullptr) return DIMQ_ERR_NULL_POINTER;
+  if (polls == 0 || polls > 4096) return DIMQ_ERR_BAD_SIZE;   // at most 4096 polls of <= 20 us each
+  return launch_bounded_wait_selftest(polls, result, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int dimq_linear_wq(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias,

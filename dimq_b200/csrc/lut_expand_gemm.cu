@@ -612,6 +612,8 @@ int passes_for(int x_dtype, const dimq_wq_weight* w) { return (x_dtype == DIMQ_B
 
 }  // namespace
 
+int read_dense_status(uint32_t* status) { return tc::read_and_clear_device_status(status); }
+
 // ---- GEMM ----------------------------------------------------------------------------------------
 
 // Smallest M for which expanding the weight first pays (below it the in-pipeline kernel or its split-K

@@ -1336,12 +1336,36 @@ int launch_conv2d_wq_tc(const void* x, int x_dtype, const dimq_wq_weight* w, con
   return finish_launch(tmaps, p, w, w->packed_khwc, x_dtype, bias, bias_dtype, residual, y, y_dtype, epilogue, 0, st);
 }
 
-int read_device_status(uint32_t* status) {
-  cudaError_t e = cudaMemcpyFromSymbol(status, tc::g_device_status, sizeof(uint32_t));
-  if (e != cudaSuccess) return static_cast<int>(e);
-  const uint32_t zero = 0;
-  e = cudaMemcpyToSymbol(tc::g_device_status, &zero, sizeof(uint32_t));
-  return e == cudaSuccess ? DIMQ_OK : static_cast<int>(e);
+int read_device_status(uint32_t* status) { return tc::read_and_clear_device_status(status); }
+
+namespace {
+
+// One warp waits, with a poll limit the caller chooses, on an mbarrier that nothing ever arrives at,
+// and reports what the bounded wait did: result[0] = 1 if the wait returned "gave up", result[1] = the
+// CTA abort flag afterwards.  The status word is left set for dimq_last_device_status.
+__global__ void __launch_bounds__(32, 1) bounded_wait_selftest_kernel(uint32_t polls, uint32_t* result) {
+  __shared__ uint64_t bar;
+  __shared__ volatile uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    tc::mbar_init(tc::smem_u32(&bar), 1);
+    abort_flag = 0u;
+    tc::fence_barrier_init();
+  }
+  __syncwarp();
+  const bool got = tc::mbar_wait(tc::smem_u32(&bar), 0u, &abort_flag, 0x7E57u, polls);
+  const bool all_gave_up = __all_sync(0xFFFFFFFFu, !got);
+  __syncwarp();
+  if (threadIdx.x == 0) {
+    result[0] = all_gave_up ? 1u : 0u;
+    result[1] = abort_flag;
+  }
+}
+
+}  // namespace
+
+int launch_bounded_wait_selftest(uint32_t polls, uint32_t* result, cudaStream_t st) {
+  bounded_wait_selftest_kernel<<<1, 32, 0, st>>>(polls, result);
+  return launch_status();
 }
 
 }  // namespace dimq

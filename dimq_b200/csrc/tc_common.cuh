@@ -18,8 +18,19 @@ constexpr uint32_t kSpinLimit = 1u << 17;
 // is woken as soon as the phase completes, so a generous hint removes polling traffic, not latency.
 constexpr uint32_t kSuspendHintNs = 20000u;
 
-// Status word of the last tcgen05 kernel that gave up a wait (0 = none).
-__device__ uint32_t g_device_status;
+// Status word of the last tcgen05 kernel of THIS translation unit that gave up a wait (0 = none):
+// the variable has internal linkage, so every .cu file that includes this header owns one and
+// exports a reader for it (dimq_last_device_status ORs them).
+static __device__ uint32_t g_device_status;
+
+// Reads and clears this translation unit's status word (host side; synchronises the device).
+static inline int read_and_clear_device_status(uint32_t* status) {
+  cudaError_t e = cudaMemcpyFromSymbol(status, g_device_status, sizeof(uint32_t));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const uint32_t zero = 0;
+  e = cudaMemcpyToSymbol(g_device_status, &zero, sizeof(uint32_t));
+  return e == cudaSuccess ? DIMQ_OK : static_cast<int>(e);
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -70,8 +81,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait.  Returns false when the limit ran out or another thread of the
 // CTA already gave up; `code` identifies the waiter in the status word.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          uint32_t code) {
-  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+                                          uint32_t code, uint32_t limit = kSpinLimit) {
+  for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 255u) == 255u && *abort_flag != 0u) return false;
   }

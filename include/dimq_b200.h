@@ -288,9 +288,18 @@ DIMQ_API int dimq_im2col(const void* x, int dtype, const dimq_conv_geom* geom, i
 DIMQ_API int dimq_max_pool_nhwc(const void* x, void* y, int dtype, int64_t batch, int64_t height, int64_t width,
                                 int64_t channels, int kernel, int stride, int pad, void* stream);
 
-/* Status word written by the last tcgen05 kernel on this thread's device that
- * gave up a bounded wait (0 = none).  Reading it synchronises the device. */
+/* Status word written by the last tensor-core kernel on this thread's device that
+ * gave up a bounded wait (0 = none; bit 31 set plus a code naming the waiter otherwise).  Reading it
+ * synchronises the device and clears the word. */
 DIMQ_API int dimq_last_device_status(uint32_t* status);
+
+/* Health check of the bounded-wait mechanism every pipeline barrier of the tensor-core kernels uses:
+ * one warp waits on a barrier that nothing arrives at, gives up after `polls` polls (1..4096, each at
+ * most 20 us), and writes result[0] = 1 (the wait reported "gave up") and result[1] = the CTA's abort
+ * flag to the two device words at `result`.  dimq_last_device_status then returns 0x80007E57 once.
+ * The kernel returns normally: nothing traps or hangs.  No counterpart in the reference (its kernels
+ * have no device-side waits). */
+DIMQ_API int dimq_selftest_bounded_wait(uint32_t polls, uint32_t* result, void* stream);
 
 #ifdef __cplusplus
 }

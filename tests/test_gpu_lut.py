@@ -506,3 +506,29 @@ def test_conv2d_wq_generic_per_channel_codebooks(ops, bits):
                              (oc, icg, kh, kw), kwargs["stride"], kwargs["padding"], kwargs["dilation"], 2, bits=bits,
                              group_rows=1, epilogue="relu")
     np.testing.assert_allclose(got.cpu().numpy(), np.maximum(want, 0), rtol=1e-4, atol=1e-4)
+
+
+def test_bounded_wait_expires_and_the_context_stays_usable(ops):
+    """A wait with a short poll limit on a barrier nobody arrives at must give up, set the CTA abort
+    flag and the status word, and return; the status reads once and clears; a GEMM right after runs."""
+    import ctypes as C
+
+    from dimq_b200 import _lib
+
+    assert ops.last_device_status() == 0
+    result = torch.zeros(2, dtype=torch.int32, device="cuda")
+    st = _lib.lib().dimq_selftest_bounded_wait(C.c_uint32(16), _lib.ptr(result), _lib.stream_ptr(result.device))
+    assert st == 0
+    torch.cuda.synchronize()
+    assert result.tolist() == [1, 1]
+    assert ops.last_device_status() == 0x80007E57
+    assert ops.last_device_status() == 0                      # reading cleared it
+    assert _lib.lib().dimq_selftest_bounded_wait(C.c_uint32(0), _lib.ptr(result), None) == -2   # argument check
+    cw = make_weight(256, 512, 3, seed=1, group_rows=128, cb_dtype="bf16")
+    rng = np.random.default_rng(0)
+    for m in (400, 1500):       # the in-pipeline kernel and the expanded form, right after the expiry
+        x = bf16_round(rng.standard_normal((m, 512)).astype(np.float32))
+        got = ops.dimq_linear_wq(_cuda(x, torch.bfloat16), _cuda(cw["packed"]), _cuda(cw["codebooks"], torch.bfloat16),
+                                 None, 256, 512, bits=3, group_rows=128)
+        _assert_close(got, o.linear_wq(x, cw["packed"], cw["codebooks"], 3, 256, 512, None, 128), f"m={m}")
+    assert ops.last_device_status() == 0
