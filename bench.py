@@ -8,13 +8,19 @@ per 128 output rows) over a batch of 128 images per GPU, bf16 activations.  All 
 Linears run through ``libdimq_b200.so`` (weight-only LUT GEMM); attention, LayerNorm and the
 patch embedding are dense bf16 PyTorch ops.  Rank 0 prints one JSON line.
 
-``value``  — images/s with the images already in HBM (CUDA-graph replay, CUDA events).
-``e2e``    — the same forward called with pinned HOST images: H2D copy + forward + D2H of the
-             logits inside the timed region.
-``roofline`` — the LUT-GEMM kernel: algorithmic flops of the quantised Linears divided by the
-             summed CUDA-event duration of exactly those launches (an instrumented eager pass).
+``value``     — images/s with the images already in HBM (CUDA-graph replay, CUDA events).
+``e2e``       — the same forward called with pinned HOST images: H2D copy + forward + D2H of the
+                logits inside the timed region.
+``roofline``  — the quantised layers: their algorithmic flops divided by the summed CUDA-event
+                duration of exactly those calls (an instrumented eager pass).
+``secondary`` — the same numbers for the other model of the metric (ResNet-18, batch 256 per GPU,
+                4-bit per-layer codebooks, stem and classifier at 8 bits).
+``strong``    — N > 1 only: the configurations' batches (128 / 256) split over the GPUs, and the
+                gathered logits of one fixed batch compared with a single-GPU forward of it.
+``micro``     — the index-streaming regime: M in {1, 4, 16} on the 1024 -> 4096 / 4096 -> 1024 shapes
+                over a ring of distinct weights larger than the L2.
 ``cpu_baseline`` / ``--impl reference`` — the reference's CPU path (dequantise + fp32
-             ``F.linear``, PyTorch CPU, all host threads) on a bounded sample of the same workload.
+                ``F.linear`` / ``F.conv2d``, PyTorch CPU, all host threads) on a bounded sample.
 """
 
 from __future__ import annotations
@@ -42,9 +48,6 @@ WORKLOADS = {
 FALLBACK_TFLOPS = 1590.0
 FALLBACK_HBM_GBS = 6650.0
 CPU_SAMPLE_IMAGES = 8
-
-
-NCU_DRAM_BYTES_PER_FLOP = 16.45e6 / 38.65e9
 
 
 def _peaks():
@@ -223,6 +226,241 @@ def run_micro(args) -> None:
     }), flush=True)
 
 
+def small_m_micro(dev) -> dict:
+    """The index-streaming regime: M in {1, 4, 16} on the 1024 -> 4096 and 4096 -> 1024 shapes (4-bit,
+    bf16 activations, fp16 codebook as the reference's packed export stores it), the weight of every
+    call different and the ring of weights larger than the L2, one CUDA graph of back-to-back calls."""
+    import torch
+
+    from dimq_b200 import ops
+
+    path = ROOT / "MEASURED_PEAKS.json"
+    hbm_peak = float(json.loads(path.read_text()).get("hbm_gbs", FALLBACK_HBM_GBS)) if path.exists() else FALLBACK_HBM_GBS
+    out = {"unit": "us per call", "index_gbs_peak": hbm_peak, "peak_source": "measured" if path.exists() else "fallback",
+           "weights": "4-bit, one fp16 codebook per layer; a ring of 136 distinct 2 MB index tensors (272 MB > L2), L2-cold",
+           "cases": []}
+    copies, bits = 136, 4
+    for (k, n) in ((1024, 4096), (4096, 1024)):
+        index_bytes = n * k * bits // 8
+        packed = [torch.randint(0, 256, (index_bytes,), dtype=torch.uint8, device=dev) for _ in range(copies)]
+        cb = (torch.randn(1, 16, device=dev) * 0.02).sort(dim=1).values.to(torch.float16)
+        for m in (1, 4, 16):
+            x = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
+            call = lambda pw: ops.dimq_linear_wq(x, pw, cb, None, n, k, bits=bits, out_dtype=torch.bfloat16)
+            call(packed[0])
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for pw in packed:
+                    call(pw)
+            for _ in range(3):
+                graph.replay()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(5):
+                graph.replay()
+            end.record()
+            torch.cuda.synchronize()
+            us = start.elapsed_time(end) * 1e3 / (5 * copies)
+            out["cases"].append({"m": m, "k": k, "n": n, "us": us, "index_gbs": index_bytes / us / 1e3,
+                                 "index_gbs_frac": index_bytes / us / 1e3 / hbm_peak})
+        del packed
+    return out
+
+
+class ModelBench:
+    """One model on this rank: CUDA graphs over rotating inputs, timed resident and end to end."""
+
+    def __init__(self, workload: str, batch: int, dev, rank: int, seed_images: int = 1234):
+        import torch
+
+        from dimq_b200 import _lib
+        from dimq_b200.workloads import DIMQResNet18, DIMQViT, build_resnet18_checkpoint, build_vit_b16_checkpoint
+
+        self.workload, self.batch, self.dev = workload, batch, dev
+        if workload == "vit_b16":
+            self.ckpt = build_vit_b16_checkpoint(seed=0, device=dev)
+            self.model = DIMQViT(self.ckpt).to(dev).eval()
+            self.flops_per_step = self.model.lut_gemm_flops(batch)
+        else:
+            self.ckpt = build_resnet18_checkpoint(seed=0, device=dev)
+            self.model = DIMQResNet18(self.ckpt).to(dev).eval()
+            self.flops_per_step = self.model.lut_flops(batch)
+        self.n_bufs = 4  # rotating image buffers: with the activations of a step, far more than the 126 MB L2
+        gen = torch.Generator(device="cpu").manual_seed(seed_images + rank)
+        self.host_images = [torch.randn(batch, 3, 224, 224, generator=gen).to(torch.bfloat16).pin_memory()
+                            for _ in range(self.n_bufs)]
+        self.dev_images = [h.to(dev, non_blocking=True) for h in self.host_images]
+        torch.cuda.synchronize()
+        self.stream = torch.cuda.Stream(device=dev)
+        self.copy_stream = torch.cuda.Stream(device=dev)
+        self.gather_stream = torch.cuda.Stream(device=dev)
+        # two staging buffers: the host->device copy of step i + 1 runs on its own stream under step i
+        self.staging = [torch.empty_like(self.dev_images[0]) for _ in range(2)]
+        self.h2d_done = [torch.cuda.Event() for _ in range(2)]
+        self.compute_done = [torch.cuda.Event() for _ in range(2)]
+        self.host_logits = torch.empty(batch, 1000, dtype=torch.float32).pin_memory()
+        self.graphs, self.outs = [], []
+        self.gather_done = {}   # buffer index -> event of the last gather that read its logits
+        with torch.cuda.stream(self.stream):
+            for _ in range(2):
+                self.model(self.dev_images[0])
+            self.stream.synchronize()
+            before = _lib.LAUNCH_COUNT[0]
+            for src in self.dev_images + self.staging:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=self.stream):
+                    out = self.model(src)
+                self.graphs.append(g)
+                self.outs.append(out)
+            self.launches_per_forward = (_lib.LAUNCH_COUNT[0] - before) // len(self.graphs)
+
+    def _replay(self, buf: int, world: int) -> None:
+        """Replay the graph of buffer `buf`, then all-gather its logits on a side stream so that the
+        collective overlaps the next step's forward.  A replay waits for the gather that last read the
+        same logits buffer."""
+        import torch
+
+        from dimq_b200.dist import gather_logits
+
+        if buf in self.gather_done:
+            self.stream.wait_event(self.gather_done[buf])
+        self.graphs[buf].replay()
+        if world == 1:
+            return
+        done = torch.cuda.Event()
+        done.record(self.stream)
+        with torch.cuda.stream(self.gather_stream):
+            self.gather_stream.wait_event(done)
+            gather_logits(self.outs[buf])
+            ev = torch.cuda.Event()
+            ev.record(self.gather_stream)
+            self.gather_done[buf] = ev
+
+    def step_resident(self, i: int, world: int) -> None:
+        self._replay(i % self.n_bufs, world)
+
+    def step_e2e(self, i: int, world: int) -> None:
+        import torch
+
+        b = i % 2
+        with torch.cuda.stream(self.copy_stream):
+            self.copy_stream.wait_event(self.compute_done[b])  # the forward that last read this buffer
+            self.staging[b].copy_(self.host_images[i % self.n_bufs], non_blocking=True)
+            self.h2d_done[b].record(self.copy_stream)
+        self.stream.wait_event(self.h2d_done[b])
+        self._replay(self.n_bufs + b, world)
+        self.host_logits.copy_(self.outs[self.n_bufs + b], non_blocking=True)
+        self.compute_done[b].record(self.stream)
+
+    def run_timed(self, step_fn, steps: int, warmup: int, world: int) -> float:
+        """ms for `steps` steps: CUDA events on the launching stream, barrier + synchronize on both sides,
+        the side-stream gathers joined before the end event, max over ranks."""
+        import torch
+        import torch.distributed as dist
+
+        def barrier():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        with torch.cuda.stream(self.stream):
+            for i in range(warmup):
+                step_fn(i, world)
+            self.copy_stream.synchronize()
+            self.gather_stream.synchronize()
+            barrier()
+            start = torch.cuda.Event(enable_timing=True)
+            end = torch.cuda.Event(enable_timing=True)
+            start.record(self.stream)
+            self.copy_stream.wait_event(start)  # no copy of a timed step starts before the timed region
+            for i in range(steps):
+                step_fn(i, world)
+            self.stream.wait_stream(self.gather_stream)
+            end.record(self.stream)
+            barrier()
+            ms = torch.tensor([start.elapsed_time(end)], device=self.dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    def roofline(self, roof_steps: int = 3) -> dict:
+        """The quantised layers alone: an eager pass with CUDA events around every LUT linear / conv call
+        (launches queued behind a sleep kernel so that the events bracket execution, not launch gaps)."""
+        import torch
+
+        from dimq_b200 import modules as _modules
+        from dimq_b200 import ops
+
+        events = []
+        orig, orig_conv = ops.dimq_linear_wq, ops.dimq_conv2d_wq
+
+        def timed(fn):
+            def wrapper(*a, **kw):
+                s = torch.cuda.Event(enable_timing=True)
+                e = torch.cuda.Event(enable_timing=True)
+                s.record(torch.cuda.current_stream())
+                y = fn(*a, **kw)
+                e.record(torch.cuda.current_stream())
+                events.append((s, e))
+                return y
+            return wrapper
+
+        _modules.ops.dimq_linear_wq = timed(orig)
+        _modules.ops.dimq_conv2d_wq = timed(orig_conv)
+        try:
+            with torch.cuda.stream(self.stream):
+                for i in range(roof_steps):
+                    torch.cuda._sleep(int(60e6))
+                    self.model(self.dev_images[i % self.n_bufs])
+                self.stream.synchronize()
+        finally:
+            _modules.ops.dimq_linear_wq = orig
+            _modules.ops.dimq_conv2d_wq = orig_conv
+        ms = sum(s.elapsed_time(e) for s, e in events)
+        peak, peak_kind = _peaks()
+        achieved = self.flops_per_step * roof_steps / (ms / 1e3) / 1e12
+        return {"kernel": "lut_dense_tc_kernel (dense TMA + tcgen05 GEMM / implicit-GEMM conv over the weight "
+                          "lut_expand_kernel writes once per call; both kernels are inside the timed calls)",
+                "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "peak_source": peak_kind, "calls_timed": len(events), "avg_call_ms": ms / max(len(events), 1),
+                "flops_per_step": self.flops_per_step}
+
+    def release(self) -> None:
+        import torch
+
+        self.graphs.clear()
+        self.outs.clear()
+        self.model = None
+        torch.cuda.empty_cache()
+
+
+def parity_vs_one_gpu(workload: str, global_batch: int, dev, world: int, rank: int):
+    """Rank r runs its shard of one fixed global batch, the logits are all-gathered, and rank 0 compares
+    them with its own forward of the whole batch."""
+    import torch
+
+    from dimq_b200.dist import gather_logits, shard_bounds
+    from dimq_b200.workloads import DIMQResNet18, DIMQViT, build_resnet18_checkpoint, build_vit_b16_checkpoint
+
+    if workload == "vit_b16":
+        model = DIMQViT(build_vit_b16_checkpoint(seed=0, device=dev)).to(dev).eval()
+    else:
+        model = DIMQResNet18(build_resnet18_checkpoint(seed=0, device=dev)).to(dev).eval()
+    images = torch.randn(global_batch, 3, 224, 224, generator=torch.Generator().manual_seed(77)).to(torch.bfloat16)
+    lo, hi = shard_bounds(global_batch, rank, world)
+    local = model(images[lo:hi].to(dev)).float()
+    gathered = gather_logits(local, total=global_batch)
+    result = None
+    if rank == 0:
+        whole = model(images.to(dev)).float()
+        diff = (gathered - whole).double()
+        result = {"max_abs": float(diff.abs().max()), "rel_l2": float(diff.norm() / whole.double().norm())}
+    del model
+    torch.cuda.empty_cache()
+    return result
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -231,7 +469,9 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="vit_b16", choices=["vit_b16", "resnet18"],
-                    help="vit_b16 is the headline line; resnet18 prints the same line for the ResNet-18 config")
+                    help="the headline model of the line; the other one is reported under `secondary`")
+    ap.add_argument("--only", action="store_true", help="skip the secondary model, the strong-scaling pass and the "
+                                                         "small-M micro numbers (profiling runs)")
     ap.add_argument("--micro", default=None, metavar="M,K,N,BITS[,ALGO[,COPIES]]",
                     help="time one weight-only LUT GEMM instead of a model (bf16 activations, bf16 codebook per "
                          "128 rows at 3 bits, per layer otherwise); COPIES distinct weights are rotated so that "
@@ -249,9 +489,8 @@ def main() -> None:
     import torch
     import torch.distributed as dist
 
-    from dimq_b200 import _lib, ops
-    from dimq_b200.dist import gather_logits
-    from dimq_b200.workloads import DIMQResNet18, DIMQViT, build_resnet18_checkpoint, build_vit_b16_checkpoint
+    from dimq_b200 import ops
+    from dimq_b200.dist import shard_bounds
 
     ops.require_extension()  # no CPU fallback: fail loudly when the CUDA library is missing
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -264,125 +503,44 @@ def main() -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    WORKLOAD, B, weight_desc = WORKLOADS[args.workload]
+    other = "resnet18" if args.workload == "vit_b16" else "vit_b16"
+    results = {}
     with torch.no_grad():
-        if args.workload == "vit_b16":
-            ckpt = build_vit_b16_checkpoint(seed=0, device=dev)
-            model = DIMQViT(ckpt).to(dev).eval()
-            flops_per_step = model.lut_gemm_flops(B)
-        else:
-            ckpt = build_resnet18_checkpoint(seed=0, device=dev)
-            model = DIMQResNet18(ckpt).to(dev).eval()
-            flops_per_step = model.lut_flops(B)
-        n_bufs = 4  # rotating image buffers (4 x 38.5 MB or more): larger than the 126 MB L2
-        gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
-        host_images = [torch.randn(B, 3, 224, 224, generator=gen).to(torch.bfloat16).pin_memory() for _ in range(n_bufs)]
-        dev_images = [h.to(dev, non_blocking=True) for h in host_images]
-        torch.cuda.synchronize()
-
-        # ---- CUDA graphs: one per resident input buffer, plus one reading a staging buffer (e2e) ----
-        stream = torch.cuda.Stream(device=dev)
-        # two staging buffers: the host->device copy of step i + 1 runs on its own stream under step i
-        staging = [torch.empty_like(dev_images[0]) for _ in range(2)]
-        copy_stream = torch.cuda.Stream(device=dev)
-        h2d_done = [torch.cuda.Event() for _ in range(2)]
-        compute_done = [torch.cuda.Event() for _ in range(2)]
-        host_logits = torch.empty(B, 1000, dtype=torch.float32).pin_memory()
-        graphs, outs = [], []
-        with torch.cuda.stream(stream):
-            for _ in range(2):
-                model(dev_images[0])
-            stream.synchronize()
-            launches_before = _lib.LAUNCH_COUNT[0]
-            for src in dev_images + staging:
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=stream):
-                    out = model(src)
-                graphs.append(g)
-                outs.append(out)
-            launches_per_forward = (_lib.LAUNCH_COUNT[0] - launches_before) // len(graphs)
-
-        def barrier():
-            if world > 1:
-                dist.barrier()
-            torch.cuda.synchronize()
-
-        def step_resident(i: int) -> None:
-            graphs[i % n_bufs].replay()
-            if world > 1:
-                gather_logits(outs[i % n_bufs])
-
-        def step_e2e(i: int) -> None:
-            b = i % 2
-            with torch.cuda.stream(copy_stream):
-                copy_stream.wait_event(compute_done[b])  # the forward that last read this buffer
-                staging[b].copy_(host_images[i % n_bufs], non_blocking=True)
-                h2d_done[b].record(copy_stream)
-            stream.wait_event(h2d_done[b])
-            graphs[n_bufs + b].replay()
-            if world > 1:
-                gather_logits(outs[n_bufs + b])
-            host_logits.copy_(outs[n_bufs + b], non_blocking=True)
-            compute_done[b].record(stream)
-
-        def run_timed(step_fn) -> float:
-            with torch.cuda.stream(stream):
-                for i in range(args.warmup):
-                    step_fn(i)
-                copy_stream.synchronize()
-                barrier()
-                start = torch.cuda.Event(enable_timing=True)
-                end = torch.cuda.Event(enable_timing=True)
-                start.record(stream)
-                copy_stream.wait_event(start)  # no copy of a timed step starts before the timed region
-                for i in range(args.steps):
-                    step_fn(i)
-                end.record(stream)
-                barrier()
-                ms = torch.tensor([start.elapsed_time(end)], device=dev)
-            if world > 1:
-                dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-            return float(ms.item())
-
-        sampler = ClockSampler(local_rank)
-        if rank == 0:
-            sampler.start()
-        ms_resident = run_timed(step_resident)
-        clocks = sampler.stop() if rank == 0 else None
-        ms_e2e = run_timed(step_e2e)
-
-        # ---- roofline of the dominant kernel: eager pass with events around every LUT-GEMM launch ----
-        events = []
-        orig, orig_conv = ops.dimq_linear_wq, ops.dimq_conv2d_wq
-
-        def timed(fn):
-            def wrapper(*a, **kw):
-                s = torch.cuda.Event(enable_timing=True)
-                e = torch.cuda.Event(enable_timing=True)
-                s.record(torch.cuda.current_stream())
-                y = fn(*a, **kw)
-                e.record(torch.cuda.current_stream())
-                events.append((s, e))
-                return y
-            return wrapper
-
-        roof_steps = 3
-        from dimq_b200 import modules as _modules
-        _modules.ops.dimq_linear_wq = timed(orig)
-        _modules.ops.dimq_conv2d_wq = timed(orig_conv)
-        try:
-            with torch.cuda.stream(stream):
-                for i in range(roof_steps):
-                    # keep the GPU busy while the host queues the step, so that the event pairs
-                    # bracket kernel execution and not launch gaps
-                    torch.cuda._sleep(int(60e6))
-                    model(dev_images[i % n_bufs])
-                stream.synchronize()
-        finally:
-            _modules.ops.dimq_linear_wq = orig
-            _modules.ops.dimq_conv2d_wq = orig_conv
-        gemm_ms = sum(s.elapsed_time(e) for s, e in events)
-        gemm_launches = len(events)
+        # ---- weak scaling: the configuration's batch on every GPU (the headline and the secondary model) ----
+        for name in ([args.workload] if args.only else [args.workload, other]):
+            _, B, _ = WORKLOADS[name]
+            mb = ModelBench(name, B, dev, rank)
+            sampler = ClockSampler(local_rank)
+            if rank == 0:
+                sampler.start()
+            ms_res = mb.run_timed(mb.step_resident, args.steps, args.warmup, world)
+            clocks = sampler.stop() if rank == 0 else None
+            ms_e2e = mb.run_timed(mb.step_e2e, args.steps, args.warmup, world)
+            roof = mb.roofline()
+            cpu = cpu_baseline(mb.ckpt, name) if (world == 1 and rank == 0 and not args.no_cpu_baseline
+                                                  and name == args.workload) else None
+            results[name] = {"B": B, "ms_res": ms_res, "ms_e2e": ms_e2e, "clocks": clocks, "roofline": roof,
+                             "launches": mb.launches_per_forward, "cpu": cpu}
+            mb.release()
+            del mb
+        # ---- strong scaling: the configuration's batch split over the GPUs (BASELINE.json's wording) ----
+        strong = None
+        if world > 1 and not args.only:
+            strong = {}
+            for name in (args.workload, other):
+                _, B, _ = WORKLOADS[name]
+                lo, hi = shard_bounds(B, rank, world)
+                mb = ModelBench(name, hi - lo, dev, rank)
+                ms_res = mb.run_timed(mb.step_resident, args.steps, args.warmup, world)
+                ms_e2e = mb.run_timed(mb.step_e2e, args.steps, args.warmup, world)
+                mb.release()
+                del mb
+                par = parity_vs_one_gpu(name, B, dev, world, rank)
+                strong[name] = {"global_batch": B, "images_per_gpu": hi - lo,
+                                "value": B * args.steps / (ms_res / 1e3), "unit": "images/s",
+                                "ms_per_step": ms_res / args.steps,
+                                "e2e_value": B * args.steps / (ms_e2e / 1e3), "parity_vs_1gpu": par}
+        micro = small_m_micro(dev) if (rank == 0 and not args.only) else None
 
     if world > 1:
         dist.barrier()
@@ -391,34 +549,51 @@ def main() -> None:
             dist.destroy_process_group()
         return
 
-    images_total = world * B * args.steps
-    value = images_total / (ms_resident / 1e3)
-    e2e_value = images_total / (ms_e2e / 1e3)
-    peak, peak_kind = _peaks()
-    flops = flops_per_step * roof_steps
-    achieved = flops / (gemm_ms / 1e3) / 1e12
-    line = {
-        "metric": f"{args.workload}_dimq_images_per_s", "value": value, "unit": "images/s", "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_resident / args.steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "global_batch": world * B, "weights": weight_desc,
-                   "l2": f"{n_bufs} rotating image buffers and >126 MB of activations per step",
-                   "parallelism": f"dp{world} (batch-sharded replicas, all-gather of logits)"},
-        "e2e": {"value": e2e_value, "unit": "images/s", "ms_per_step": ms_e2e / args.steps,
-                "h2d_bytes_per_step": world * B * 3 * 224 * 224 * 2, "d2h_bytes_per_step": world * B * 1000 * 4},
-        "gpu_launches": launches_per_forward * args.steps,
-        "clocks": clocks,
-        "roofline": {"kernel": "linear_wq_tc_kernel (tcgen05 LUT GEMM / implicit-GEMM conv)", "bound": "tensor", "achieved": achieved,
-                     "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peak_kind,
-                     "launches_timed": gemm_launches, "avg_launch_ms": gemm_ms / max(gemm_launches, 1),
-                     "flops_per_step": flops / roof_steps,
-                     # DRAM bytes per launch: the ncu capture of the M = 8192 fc1 case (16.45 MB for 38.65 GFLOP,
-                     # profiles/linear_wq_tc_kernel_m8192_k768_n3072_w3.md) scaled by the flops of an average launch
-                     "traffic": NCU_DRAM_BYTES_PER_FLOP * flops / max(gemm_launches, 1),
-                     "traffic_source": "ncu capture of a smaller launch, scaled by flops"},
-    }
-    if world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline(ckpt, args.workload)
+    def model_line(name: str) -> dict:
+        r = results[name]
+        images_total = world * r["B"] * args.steps
+        return {"metric": f"{name}_dimq_images_per_s", "value": images_total / (r["ms_res"] / 1e3), "unit": "images/s",
+                "ms_per_step": r["ms_res"] / args.steps,
+                "config": {"workload": WORKLOADS[name][0], "global_batch": world * r["B"], "weights": WORKLOADS[name][2],
+                           "l2": "4 rotating image buffers and >126 MB of activations per step",
+                           "parallelism": f"dp{world} (batch-sharded replicas, all-gather of logits on a side stream)"},
+                "e2e": {"value": images_total / (r["ms_e2e"] / 1e3), "unit": "images/s",
+                        "ms_per_step": r["ms_e2e"] / args.steps,
+                        "h2d_bytes_per_step": world * r["B"] * 3 * 224 * 224 * 2,
+                        "d2h_bytes_per_step": world * r["B"] * 1000 * 4},
+                "gpu_launches": r["launches"] * args.steps, "clocks": r["clocks"], "roofline": r["roofline"]}
+
+    main_line = model_line(args.workload)
+    line = {"metric": main_line["metric"], "value": main_line["value"], "unit": "images/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": main_line["ms_per_step"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": main_line["config"], "e2e": main_line["e2e"], "gpu_launches": main_line["gpu_launches"],
+            "clocks": main_line["clocks"], "roofline": main_line["roofline"]}
+    if args.workload == "vit_b16":
+        # DRAM bytes of one launch of the dominant kernel, from an ncu capture at the real launch shape
+        # (profiles/lut_dense_tc_kernel_m25216_k768_n3072_w3.md): fc1, 43.5 MB read + 102.5 MB written
+        line["roofline"]["traffic"] = 146.0e6
+        line["roofline"]["traffic_source"] = ("ncu capture of the fc1 launch (M=25216, K=768, N=3072), one of the four "
+                                              "shapes of the step; algorithmic bytes of that launch 198.3 MB")
+    else:
+        line["roofline"]["traffic"] = None
+    if results[args.workload]["cpu"] is not None:
+        line["cpu_baseline"] = results[args.workload]["cpu"]
+    if other in results:
+        sec = model_line(other)
+        line["secondary"] = {k: sec[k] for k in ("metric", "value", "unit", "ms_per_step", "config", "e2e",
+                                                  "gpu_launches", "roofline")}
+    if strong is not None:
+        for name, s in strong.items():
+            # one GPU's time for the whole batch = the weak pass's step (the same batch per GPU)
+            one_gpu_ms = results[name]["ms_res"] / args.steps
+            s["efficiency_vs_1gpu"] = one_gpu_ms / world / s["ms_per_step"]
+            s["efficiency_basis"] = "ms per step of the weak pass (whole batch on one GPU) / N / ms per step here"
+            s["note"] = ("fixed global batch split over the GPUs; per-GPU tiles shrink, so tile quantisation and "
+                         "per-launch fixed cost bound it, not NCCL")
+        line["strong"] = strong
+    if micro is not None:
+        line["micro"] = micro
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
