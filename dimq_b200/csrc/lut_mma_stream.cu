@@ -90,6 +90,8 @@ struct MsParams {
   uint32_t x_low;  // shared address of row 0 when rows_low > 0
   uint32_t x_high; // shared address of row rows_low
   uint32_t zero;   // shared address of 256 zero bytes (the activations of MMA columns beyond M)
+  uint32_t scale;  // shared address of 32 floats: per-row factor of the converting mode (else unused)
+  int cvt;         // 1: x is bf16 in global memory and is converted to fp16 while it is staged
   int pf;          // ring slots per warp
   int bw;          // units (k chunks) per TMA box and ring slot: 1, 2 or 4
   uint32_t part;   // shared address of the partial sums: [2][warp][16 rows][MR]
@@ -141,6 +143,20 @@ __device__ __forceinline__ void static_for(F&& f) {
     f(std::integral_constant<int, I>{});
     static_for<I + 1, N>(f);
   }
+}
+
+// One lane of a converged warp: TMA copies are issued under this predicate from warp-uniform control
+// flow (issued from a `lane == 0` branch the same instruction costs several times more issue time).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred = 0;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred px;\n\t"
+      "elect.sync _|px, 0xFFFFFFFF;\n\t"
+      "@px mov.s32 %0, 1;\n\t"
+      "}\n"
+      : "+r"(pred));
+  return pred != 0;
 }
 
 constexpr uint32_t kPollLimit = 1u << 15;  // bounded wait: polls of up to 20 us each, then give up
@@ -273,10 +289,13 @@ linear_wq_mma_stream_kernel(const __grid_constant__ CUtensorMap wmap, const MsPa
   // issue the copy of the next box of the sequence: p.bw consecutive chunks of the 16 rows (lane 0
   // only; the slot must be free)
   const uint32_t slot_bytes = p.bw * C::kUnitBytes;
-  auto issue_unit = [&]() {
+  auto issue_unit = [&]() {   // whole warp: every lane keeps the cursor, one elected lane issues
     const uint32_t bar = bars_w + ld_slot * 8;
-    mbar_expect_tx(bar, slot_bytes);
-    tma_load_unit(ring_w + ld_slot * slot_bytes, &wmap, bar, (c0 + ld_j) * kChunkBytes, ld_row0);
+    if (elect_one()) {
+      mbar_expect_tx(bar, slot_bytes);
+      tma_load_unit(ring_w + ld_slot * slot_bytes, &wmap, bar, (c0 + ld_j) * kChunkBytes, ld_row0);
+    }
+    __syncwarp();
     ld_seq += p.bw;
     if (++ld_slot == p.pf) ld_slot = 0;
     ld_j += p.bw;
@@ -285,34 +304,132 @@ linear_wq_mma_stream_kernel(const __grid_constant__ CUtensorMap wmap, const MsPa
       ld_row0 += p.G * 16;
     }
   };
+  // The kernel that follows in the stream may start its own prologue now (programmatic dependent
+  // launch): everything up to the activation staging below reads only weights and codebooks.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (nch > 0) {
     if (lane == 0) {
       for (int q = 0; q < p.pf; ++q) mbar_init(bars_w + q * 8, 1);
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-      // the first copies fly while the activations and the table are being set up
-      for (int q = 0; q < p.pf && ld_seq < total; ++q) issue_unit();  // ld_seq counts units
     }
     __syncwarp();
+    // the first copies fly while the activations and the table are being set up
+    for (int q = 0; q < p.pf && ld_seq < total; ++q) issue_unit();  // ld_seq counts units
   }
   if (tid == 0) *abort_flag = 0u;
 
-  // ---- one-time staging: activations (asynchronous copies), a chunk of zeros ----
-  {
+  float* row_scale = reinterpret_cast<float*>(abs0 + p.scale);
+  // ---- one-time staging of the activations (after the table, below): asynchronous copies, or, in the
+  // converting mode, bf16 -> fp16 on the way (the codebook is fp16 / fp32, so the MMAs run in fp16) ----
+  auto stage_activations = [&]() {
     // 16-byte group v = k / 8 of a row is [chunk | t (2 bits) | s / 2 (2 bits)]; it is stored at
     // [chunk | s / 2 | t], so that a pair of MMA steps finds the four lanes of a quad in adjacent slots
     const int vec_per_row = static_cast<int>(p.K >> 3);  // 8 elements = 16 bytes
     const uint4* xg = static_cast<const uint4*>(p.x);
-    for (int m = 0; m < p.M; ++m) {
-      const uint32_t row = x_row_addr(m);
-      const uint4* src = xg + static_cast<int64_t>(m) * vec_per_row;
-      for (int v = tid; v < vec_per_row; v += kThreads) {
-        const int dv = (v & ~15) | ((v & 3) << 2) | ((v >> 2) & 3);
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(row + dv * 16), "l"(src + v) : "memory");
+    if (!p.cvt) {
+      for (int m = 0; m < p.M; ++m) {
+        const uint32_t row = x_row_addr(m);
+        const uint4* src = xg + static_cast<int64_t>(m) * vec_per_row;
+        for (int v = tid; v < vec_per_row; v += kThreads) {
+          const int dv = (v & ~15) | ((v & 3) << 2) | ((v >> 2) & 3);
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(row + dv * 16), "l"(src + v) : "memory");
+        }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      return;
+    }
+    // Converting mode.  bf16 -> fp16 is exact for 6.1e-5 <= |x| <= 65504.  Pass 1 converts as is and
+    // notes per row whether a finite value exceeds 2^15, whether any reaches 2^-10 and whether any is
+    // non-zero.  A row that is too large, or non-zero but tiny throughout, is staged again scaled by a
+    // power of two that brings its largest finite magnitude to [2^14, 2^15) (exact), and the write-back
+    // multiplies its sums by the inverse: elements more than 2^29 below the row maximum lose bits, far
+    // under the rounding of the fp32 accumulation.  All rows' vectors form one index space, four loads in
+    // flight per thread.
+    uint32_t* flags = reinterpret_cast<uint32_t*>(row_scale);   // per row: bit 0 too large, bit 1 some >= 2^-10, bit 2 non-zero
+    if (tid < 32) flags[tid] = 0u;
+    __syncthreads();
+    const int total_vec = p.M * vec_per_row;
+    auto convert_store = [&](int i, const uint4& q, float f, uint32_t& note) {
+      const int m = i / vec_per_row, v = i - m * vec_per_row;
+      const int dv = (v & ~15) | ((v & 3) << 2) | ((v >> 2) & 3);
+      const uint32_t in[4] = {q.x, q.y, q.z, q.w};
+      uint32_t out[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 xy = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&in[j]));
+        xy.x *= f; xy.y *= f;
+        const float a = fmaxf(fabsf(xy.x) < 3.0e38f ? fabsf(xy.x) : 0.0f, fabsf(xy.y) < 3.0e38f ? fabsf(xy.y) : 0.0f);
+        note |= (a > 32768.0f ? 1u : 0u) | (a >= 0.0009765625f ? 2u : 0u) | (a > 0.0f ? 4u : 0u);
+        const __half2 h = __float22half2_rn(xy);
+        out[j] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+      *reinterpret_cast<uint4*>(abs0 + x_row_addr(m) + dv * 16) = make_uint4(out[0], out[1], out[2], out[3]);
+    };
+    for (int i0 = tid; i0 < total_vec; i0 += 4 * kThreads) {
+      uint4 q[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i0 + u * kThreads < total_vec) q[u] = __ldg(xg + i0 + u * kThreads);   // rows are contiguous: [M][K]
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * kThreads;
+        if (i < total_vec) {
+          uint32_t note = 0u;
+          convert_store(i, q[u], 1.0f, note);
+          const int m = i / vec_per_row;
+          if ((flags[m] | note) != flags[m]) atomicOr(flags + m, note);
+        }
       }
     }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-    if (tid < 16) reinterpret_cast<uint4*>(abs0 + p.zero)[tid] = make_uint4(0u, 0u, 0u, 0u);
-  }
+    __syncthreads();
+    bool redo = false;
+    if (tid < 32 && tid < p.M) redo = (flags[tid] & 1u) != 0u || (flags[tid] & 6u) == 4u;
+    if (__syncthreads_or(redo ? 1 : 0)) {
+      // rare path: the rows that need it get their largest finite magnitude, then a power-of-two factor
+      // scratch of this path: the start of the partial-sum buffers, not in use before the main loop
+      uint32_t* row_max = reinterpret_cast<uint32_t*>(part);
+      float* row_factor = part + 32;
+      if (tid < 32) row_max[tid] = 0u;
+      __syncthreads();
+      for (int i = tid; i < total_vec; i += kThreads) {
+        const int m = i / vec_per_row;
+        if ((flags[m] & 1u) == 0u && (flags[m] & 6u) != 4u) continue;
+        const uint4 q = __ldg(xg + i);
+        const uint32_t in[4] = {q.x, q.y, q.z, q.w};
+        float a = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 xy = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&in[j]));
+          if (fabsf(xy.x) < 3.0e38f) a = fmaxf(a, fabsf(xy.x));
+          if (fabsf(xy.y) < 3.0e38f) a = fmaxf(a, fabsf(xy.y));
+        }
+        if (a > 0.0f) atomicMax(row_max + m, __float_as_uint(a));   // non-negative floats order like their bits
+      }
+      __syncthreads();
+      if (tid < 32) {
+        float f = 1.0f;
+        const float mx = __uint_as_float(row_max[tid]);
+        if (mx > 0.0f) {
+          int e;
+          frexpf(mx, &e);               // mx = frac * 2^e, frac in [0.5, 1)
+          f = ldexpf(1.0f, 15 - e);     // mx * f in [2^14, 2^15)
+        }
+        row_factor[tid] = f;
+      }
+      __syncthreads();
+      for (int i = tid; i < total_vec; i += kThreads) {
+        const int m = i / vec_per_row;
+        if (row_factor[m] == 1.0f) continue;
+        uint32_t note = 0u;
+        convert_store(i, __ldg(xg + i), row_factor[m], note);
+      }
+      __syncthreads();
+      if (tid < 32) row_scale[tid] = 1.0f / row_factor[tid];   // what the row's sums are multiplied by
+    } else if (tid < 32) {
+      row_scale[tid] = 1.0f;
+    }
+  };
+  if (tid < 16) reinterpret_cast<uint4*>(abs0 + p.zero)[tid] = make_uint4(0u, 0u, 0u, 0u);
 
   // pair table of one codebook group, one copy per lane: word (entry * 32 + lane)
   auto build_table = [&](int64_t group, bool preloaded) {
@@ -347,6 +464,9 @@ linear_wq_mma_stream_kernel(const __grid_constant__ CUtensorMap wmap, const MsPa
   };
   int64_t cur_group = first_group;
   build_table(cur_group, true);
+  // the activations may be the output of the kernel before this one in the stream: wait for it
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  stage_activations();
   asm volatile("cp.async.wait_all;" ::: "memory");
   __syncthreads();
 
@@ -387,6 +507,7 @@ linear_wq_mma_stream_kernel(const __grid_constant__ CUtensorMap wmap, const MsPa
       const float* src = base + static_cast<size_t>(sl) * p.wpr * (16 * MR) + r * MR + m;
       float v = 0.0f;
       for (int wi = 0; wi < p.wpr; ++wi) v += src[wi * (16 * MR)];
+      if (p.cvt && m < p.M) v *= row_scale[m];
       const int64_t n = (static_cast<int64_t>(it) * p.G + sl) * 16 + r;
       if (m < p.M && n < p.N) {
         const float vb = v + (p.bias != nullptr ? load_as_float(p.bias, p.bias_dtype, n) : 0.0f);
@@ -452,6 +573,9 @@ linear_wq_mma_stream_kernel(const __grid_constant__ CUtensorMap wmap, const MsPa
           seq_live = false;
         }
       }
+      // the lanes poll the same barrier but may read the abort flag at different moments: agree
+      box_ok = __all_sync(0xFFFFFFFFu, box_ok);
+      if (!box_ok) seq_live = false;
     }
     const uint32_t src = ring_w + pr_slot * slot_bytes + g * row_pitch + sub * kChunkBytes + t * (4 * BITS);
 #pragma unroll
@@ -471,7 +595,7 @@ linear_wq_mma_stream_kernel(const __grid_constant__ CUtensorMap wmap, const MsPa
     if (++sub == p.bw) {
       sub = 0;
       __syncwarp();  // every lane has its words of the last unit: the slot may be overwritten
-      if (lane == 0 && box_ok && ld_seq < total) issue_unit();
+      if (box_ok && ld_seq < total) issue_unit();
       if (++pr_slot == p.pf) { pr_slot = 0; pr_phase ^= 1u; }
     }
     return box_ok;
@@ -546,7 +670,7 @@ linear_wq_mma_stream_kernel(const __grid_constant__ CUtensorMap wmap, const MsPa
 
 struct Plan {
   int G, wpr, cpw, chunks, total_it, ipc, ctas, nb, rows_low, pf, bw;
-  uint32_t x_low, x_high, ring, bars, part, zero;
+  uint32_t x_low, x_high, ring, bars, part, zero, scale;
   size_t smem;
 };
 
@@ -584,7 +708,8 @@ bool make_plan(const dimq_wq_weight* w, int64_t M, int64_t N, int64_t K, Plan* o
   const size_t low = sizeof(float) * 16;  // codewords
   bp.bars = static_cast<uint32_t>(kLowStart + low);
   bp.zero = static_cast<uint32_t>((bp.bars + kWarps * kMaxPf * 8 + 16 + 127) & ~size_t(127));  // after the abort flag
-  const size_t low_end = bp.zero + 256;
+  bp.scale = bp.zero + 256;                    // 32 per-row factors of the converting mode
+  const size_t low_end = bp.scale + 128;
   if (low_end > C::kTableAddr) return false;
   // row stride 2 K + 64 bytes: the eight lanes of a quarter-warp (two rows x four 16-byte slots) cover
   // 128 consecutive bytes modulo the bank width
@@ -631,7 +756,21 @@ int launch_one(const CUtensorMap& wmap, MsParams& p, const Plan& plan, cudaStrea
   e = cudaGetSymbolAddress(&status, g_ms_status);
   if (e != cudaSuccess) return static_cast<int>(e);
   p.status = static_cast<uint32_t*>(status);
-  kern<<<plan.ctas, kThreads, plan.smem, st>>>(wmap, p);
+  // programmatic dependent launch: this kernel's prologue (barriers, first index copies, table) may
+  // overlap the tail of the kernel before it in the stream; it waits (griddepcontrol.wait) before it
+  // reads the activations or writes anything
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(plan.ctas));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = plan.smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, kern, wmap, p);
+  if (e != cudaSuccess) return static_cast<int>(e);
   return launch_status();
 }
 
@@ -646,11 +785,11 @@ int launch_bits(const CUtensorMap& wmap, MsParams& p, const Plan& plan, bool f16
 
 }  // namespace
 
-// 16-bit activations whose format the codewords can take without a second term (fp16 activations, or
-// bf16 activations with a bf16 codebook), M <= 32, K a multiple of 128, 2-, 3- or 4-bit indices.
+// 16-bit activations, M <= 32, K a multiple of 128, 2-, 3- or 4-bit indices.  fp16 activations run
+// fp16 MMAs, bf16 activations with a bf16 codebook bf16 MMAs; bf16 activations with an fp16 / fp32
+// codebook (what the reference's packed export stores) are converted to fp16 while they are staged.
 bool mma_stream_supported(const void* x, int x_dtype, const dimq_wq_weight* w, int64_t M, int64_t N, int64_t K) {
   if (x_dtype != DIMQ_F16 && x_dtype != DIMQ_BF16) return false;
-  if (x_dtype == DIMQ_BF16 && w->cb_dtype != DIMQ_BF16) return false;
   if (M < 1 || M > 32 || N < 1 || K < kChunkK || K % kChunkK != 0) return false;
   if (w->bits != 2 && w->bits != 3 && w->bits != 4) return false;
   if (w->groups > 1 && w->group_rows % 16 != 0) return false;
@@ -674,6 +813,8 @@ int launch_linear_wq_mma_stream(const void* x, int x_dtype, const dimq_wq_weight
   p.G = plan.G; p.wpr = plan.wpr; p.cpw = plan.cpw; p.chunks = plan.chunks; p.total_it = plan.total_it;
   p.ipc = plan.ipc; p.xs = static_cast<int>(K) + 32; p.rows_low = plan.rows_low; p.x_low = plan.x_low; p.x_high = plan.x_high;
   p.pf = plan.pf; p.bw = plan.bw; p.ring = plan.ring; p.bars = plan.bars; p.part = plan.part; p.zero = plan.zero;
+  p.scale = plan.scale;
+  p.cvt = (x_dtype == DIMQ_BF16 && w->cb_dtype != DIMQ_BF16) ? 1 : 0;
   // the packed index matrix as [N rows][K * bits / 8 bytes]; one box = one unit (16 rows x 128 k)
   CUtensorMap wmap;
   const uint64_t row_bytes = static_cast<uint64_t>(K) * w->bits / 8;
@@ -682,7 +823,7 @@ int launch_linear_wq_mma_stream(const void* x, int x_dtype, const dimq_wq_weight
   const uint32_t box[2] = {static_cast<uint32_t>(plan.bw * kChunkK * w->bits / 8), 16u};
   const int rc = encode_plain_tensor_map(&wmap, 1, 2, w->packed, dims, strides, box);
   if (rc != DIMQ_OK) return rc;
-  const bool f16 = x_dtype == DIMQ_F16;
+  const bool f16 = x_dtype == DIMQ_F16 || p.cvt != 0;
   switch (w->bits) {
     case 2: return launch_bits<2>(wmap, p, plan, f16, st);
     case 3: return launch_bits<3>(wmap, p, plan, f16, st);

@@ -262,11 +262,13 @@ def test_linear_wq_stream_small_m(ops, bits, m):
 
 # ---- small-M index-streaming kernel for 16-bit activations (pair tables + warp MMA) ---------
 
+# (activation dtype, codebook rounding, codebook dtype); the last one is the reference export's default
+# (fp16 codebook) under bf16 activations: the kernel converts the activations to fp16 while staging them
 MS_MODES = [(torch.bfloat16, "bf16", torch.bfloat16), (torch.float16, np.float16, torch.float16),
-            (torch.float16, np.float32, torch.float32)]
+            (torch.float16, np.float32, torch.float32), (torch.bfloat16, np.float16, torch.float16)]
 
 
-@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("mode", [0, 1, 2, 3])
 @pytest.mark.parametrize("bits", [2, 3, 4])
 @pytest.mark.parametrize("m,k,n,grp", [(1, 128, 16, None), (3, 768, 100, None), (8, 1024, 520, 128), (9, 1024, 4096, None),
                                        (16, 4096, 1024, None), (17, 256, 33, 16), (32, 2048, 300, 32),
@@ -326,11 +328,35 @@ def test_linear_wq_mma_stream_rejects_what_it_cannot_take(ops):
     pw, cb = _cuda(case["packed"]), _cuda(case["codebooks"])
     with pytest.raises(RuntimeError):  # fp32 activations
         ops.dimq_linear_wq(x, pw, cb, None, 64, 256, bits=4, algo="mma_stream")
-    with pytest.raises(RuntimeError):  # bf16 activations with an fp32 codebook would need a second term
-        ops.dimq_linear_wq(x.to(torch.bfloat16), pw, cb, None, 64, 256, bits=4, algo="mma_stream")
     with pytest.raises(RuntimeError):  # more than 32 rows
         ops.dimq_linear_wq(torch.zeros(33, 256, device="cuda", dtype=torch.float16), pw, cb, None, 64, 256, bits=4,
                            algo="mma_stream")
+
+
+def test_linear_wq_mma_stream_converts_bf16_activations_of_any_magnitude(ops):
+    """bf16 activations with an fp16 codebook run as fp16 MMAs.  Rows whose largest magnitude lies
+    outside the exactly convertible range are scaled by a power of two on the way in and back on the
+    way out, so huge, tiny, zero and mixed rows all keep the weight-only tolerance (relative here: the
+    rows span 40 orders of magnitude)."""
+    m, k, n = 7, 512, 96
+    case = make_weight(n, k, 4, seed=5)                      # fp16-rounded codebook
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    x[1] *= 1.0e6            # beyond fp16's 65504
+    x[2] *= 1.0e-9           # below fp16's subnormals
+    x[3] = 0.0               # all zero
+    x[4, :5] *= 3.0e37       # a few huge values among ordinary ones
+    x[5] *= 1.0e-20
+    x[6] *= 3.0e30
+    x = bf16_round(x)
+    want = o.linear_wq(x, case["packed"], case["codebooks"], 4, n, k).astype(np.float64)
+    got = ops.dimq_linear_wq(_cuda(x, torch.bfloat16), _cuda(case["packed"]), _cuda(case["codebooks"], torch.float16),
+                             None, n, k, bits=4, algo="mma_stream").cpu().numpy().astype(np.float64)
+    assert ops.last_device_status() == 0 and np.isfinite(got).all()
+    for row in range(m):
+        scale = np.linalg.norm(want[row])
+        err = np.linalg.norm(got[row] - want[row])
+        assert err <= 1e-3 * scale + (0.0 if scale > 0 else 1e-30), (row, err, scale)
 
 
 TC_SHAPES = [(192, 64, 128), (200, 128, 130), (577, 768, 384), (64, 1024, 256), (16, 256, 128)]
@@ -451,6 +477,17 @@ def test_linear_wq_m_sweep_auto_dispatch(ops, bits, k, n, m):
     got = ops.dimq_linear_wq(_cuda(x, torch.bfloat16), case["packed_cuda"], case["cb_cuda"], None, n, k, bits=bits)
     assert ops.last_device_status() == 0
     _assert_close(got, want, f"sweep bits={bits} m={m} {k}->{n}")
+    if m <= 32:
+        # the index-streaming kernel is what the automatic choice runs here (fp16 codebook, bf16 activations:
+        # the reference export's default): the two results are the same bits
+        try:
+            forced = ops.dimq_linear_wq(_cuda(x, torch.bfloat16), case["packed_cuda"], case["cb_cuda"], None, n, k,
+                                        bits=bits, algo="mma_stream")
+        except RuntimeError as err:
+            # 16 rows of 4096 activations do not fit beside the 64 KB table of the 2-bit form
+            assert (m, k, bits) == (16, 4096, 2) and "does not support" in str(err), err
+        else:
+            assert torch.equal(got, forced)
 
 
 _SWEEP_CACHE: dict = {}
