@@ -18,6 +18,7 @@ from .export import (
     pack_u4_indices,
     unpack_u4_indices,
 )
+from .calibration import ActivationRangeCollector, apply_activation_qparams, calibrate_activation_qparams
 from .modules import DIMQConv2d, DIMQLinear, make_packed_layer, replace_modules_with_packed_dimq
 from .ops import (
     build_product_table,
@@ -36,7 +37,8 @@ from .ops import (
 )
 
 __all__ = [
-    "DIMQConv2d", "DIMQLinear", "activation_qparams_from_minmax", "assign_weight_indices", "build_product_table",
+    "ActivationRangeCollector", "DIMQConv2d", "DIMQLinear", "activation_qparams_from_minmax", "apply_activation_qparams",
+    "calibrate_activation_qparams", "assign_weight_indices", "build_product_table",
     "default_activation_qparams", "dimq_conv2d_lut", "dimq_conv2d_wq", "dimq_linear_lut", "dimq_linear_wq",
     "export_compact_checkpoint", "export_packed_dimq_checkpoint", "hard_quantize", "hard_quantize_weight",
     "infer_module_hparams", "is_available", "load_compact_checkpoint", "make_packed_layer", "pack_bits", "pack_u4",

@@ -34,7 +34,7 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads)
 centre_quantize_kernel(const T* __restrict__ x, __nv_bfloat16* __restrict__ out, int64_t n, float scale, int zp,
                        int vec_ok, const void* __restrict__ codebook, int cb_dtype, float* __restrict__ scaled_cb) {
-  if (blockIdx.x == 0 && threadIdx.x < 16)
+  if (scaled_cb != nullptr && blockIdx.x == 0 && threadIdx.x < 16)
     scaled_cb[threadIdx.x] = __fmul_rn(scale, load_as_float(codebook, cb_dtype, threadIdx.x));
   const int64_t base = (static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x) * 8;
   if (base >= n) return;
@@ -91,6 +91,17 @@ int check_a4_args(int x_dtype, int cb_dtype, const void* bias, int bias_dtype, f
 }  // namespace dimq
 
 using namespace dimq;
+
+extern "C" int dimq_centre_quantize_u4(const void* x, int x_dtype, int64_t numel, float act_scale, int act_zp,
+                                       void* codes_bf16, void* stream) {
+  if (numel < 0) return DIMQ_ERR_BAD_SIZE;
+  if (!valid_dtype(x_dtype)) return DIMQ_ERR_BAD_DTYPE;
+  if (!(act_scale > 0.0f) || act_zp < 0 || act_zp > 15) return DIMQ_ERR_BAD_QPARAMS;
+  if (numel == 0) return DIMQ_OK;
+  if (x == nullptr || codes_bf16 == nullptr) return DIMQ_ERR_NULL_POINTER;
+  return launch_centre_quantize(x, x_dtype, numel, act_scale, act_zp, nullptr, DIMQ_F32, nullptr,
+                                static_cast<__nv_bfloat16*>(codes_bf16), static_cast<cudaStream_t>(stream));
+}
 
 extern "C" int dimq_a4_workspace_bytes(int64_t x_numel, int64_t conv_weight_numel, int64_t* bytes) {
   if (bytes == nullptr) return DIMQ_ERR_NULL_POINTER;

@@ -187,7 +187,7 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads)
 hard_quantize_kernel(const T* __restrict__ w, int64_t n, int64_t cols, const float* __restrict__ codebooks,
                      int entries, int64_t groups, int64_t group_rows, uint8_t* __restrict__ idx_out,
-                     uint8_t* __restrict__ packed, int bits, int use_smem, int vec_ok) {
+                     uint8_t* __restrict__ packed, int bits, int use_smem, int vec_ok, T* __restrict__ fake_out) {
   extern __shared__ float cb_s[];
   // sorted_s[g] != 0: codebook g is finite and non-decreasing, so the nearest codeword of a finite weight
   // is found by bisection (see below) instead of K distance evaluations
@@ -326,6 +326,20 @@ hard_quantize_kernel(const T* __restrict__ w, int64_t n, int64_t cols, const flo
       for (int i = 0; i < 8 && base + i < n; ++i) idx_out[base + i] = static_cast<uint8_t>(r[i]);
     }
   }
+  if (fake_out != nullptr) {
+    // straight-through fake quantisation, value of  w + (c[idx].to(w.dtype) - w)  with every operation
+    // rounded to the weight's type, as PyTorch evaluates quant/dimq_wrapper.py:72-75
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (base + i < n) {
+        const int64_t g = ((base + i) / cols) / group_rows;
+        const float* cb = use_smem ? cb_s + g * entries : codebooks + g * entries;
+        const float c = to_float<T>(from_float<T>(cb[r[i]]));
+        const float diff = to_float<T>(from_float<T>(__fsub_rn(c, f[i])));
+        fake_out[base + i] = from_float<T>(__fadd_rn(f[i], diff));
+      }
+    }
+  }
   if (packed != nullptr) {
     // 8 indices -> `bits` bytes at byte offset t*bits of the flattened stream
     const uint32_t mask = (1u << bits) - 1u;
@@ -435,9 +449,9 @@ extern "C" int dimq_build_product_table(const void* codebook, int cb_dtype, int6
   return launch_status();
 }
 
-extern "C" int dimq_hard_quantize(const void* w, int w_dtype, int64_t rows, int64_t cols, const float* codebooks,
-                                  int entries, int64_t group_rows, uint8_t* indices, uint8_t* packed, int bits,
-                                  void* stream) {
+static int hard_quantize_launch(const void* w, int w_dtype, int64_t rows, int64_t cols, const float* codebooks,
+                                int entries, int64_t group_rows, uint8_t* indices, uint8_t* packed, int bits,
+                                void* fake_out, void* stream) {
   if (rows < 0 || cols < 0 || group_rows <= 0) return DIMQ_ERR_BAD_SIZE;
   if (entries <= 0 || entries > 256) return DIMQ_ERR_BAD_SIZE;
   if (!valid_dtype(w_dtype)) return DIMQ_ERR_BAD_DTYPE;
@@ -448,7 +462,7 @@ extern "C" int dimq_hard_quantize(const void* w, int w_dtype, int64_t rows, int6
   const int64_t n = rows * cols;
   if (n == 0) return DIMQ_OK;
   if (w == nullptr || codebooks == nullptr) return DIMQ_ERR_NULL_POINTER;
-  if (indices == nullptr && packed == nullptr) return DIMQ_ERR_NULL_POINTER;
+  if (indices == nullptr && packed == nullptr && fake_out == nullptr) return DIMQ_ERR_NULL_POINTER;
   const int64_t groups = (rows + group_rows - 1) / group_rows;
   const int use_smem = groups * entries <= kHqSmemEntries;
   const size_t smem = use_smem ? sizeof(float) * static_cast<size_t>(groups * entries) + static_cast<size_t>(groups) : 0;
@@ -459,14 +473,28 @@ extern "C" int dimq_hard_quantize(const void* w, int w_dtype, int64_t rows, int6
   if (w_dtype == DIMQ_F32)
     hard_quantize_kernel<float><<<blocks, kThreads, smem, st>>>(static_cast<const float*>(w), n, cols, codebooks,
                                                                 entries, groups, group_rows, indices, packed, pbits,
-                                                                use_smem, vec_ok);
+                                                                use_smem, vec_ok, static_cast<float*>(fake_out));
   else if (w_dtype == DIMQ_F16)
     hard_quantize_kernel<__half><<<blocks, kThreads, smem, st>>>(static_cast<const __half*>(w), n, cols, codebooks,
                                                                  entries, groups, group_rows, indices, packed, pbits,
-                                                                 use_smem, vec_ok);
+                                                                 use_smem, vec_ok, static_cast<__half*>(fake_out));
   else
     hard_quantize_kernel<__nv_bfloat16><<<blocks, kThreads, smem, st>>>(
         static_cast<const __nv_bfloat16*>(w), n, cols, codebooks, entries, groups, group_rows, indices, packed,
-        pbits, use_smem, vec_ok);
+        pbits, use_smem, vec_ok, static_cast<__nv_bfloat16*>(fake_out));
   return launch_status();
+}
+
+extern "C" int dimq_hard_quantize(const void* w, int w_dtype, int64_t rows, int64_t cols, const float* codebooks,
+                                  int entries, int64_t group_rows, uint8_t* indices, uint8_t* packed, int bits,
+                                  void* stream) {
+  if (indices == nullptr && packed == nullptr && rows * cols != 0) return DIMQ_ERR_NULL_POINTER;
+  return hard_quantize_launch(w, w_dtype, rows, cols, codebooks, entries, group_rows, indices, packed, bits, nullptr,
+                              stream);
+}
+
+extern "C" int dimq_fake_quantize_ste(const void* w, int w_dtype, int64_t rows, int64_t cols, const float* codebooks,
+                                      int entries, int64_t group_rows, void* out, uint8_t* indices, void* stream) {
+  if (out == nullptr && rows * cols != 0) return DIMQ_ERR_NULL_POINTER;
+  return hard_quantize_launch(w, w_dtype, rows, cols, codebooks, entries, group_rows, indices, nullptr, 8, out, stream);
 }

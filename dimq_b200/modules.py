@@ -48,6 +48,17 @@ class _PackedBase(nn.Module):
             raise ValueError("the W4A4 mode needs 4-bit indices and one 16-entry codebook; "
                              "pass act_scale=None for weight-only layers")
 
+    def _scaled_codebook(self) -> torch.Tensor:
+        """``act_scale * codebook`` in fp32 (the weight operand of the tensor-core W4A4 form), built once
+        and rebuilt when the codebook buffer or the scale changes."""
+        cb = self.codebook
+        key = (cb.data_ptr(), cb._version, cb.device, self.act_scale)
+        if getattr(self, "_scaled_cb_key", None) != key:
+            self._scaled_cb = cb.detach().float().reshape(-1) * torch.tensor(self.act_scale, dtype=torch.float32,
+                                                                               device=cb.device)
+            self._scaled_cb_key = key
+        return self._scaled_cb
+
     def _check_input(self, x: torch.Tensor) -> None:
         if not self.use_cuda_kernel:
             raise RuntimeError("dimq_b200 has no Python fallback path (use_cuda_kernel=False is not supported)")
@@ -74,8 +85,17 @@ class DIMQLinear(_PackedBase):
             return ops.dimq_linear_wq(x, self.packed_weight, self.codebook, self.bias, self.out_features,
                                       self.in_features, bits=self.bits, group_rows=self.group_rows,
                                       out_dtype=self.out_dtype, epilogue=self.epilogue, residual=residual)
-        if residual is not None:
-            raise RuntimeError("a fused residual needs the weight-only mode")
+        rows = x.numel() // self.in_features
+        if rows >= ops.A4_TC_MIN_ROWS and self.in_features % 64 == 0:
+            # many rows: centred activation codes (exact in bf16) times the scaled codebook through the
+            # weight-only tensor-core path; per-layer state is cached, nothing is re-derived per call
+            codes = ops.centre_quantize_u4(x, self.act_scale, self.act_zero_point)
+            return ops.dimq_linear_wq(codes, self.packed_weight, self._scaled_codebook(), self.bias,
+                                      self.out_features, self.in_features, bits=4, out_dtype=self.out_dtype,
+                                      epilogue=self.epilogue, residual=residual)
+        if residual is not None or self.epilogue is not None:
+            raise RuntimeError("a fused epilogue or residual needs the weight-only mode or at least "
+                               f"{ops.A4_TC_MIN_ROWS} activation rows")
         return ops.dimq_linear_lut(x, self.packed_weight, self.codebook, self.act_scale, self.act_zero_point,
                                    self.bias, self.out_features, self.in_features)
 
@@ -127,8 +147,23 @@ class DIMQConv2d(_PackedBase):
                                       self.stride, self.padding, self.dilation, self.groups, bits=self.bits,
                                       group_rows=self.group_rows, out_dtype=self.out_dtype, epilogue=self.epilogue,
                                       residual=residual, packed_khwc=self._prepacked())
-        if residual is not None:
-            raise RuntimeError("a fused residual needs the weight-only mode")
+        khwc = self._prepacked()
+        channels_last = x.dim() == 4 and x.is_contiguous(memory_format=torch.channels_last) and not x.is_contiguous()
+        if khwc is not None and channels_last and self.stride[0] == self.stride[1] and self.stride[0] in (1, 2):
+            oh = (x.shape[2] + 2 * self.padding[0] - self.dilation[0] * (self.weight_shape[2] - 1) - 1) // self.stride[0] + 1
+            ow = (x.shape[3] + 2 * self.padding[1] - self.dilation[1] * (self.weight_shape[3] - 1) - 1) // self.stride[1] + 1
+            if x.shape[0] * oh * ow >= ops.A4_TC_MIN_ROWS:
+                # many output pixels: centred activation codes times the scaled codebook through the
+                # weight-only implicit-GEMM path, with the re-ordered indices and the scaled codebook
+                # cached on the module (no per-call index re-order)
+                codes = ops.centre_quantize_u4(x, self.act_scale, self.act_zero_point)
+                return ops.dimq_conv2d_wq(codes, self.packed_weight, self._scaled_codebook(), self.bias,
+                                          self.weight_shape, self.stride, self.padding, self.dilation, self.groups,
+                                          bits=4, out_dtype=self.out_dtype, epilogue=self.epilogue, residual=residual,
+                                          packed_khwc=khwc)
+        if residual is not None or self.epilogue is not None:
+            raise RuntimeError("a fused epilogue or residual needs the weight-only mode, or channels_last input "
+                               f"with at least {ops.A4_TC_MIN_ROWS} output pixels")
         return ops.dimq_conv2d_lut(x, self.packed_weight, self.codebook, self.act_scale, self.act_zero_point,
                                    self.bias, self.weight_shape, self.stride, self.padding, self.dilation,
                                    self.groups)

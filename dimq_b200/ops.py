@@ -147,6 +147,25 @@ def _a4_workspace(x_numel: int, conv_weight_numel: int, device: torch.device) ->
     return torch.empty(need.value, dtype=torch.uint8, device=device)
 
 
+def centre_quantize_u4(x: torch.Tensor, act_scale: float, act_zero_point: int) -> torch.Tensor:
+    """``clamp(rint(x / act_scale) + z, 0, 15) - z`` as bf16, same shape and memory format as ``x``:
+    the activation codes of the W4A4 ops with the zero point removed (integers in [-15, 15])."""
+    require_extension()
+    _require_cuda(x, "centre_quantize_u4")
+    if not x.is_floating_point():
+        raise RuntimeError("centre_quantize_u4 expects floating input")
+    _check_qparams(act_scale, act_zero_point)
+    dense = x.is_contiguous() or (x.dim() == 4 and x.is_contiguous(memory_format=torch.channels_last))
+    xc = x if dense else x.contiguous()
+    out = torch.empty_like(xc, dtype=torch.bfloat16)       # keeps the strides of a dense tensor
+    with torch.cuda.device(xc.device):
+        st = _lib.lib().dimq_centre_quantize_u4(_lib.ptr(xc), _lib.dtype_code(xc, "x"), C.c_int64(xc.numel()),
+                                                C.c_float(act_scale), C.c_int(act_zero_point), _lib.ptr(out),
+                                                _lib.stream_ptr(xc.device))
+    _lib.check(st, "centre_quantize_u4")
+    return out
+
+
 def _linear_lut_impl(x, packed_w, codebook, act_scale, act_zp, bias, out_features, in_features):
     _require_cuda(x, "linear_lut")
     _require_cuda(packed_w, "linear_lut")
@@ -442,6 +461,44 @@ def hard_quantize(w: torch.Tensor, codebooks: torch.Tensor, *, group_rows: int |
                                            _lib.stream_ptr(wc.device))
     _lib.check(st, "hard_quantize")
     return idx, packed
+
+
+def fake_quantize_ste(w: torch.Tensor, codebooks: torch.Tensor, *, group_rows: int | None = None,
+                      return_indices: bool = False):
+    """``w + (codebook[idx].to(w.dtype) - w)`` with ``idx`` the nearest codeword (ties to the lowest
+    index), in one kernel: the value of the straight-through fake quantisation of
+    quant/dimq_wrapper.py:72-75.  Returns ``out`` or ``(out, idx uint8)``."""
+    require_extension()
+    _require_cuda(w, "fake_quantize_ste")
+    if not w.is_floating_point() or w.dtype == torch.float64:
+        raise RuntimeError("fake_quantize_ste expects float32, float16 or bfloat16 weights")
+    wc = w.contiguous()
+    cb = codebooks.detach().to(device=wc.device, dtype=torch.float32).contiguous()
+    if cb.dim() == 1:
+        cb = cb.view(1, -1)
+    entries = cb.shape[1]
+    if entries == 0:
+        raise RuntimeError("centers must be non-empty")
+    if entries > 256:
+        raise RuntimeError("fake_quantize_ste supports at most 256 centres")
+    if cb.shape[0] == 1:
+        rows, cols, grp = 1, wc.numel(), 1
+    else:
+        if group_rows is None or wc.dim() < 1:
+            raise RuntimeError("grouped codebooks need group_rows")
+        rows = wc.shape[0]
+        cols = wc.numel() // max(rows, 1)
+        grp = int(group_rows)
+        if cb.shape[0] * grp < rows:
+            raise RuntimeError("not enough codebooks for the rows of w")
+    out = torch.empty_like(wc)
+    idx = torch.empty(wc.shape, dtype=torch.uint8, device=wc.device) if return_indices else None
+    with torch.cuda.device(wc.device):
+        st = _lib.lib().dimq_fake_quantize_ste(_lib.ptr(wc), _lib.dtype_code(wc, "w"), C.c_int64(rows), C.c_int64(cols),
+                                               _lib.ptr(cb), C.c_int(entries), C.c_int64(grp), _lib.ptr(out),
+                                               _lib.ptr(idx), _lib.stream_ptr(wc.device))
+    _lib.check(st, "fake_quantize_ste")
+    return (out, idx) if return_indices else out
 
 
 def _wq_weight(packed_weight: torch.Tensor, codebooks: torch.Tensor, bits: int, out_rows: int, numel: int,

@@ -318,6 +318,22 @@ class DIMQResNet18(nn.Module):
         pooled = x.mean(dim=(2, 3)).to(self.act_dtype)
         return self.fc(pooled.contiguous())
 
+    @torch.no_grad()
+    def calibrate(self, batches) -> dict[str, dict[str, Any]]:
+        """Per-layer u4 activation parameters from the input ranges the 4-bit convolutions see over
+        ``batches`` (keys are the checkpoint's layer names)."""
+        from .calibration import calibrate_activation_qparams
+
+        q = calibrate_activation_qparams(self, batches, select=lambda name, m: name.startswith("convs."))
+        return {name[len("convs."):].replace("__", "."): v for name, v in q.items()}
+
+    def set_activation_qparams(self, qparams: dict[str, dict[str, Any]]) -> int:
+        """Switch the named 4-bit convolutions to the W4A4 mode (the stem and the classifier, 8-bit, stay
+        weight-only, as the reference's default configuration leaves the first and last layer alone)."""
+        from .calibration import apply_activation_qparams
+
+        return apply_activation_qparams(self, {"convs." + k.replace(".", "__"): v for k, v in qparams.items()})
+
     def lut_flops(self, batch: int, image: int = 224) -> float:
         """Algorithmic flops (2 * outputs * K) of every quantised layer for one forward."""
         total = 0.0

@@ -140,6 +140,16 @@ DIMQ_API int dimq_hard_quantize(const void* w, int w_dtype, int64_t rows, int64_
                        int entries, int64_t group_rows, uint8_t* indices, uint8_t* packed, int bits,
                        void* stream);
 
+/* Straight-through fake quantisation of the QAT forward: out = w + (codebook[g][idx].to(w's type) - w),
+ * every operation rounded to the weight's element type as PyTorch evaluates it, idx as in
+ * dimq_hard_quantize; `out` has w's element type, `indices` (uint8, may be NULL) receives idx.  One
+ * pass over w instead of argmin + gather + two elementwise kernels.  Its gradient is the identity on w
+ * and none on the codebook, so the host side needs no backward kernel.
+ * Replaces the forward of fake_quant_weight in "hard_ste" mode, quant/dimq_wrapper.py:72-75, which
+ * calls hard_quantize_weight (quant/dimq.py:197-221) on every step. */
+DIMQ_API int dimq_fake_quantize_ste(const void* w, int w_dtype, int64_t rows, int64_t cols, const float* codebooks,
+                                    int entries, int64_t group_rows, void* out, uint8_t* indices, void* stream);
+
 /* ---- weight-only LUT GEMM / conv ---------------------------------------- */
 
 typedef struct dimq_wq_weight {
@@ -254,6 +264,15 @@ DIMQ_API int dimq_conv2d_wq_expand(const void* x, int x_dtype, const dimq_wq_wei
  * DIMQ_ERR_UNSUPPORTED where the tensor-core kernel does not apply (linear: K a multiple of 64;
  * convolution: channels_last x and y, groups 1, in_channels a multiple of 64, stride 1 or 2). */
 DIMQ_API int dimq_a4_workspace_bytes(int64_t x_numel, int64_t conv_weight_numel, int64_t* bytes);
+
+/* The first half of the two calls above on its own: codes[i] = bf16(clamp(rint(x[i] / act_scale) + act_zp,
+ * 0, 15) - act_zp), the reference's activation quantiser (csrc/dimq_pack.cu:37-48, dimq_common.cuh:17-21)
+ * with the zero point already subtracted; an integer in [-15, 15], exact in bf16, element order of x kept.
+ * A caller that keeps per-layer state (the scaled codebook act_scale * C, the re-ordered indices) feeds
+ * these codes to dimq_linear_wq_ws / dimq_conv2d_wq_ws and gets the W4A4 result without the per-call
+ * index re-order of dimq_conv2d_lut_tc. */
+DIMQ_API int dimq_centre_quantize_u4(const void* x, int x_dtype, int64_t numel, float act_scale, int act_zp,
+                                     void* codes_bf16, void* stream);
 DIMQ_API int dimq_linear_lut_tc(const void* x, int x_dtype, const uint8_t* packed_w, const void* codebook,
                                 int cb_dtype, float act_scale, int act_zp, const void* bias, int bias_dtype,
                                 float* y, int64_t M, int64_t N, int64_t K, void* workspace,

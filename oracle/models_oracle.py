@@ -121,8 +121,12 @@ class ResNet18Oracle:
 
     STAGES = ((64, 1), (128, 2), (256, 2), (512, 2))
 
-    def __init__(self, checkpoint: dict, round_dtype: torch.dtype | None = None) -> None:
+    def __init__(self, checkpoint: dict, round_dtype: torch.dtype | None = None,
+                 act_qparams: dict | None = None) -> None:
         self.round_dtype = round_dtype
+        # W4A4 mode: layers named here see their input through the reference's uniform affine u4
+        # quantiser (dimq_backend/reference.py:11-29), the contract of dimq_conv2d_reference (:113-144)
+        self.act_qparams = act_qparams or {}
         self.w, self.b, self.meta = {}, {}, {}
         for name, layer in checkpoint["layers"].items():
             self.w[name] = dequantize_layer(layer)
@@ -134,6 +138,10 @@ class ResNet18Oracle:
 
     def _conv(self, name, x):
         m = self.meta[name]
+        if name in self.act_qparams:
+            scale, zp = float(self.act_qparams[name]["scale"]), int(self.act_qparams[name]["zero_point"])
+            q = torch.clamp(torch.round(x.float() / scale) + zp, 0, 15)
+            x = scale * (q - zp)
         return F.conv2d(x, self.w[name], self.b[name], tuple(m["stride"]), tuple(m["padding"]))
 
     @torch.no_grad()

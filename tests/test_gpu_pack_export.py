@@ -228,3 +228,42 @@ def test_export_helpers_round_trip(ops, golden):
     w = torch.from_numpy(golden["hq_k16_w"])
     cb = torch.from_numpy(golden["hq_k16_centers"])
     assert np.array_equal(export.assign_weight_indices(w, cb).numpy(), golden["hq_k16_idx"])
+
+
+# ---- QAT side: straight-through fake quantisation (quant/dimq_wrapper.py:72-75) ----------------------
+
+@pytest.mark.parametrize("key", ["hq_k4", "hq_k8", "hq_k16", "hq_k256"])
+def test_fake_quant_weight_matches_reference_expression(ops, golden, key):
+    """Forward value bit-equal to  w + (centers[idx] - w)  built from the reference's own outputs
+    (hard_quantize_weight's values), gradient = identity on the weight, none on the centres."""
+    from dimq_b200.qat import fake_quant_weight
+
+    w = torch.from_numpy(golden[key + "_w"]).cuda().requires_grad_(True)
+    centers = torch.from_numpy(golden[key + "_centers"]).cuda().requires_grad_(True)
+    out = fake_quant_weight(w, centers, 262144)
+    want = golden[key + "_w"] + (golden[key + "_vals"] - golden[key + "_w"])      # fp32, operation by operation
+    assert np.array_equal(out.detach().cpu().numpy(), want)
+    g = torch.randn_like(out)
+    out.backward(g)
+    assert torch.equal(w.grad, g) and centers.grad is None
+    fq, idx = ops.fake_quantize_ste(w.detach(), centers.detach(), return_indices=True)
+    assert np.array_equal(idx.cpu().numpy(), golden[key + "_idx"].astype(np.uint8))
+    assert torch.equal(fq, out.detach())
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_fake_quant_weight_half_types_and_groups(ops, dtype):
+    """16-bit weights: every operation rounds to the weight's type, as PyTorch evaluates the expression;
+    grouped codebooks apply slice by slice."""
+    from dimq_b200.qat import fake_quant_weight
+
+    torch.manual_seed(0)
+    w = (torch.randn(300, 77) * 0.05).to(dtype).cuda()
+    books = torch.sort(torch.randn(3, 8) * 0.05, dim=1).values.cuda()
+    out = fake_quant_weight(w, books, group_rows=128)
+    idx, _ = ops.hard_quantize(w, books, group_rows=128)
+    rows = torch.arange(300, device="cuda") // 128
+    hard = books[rows[:, None], idx.long()].to(dtype)
+    assert torch.equal(out, w + (hard - w))
+    with pytest.raises(ValueError):
+        fake_quant_weight(w, books[:, :0])
