@@ -17,6 +17,8 @@ patch embedding are dense bf16 PyTorch ops.  Rank 0 prints one JSON line.
                 4-bit per-layer codebooks, stem and classifier at 8 bits).
 ``strong``    — N > 1 only: the configurations' batches (128 / 256) split over the GPUs, and the
                 gathered logits of one fixed batch compared with a single-GPU forward of it.
+``w4a4``      — ResNet-18 in the reference's W4A4 contract: activations quantised to u4 per layer with
+                calibrated parameters, on the tensor cores.
 ``micro``     — the index-streaming regime: M in {1, 4, 16} on the 1024 -> 4096 / 4096 -> 1024 shapes
                 over a ring of distinct weights larger than the L2.
 ``cpu_baseline`` / ``--impl reference`` — the reference's CPU path (dequantise + fp32
@@ -286,6 +288,13 @@ class ModelBench:
             self.ckpt = build_resnet18_checkpoint(seed=0, device=dev)
             self.model = DIMQResNet18(self.ckpt).to(dev).eval()
             self.flops_per_step = self.model.lut_flops(batch)
+            if workload == "resnet18_w4a4":
+                # the reference's actual contract: 4-bit weights AND 4-bit activations.  Per-layer u4
+                # parameters from a calibration pass over 16 synthetic images, then every 4-bit
+                # convolution runs in the W4A4 mode (stem and classifier stay 8-bit weight-only).
+                gen_c = torch.Generator(device="cpu").manual_seed(99)
+                calib = [torch.randn(8, 3, 224, 224, generator=gen_c).to(torch.bfloat16).to(dev) for _ in range(2)]
+                self.model.set_activation_qparams(self.model.calibrate(calib))
         self.n_bufs = 4  # rotating image buffers: with the activations of a step, far more than the 126 MB L2
         gen = torch.Generator(device="cpu").manual_seed(seed_images + rank)
         self.host_images = [torch.randn(batch, 3, 224, 224, generator=gen).to(torch.bfloat16).pin_memory()
@@ -523,6 +532,22 @@ def main() -> None:
                              "launches": mb.launches_per_forward, "cpu": cpu}
             mb.release()
             del mb
+        w4a4 = None
+        if not args.only:
+            B = WORKLOADS["resnet18"][1]
+            mb = ModelBench("resnet18_w4a4", B, dev, rank)
+            ms_res = mb.run_timed(mb.step_resident, args.steps, args.warmup, world)
+            ms_e2e = mb.run_timed(mb.step_e2e, args.steps, args.warmup, world)
+            w4a4 = {"metric": "resnet18_dimq_w4a4_images_per_s", "value": world * B * args.steps / (ms_res / 1e3),
+                    "unit": "images/s", "ms_per_step": ms_res / args.steps,
+                    "e2e": {"value": world * B * args.steps / (ms_e2e / 1e3), "unit": "images/s",
+                            "ms_per_step": ms_e2e / args.steps},
+                    "gpu_launches": mb.launches_per_forward * args.steps,
+                    "config": {"workload": "resnet18_w4a4_calibrated_batch256_per_gpu", "global_batch": world * B,
+                               "activations": "per-tensor affine u4 per layer, parameters from a min/max calibration "
+                                              "pass over 16 synthetic images; stem and classifier 8-bit weight-only"}}
+            mb.release()
+            del mb
         # ---- strong scaling: the configuration's batch split over the GPUs (BASELINE.json's wording) ----
         strong = None
         if world > 1 and not args.only:
@@ -583,6 +608,8 @@ def main() -> None:
         sec = model_line(other)
         line["secondary"] = {k: sec[k] for k in ("metric", "value", "unit", "ms_per_step", "config", "e2e",
                                                   "gpu_launches", "roofline")}
+    if w4a4 is not None:
+        line["w4a4"] = w4a4
     if strong is not None:
         for name, s in strong.items():
             # one GPU's time for the whole batch = the weak pass's step (the same batch per GPU)

@@ -40,6 +40,12 @@ int64_t conv_dense_workspace_bytes(int x_dtype, const dimq_wq_weight* w, const d
 int launch_conv2d_wq_dense(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
                            const void* residual, void* y, int y_dtype, const dimq_conv_geom* g, int epilogue,
                            void* workspace, int64_t workspace_bytes, cudaStream_t st);
+bool stem_conv_supported(const void* x, int x_dtype, const dimq_wq_weight* w, const dimq_conv_geom* g, const void* y,
+                         int y_dtype, const void* residual);
+int64_t stem_conv_workspace_bytes(int x_dtype, const dimq_wq_weight* w, const dimq_conv_geom* g);
+int launch_stem_conv(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
+                     const void* residual, void* y, int y_dtype, const dimq_conv_geom* g, int epilogue, void* workspace,
+                     int64_t workspace_bytes, cudaStream_t st);
 int read_device_status(uint32_t* status);
 int read_ms_status(uint32_t* status);
 int read_dense_status(uint32_t* status);
@@ -230,7 +236,8 @@ extern "C" int dimq_conv2d_wq_workspace_bytes(const void* x, int x_dtype, const 
   if (dimq_conv_out_size(&g) != DIMQ_OK || check_wq_weight(w, g.out_channels) != DIMQ_OK) return DIMQ_OK;
   if (!dense_pays(static_cast<int64_t>(g.batch) * g.out_h * g.out_w)) return DIMQ_OK;
   if ((static_cast<int64_t>(g.out_channels) * 2) % 16 != 0) return DIMQ_OK;
-  if (conv_dense_supported(x, x_dtype, w, &g, x, x_dtype, nullptr)) *bytes = conv_dense_workspace_bytes(x_dtype, w, &g);
+  if (stem_conv_supported(x, x_dtype, w, &g, x, x_dtype, nullptr)) *bytes = stem_conv_workspace_bytes(x_dtype, w, &g);
+  else if (conv_dense_supported(x, x_dtype, w, &g, x, x_dtype, nullptr)) *bytes = conv_dense_workspace_bytes(x_dtype, w, &g);
   return DIMQ_OK;
 }
 
@@ -260,6 +267,9 @@ extern "C" int dimq_conv2d_wq_expand(const void* x, int x_dtype, const dimq_wq_w
   const int rc = conv_wq_checks(x, x_dtype, w, bias, bias_dtype, y, y_dtype, geom, epilogue, &g, &empty);
   if (rc != DIMQ_OK) return rc;
   if (empty) return DIMQ_OK;
+  if (stem_conv_supported(x, x_dtype, w, &g, y, y_dtype, residual))
+    return launch_stem_conv(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, &g, epilogue, workspace,
+                            workspace_bytes, static_cast<cudaStream_t>(stream));
   return launch_conv2d_wq_dense(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, &g, epilogue, workspace,
                                 workspace_bytes, static_cast<cudaStream_t>(stream));
 }
@@ -274,7 +284,12 @@ extern "C" int dimq_conv2d_wq_ws(const void* x, int x_dtype, const dimq_wq_weigh
   if (empty) return DIMQ_OK;
   int64_t need = 0;
   if (workspace != nullptr && dimq_conv2d_wq_workspace_bytes(x, x_dtype, w, geom, &need) == DIMQ_OK && need > 0 &&
-      conv_dense_supported(x, x_dtype, w, &g, y, y_dtype, residual)) {
+      stem_conv_supported(x, x_dtype, w, &g, y, y_dtype, residual)) {
+    if (workspace_bytes < need) return DIMQ_ERR_SCRATCH_TOO_SMALL;
+    return launch_stem_conv(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, &g, epilogue, workspace,
+                            workspace_bytes, static_cast<cudaStream_t>(stream));
+  }
+  if (workspace != nullptr && need > 0 && conv_dense_supported(x, x_dtype, w, &g, y, y_dtype, residual)) {
     if (workspace_bytes < need) return DIMQ_ERR_SCRATCH_TOO_SMALL;
     return launch_conv2d_wq_dense(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, &g, epilogue, workspace,
                                   workspace_bytes, static_cast<cudaStream_t>(stream));

@@ -673,6 +673,451 @@ int launch_linear_wq_dense(const void* x, int x_dtype, const dimq_wq_weight* w, 
   return launch_dense(maps, p, workspace, K, x_dtype, bias, bias_dtype, residual, y_dtype, epilogue, st);
 }
 
+// ---- stem convolution: 3 input channels, stride 2 ----------------------------------------------------
+//
+// The first convolution of an image model (ResNet: 7x7, stride 2, pad 3, 3 -> 64) has too few input
+// channels for 64-channel k blocks.  Here the patch matrix exists only in shared memory: the input window
+// of a 16 x 8 output tile (NHWC, 6 bytes per pixel) is copied into shared memory, builder warps cut it into
+// the 128 patch rows of the A operand (K-major, 128-byte swizzle) and the MMA warp multiplies them with the
+// expanded weight, which stays resident in shared memory for the whole kernel.
+//   k = kh * 24 + kw * 3 + c   (kw * 3 + c < KW * 3 <= 24, kh < KH <= 8; the rest of the 192 columns is zero)
+// so the 24 values of one kernel row of a patch are 24 consecutive input elements.
+// Warp roles (448 threads): warps 0-7 build A tiles (double-buffered), warp 8 issues the MMAs, warps 9-12 are
+// the epilogue (bias / activation / residual, swizzled staging, one TMA store per 32 pixels x 32 channels),
+// warp 13 fetches the input windows (one TMA box per tile, zero fill outside the image).
+namespace {
+
+constexpr int kStemTW = 16, kStemTH = 8;        // output tile: 16 x 8 pixels of one image = 128 rows
+constexpr int kStemKRow = 24;                   // padded elements per kernel row (8 pixels x 3 channels)
+constexpr int kStemK = 192;                     // padded reduction length: 3 k blocks of 64
+constexpr int kStemBuilders = 8;
+constexpr int kStemThreads = (kStemBuilders + 1 + 4 + 1) * 32;   // builders, MMA, epilogue, window producer
+constexpr int kStemWinRows = 2 * (kStemTH - 1) + 8;          // input rows a tile can touch (KH <= 8): 22
+// elements per window row: the 114 a tile's patches span, up to 7 more in front (the TMA box starts on a
+// 16-byte boundary) - 144 makes the row pitch 72 words, which keeps the two half-warps of a patch read on
+// different banks
+constexpr int kStemWinPitch = 144;
+constexpr uint32_t kStemABytes = kBM * kStemK * 2;           // 48 KB per A buffer
+constexpr uint32_t kStemWinBytes = kStemWinRows * kStemWinPitch * 2;   // 6336: what one TMA box delivers
+constexpr uint32_t kStemWinStride = (kStemWinBytes + 127u) & ~127u;      // a TMA box must land on a 128-byte boundary
+
+struct StemParams {
+  const void* x;            // NHWC 16-bit input, 3 channels
+  const void* bias;
+  int bias_dtype;
+  const void* residual;
+  int y_dtype;
+  int64_t N;                // output channels (multiple of 16, <= 128)
+  int H, W, OH, OW, Bn;
+  int KH, KW, pad_h, pad_w;
+  int tiles_w, tiles_h, m_tiles;
+  int passes;
+  uint32_t b_bytes;         // N * 384 * passes
+  uint32_t idesc;
+  int epilogue;
+};
+
+struct StemMaps {
+  CUtensorMap x;      // input as [B][H][W * 3] elements, boxes of one tile's window
+  CUtensorMap b;      // expanded weight [N][192 * passes]
+  CUtensorMap y;      // output NHWC, boxes of 32 channels x 16 x 2 pixels
+};
+
+struct StemHeader {
+  uint64_t a_full[2], a_empty[2], d_full[2], d_empty[2], b_full, win_full[2], win_empty[2];
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+};
+
+template <int ES>
+__global__ void __launch_bounds__(kStemThreads, 1)
+lut_stem_conv_kernel(const __grid_constant__ StemMaps maps, const StemParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // [A0 | A1 (48 KB each)] [B: passes x 3 k blocks of N x 128 B] [header] [bias slices] [staging] [windows]
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* b_tile = smem + 2 * kStemABytes;
+  StemHeader* hdr = reinterpret_cast<StemHeader*>(b_tile + p.b_bytes);
+  float* bias_area = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(hdr) + kHeaderBytes);
+  unsigned char* staging = reinterpret_cast<unsigned char*>(bias_area) + 1024;   // 1024-aligned
+  constexpr uint32_t kStagingBytes = 32u * 32u * ES;
+  unsigned char* windows = staging + 4 * kStagingBytes;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const uint32_t kb_bytes = static_cast<uint32_t>(p.N) * 128u;   // one k block of the weight
+
+  if (tid == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&hdr->a_full[s]), kStemBuilders);
+      mbar_init(smem_u32(&hdr->a_empty[s]), 1);
+      mbar_init(smem_u32(&hdr->d_full[s]), 1);
+      mbar_init(smem_u32(&hdr->d_empty[s]), 4);
+      mbar_init(smem_u32(&hdr->win_full[s]), 1);
+      mbar_init(smem_u32(&hdr->win_empty[s]), kStemBuilders);
+    }
+    mbar_init(smem_u32(&hdr->b_full), 1);
+    hdr->abort_flag = 0u;
+    fence_barrier_init();
+    prefetch_tensormap(&maps.x);
+    prefetch_tensormap(&maps.b);
+    prefetch_tensormap(&maps.y);
+  }
+  if (warp == kStemBuilders) {
+    tmem_alloc(smem_u32(&hdr->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  // columns 168..191 of every patch row (k beyond KH * 24) never change: zero the two A buffers once
+  for (uint32_t i = tid; i < 2 * kStemABytes / 16; i += kStemThreads) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0u, 0u, 0u, 0u);
+  fence_proxy_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = hdr->tmem_base;
+  volatile uint32_t* abort_flag = &hdr->abort_flag;
+
+  auto tile_origin = [&](int t, int& b, int& oh0, int& ow0) {
+    ow0 = (t % p.tiles_w) * kStemTW;
+    oh0 = ((t / p.tiles_w) % p.tiles_h) * kStemTH;
+    b = t / (p.tiles_w * p.tiles_h);
+  };
+
+  if (warp == kStemBuilders + 5) {
+    // ===================== window producer =====================
+    // One TMA box per tile: input rows 2 oh0 - pad_h .. + 21, elements from the 16-byte boundary at or
+    // before pixel 2 ow0 - pad_w; rows and elements outside the image arrive as zeros.
+    uint32_t buf = 0, phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < p.m_tiles && ok; t += gridDim.x) {
+      int b, oh0, ow0;
+      tile_origin(t, b, oh0, ow0);
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->win_empty[buf]), phase ^ 1u, abort_flag, 0x2600u | buf))) { ok = false; break; }
+      const int e0 = (2 * ow0 - p.pad_w) * 3;
+      const int x_al = e0 & ~7;                      // round down to 8 elements (also right for negatives)
+      if (elect_one()) {
+        const uint32_t full = smem_u32(&hdr->win_full[buf]);
+        mbar_arrive_expect_tx(full, kStemWinBytes);
+        asm volatile(
+            "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+            ::"r"(smem_u32(windows + buf * kStemWinStride)), "l"(reinterpret_cast<uint64_t>(&maps.x)), "r"(full), "r"(x_al),
+              "r"(2 * oh0 - p.pad_h), "r"(b)
+            : "memory");
+      }
+      __syncwarp();
+      if (++buf == 2) { buf = 0; phase ^= 1u; }
+    }
+    if (!ok && lane == 0) {   // gave up: let the copy still in flight land before the CTA exits
+      for (int s2 = 0; s2 < 2; ++s2)
+        for (uint32_t it = 0; it < kSpinLimit; ++it)
+          if (mbar_try_wait(smem_u32(&hdr->win_full[s2]), 0u) || mbar_try_wait(smem_u32(&hdr->win_full[s2]), 1u)) break;
+    }
+    __syncwarp();
+  } else if (warp < kStemBuilders) {
+    // ===================== patch builders =====================
+    uint32_t buf = 0, phase = 0;
+    bool ok = true;
+    const int n_chunks = p.KH * 3;                   // 16-byte pieces of a patch row that carry data
+    const int row_elems = p.KW * 3;                  // values of one kernel row
+    for (int t = blockIdx.x; t < p.m_tiles && ok; t += gridDim.x) {
+      int b, oh0, ow0;
+      tile_origin(t, b, oh0, ow0);
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->win_full[buf]), phase, abort_flag, 0x2700u | buf))) { ok = false; break; }
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->a_empty[buf]), phase ^ 1u, abort_flag, 0x2100u | buf))) { ok = false; break; }
+      // patch rows: piece (row, chunk) = 8 consecutive elements of kernel row chunk / 3.  The patch of
+      // output column j starts at window element off + 6 j, off = distance of pixel 2 ow0 - pad_w from
+      // the box start; when off is odd the eight elements straddle five words and are funnel-shifted
+      const int e0 = (2 * ow0 - p.pad_w) * 3;
+      const int off = e0 - (e0 & ~7);
+      const uint32_t sh = (off & 1) ? 16u : 0u;
+      unsigned char* a_tile = smem + buf * kStemABytes;
+      const uint32_t* win32 = reinterpret_cast<const uint32_t*>(windows + buf * kStemWinStride);
+      for (int i = tid; i < kBM * n_chunks; i += kStemBuilders * 32) {
+        const int row = i & (kBM - 1), chunk = i >> 7;
+        const int kh = chunk / 3, part = chunk - kh * 3;
+        const int oh_l = row >> 4, ow_l = row & 15;
+        const uint32_t* src = win32 + (2 * oh_l + kh) * (kStemWinPitch / 2) + ((off + 6 * ow_l + 8 * part) >> 1);
+        uint32_t w5[5];
+#pragma unroll
+        for (int m = 0; m < 5; ++m) w5[m] = src[m];   // the fifth word may belong to the next row: it is shifted out when sh == 0
+        uint32_t q4[4];
+#pragma unroll
+        for (int m = 0; m < 4; ++m) q4[m] = __funnelshift_r(w5[m], w5[m + 1], sh);
+        // elements past the kernel row's KW * 3 values belong to the next pixel: their weights are zero,
+        // but a non-finite value there must not reach the product, so they are cleared
+        const int valid = row_elems - 8 * part;
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          if (valid <= 2 * m) q4[m] = 0u;
+          else if (valid == 2 * m + 1) q4[m] &= 0xFFFFu;
+        }
+        const uint4 q = make_uint4(q4[0], q4[1], q4[2], q4[3]);
+        const int kb = chunk >> 3, c = chunk & 7;
+        *reinterpret_cast<uint4*>(a_tile + kb * (kBM * 128) + row * 128 + ((c ^ (row & 7)) << 4)) = q;
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(smem_u32(&hdr->a_full[buf]));
+        mbar_arrive(smem_u32(&hdr->win_empty[buf]));
+      }
+      if (++buf == 2) { buf = 0; phase ^= 1u; }
+    }
+  } else if (warp == kStemBuilders) {
+    // ===================== MMA issuer =====================
+    bool ok = true;
+    if (elect_one()) {
+      mbar_arrive_expect_tx(smem_u32(&hdr->b_full), p.b_bytes);
+      for (int kb = 0; kb < 3 * p.passes; ++kb)
+        tma_load_2d(smem_u32(b_tile + kb * kb_bytes), &maps.b, smem_u32(&hdr->b_full), kb * kBK, 0);
+    }
+    __syncwarp();
+    ok = __all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->b_full), 0u, abort_flag, 0x2200u));
+    uint32_t buf = 0, phase = 0, as = 0, aph = 0;
+    const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem));
+    const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(b_tile));
+    for (int t = blockIdx.x; t < p.m_tiles && ok; t += gridDim.x) {
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->d_empty[as]), aph ^ 1u, abort_flag, 0x2300u | as))) { ok = false; break; }
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->a_full[buf]), phase, abort_flag, 0x2400u | buf))) { ok = false; break; }
+      tc_fence_after();
+      if (elect_one()) {
+        const uint32_t d_tmem = tmem_base + as * kAccCols;
+        for (int kb = 0; kb < 3 * p.passes; ++kb) {
+          const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((buf * kStemABytes + (kb % 3) * (kBM * 128)) >> 4);
+          const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((kb * kb_bytes) >> 4);
+#pragma unroll
+          for (int j = 0; j < kBK / 16; ++j)
+            mma_f16_ss(d_tmem, a_desc + static_cast<uint64_t>(2 * j), b_desc + static_cast<uint64_t>(2 * j), p.idesc,
+                       (kb | j) ? 1u : 0u);
+        }
+        mma_commit(smem_u32(&hdr->a_empty[buf]));
+        mma_commit(smem_u32(&hdr->d_full[as]));
+      }
+      __syncwarp();
+      if (++buf == 2) { buf = 0; phase ^= 1u; }
+      if (++as == kAccStages) { as = 0; aph ^= 1u; }
+    }
+  } else {
+    // ===================== epilogue =====================
+    const int quarter = warp & 3;          // TMEM lanes [32 quarter, +32): tile rows 2 quarter, 2 quarter + 1
+    const int ew = warp - (kStemBuilders + 1);
+    float* my_bias = bias_area + ew * 32;
+    unsigned char* my_out = staging + ew * kStagingBytes;
+    const int n_chunks = static_cast<int>((p.N + 31) / 32);
+    uint32_t as = 0, aph = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < p.m_tiles && ok; t += gridDim.x) {
+      int b, oh0, ow0;
+      tile_origin(t, b, oh0, ow0);
+      const int pj = quarter * 32 + lane;
+      const int oh = oh0 + (pj >> 4), ow = ow0 + (pj & 15);
+      int64_t row_off = -1;
+      if (oh < p.OH && ow < p.OW) row_off = ((static_cast<int64_t>(b) * p.OH + oh) * p.OW + ow) * p.N;
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->d_full[as]), aph, abort_flag, 0x2500u | as))) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * kAccCols;
+      for (int c = 0; c < n_chunks; ++c) {
+        const int64_t n_first = static_cast<int64_t>(c) * 32;
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld32(d_tmem + c * 32, r);
+        my_bias[lane] = (p.bias != nullptr && n_first + lane < p.N) ? load_as_float(p.bias, p.bias_dtype, n_first + lane) : 0.0f;
+        tmem_ld_wait();
+        if (c + 1 == n_chunks) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&hdr->d_empty[as]));
+        }
+        __syncwarp();
+        float v[32], res[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        const int64_t left = p.N - n_first;
+        const int valid = left >= 32 ? 32 : static_cast<int>(left);
+        const int epi = (p.epilogue == DIMQ_EPI_GELU && ES == 2) ? kEpiGelu16 : p.epilogue;
+        if (p.residual != nullptr) {
+          if (row_off >= 0)
+            load_residual<ES>(static_cast<const char*>(p.residual) + (row_off + n_first) * ES, p.y_dtype, valid, res);
+          else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) res[j] = 0.0f;
+          }
+          finish_row_epi<true>(v, my_bias, res, epi);
+        } else {
+          finish_row_epi<false>(v, my_bias, res, epi);
+        }
+        if (elect_one()) tma_store_wait_read();
+        __syncwarp();
+        if (ES == 2) {
+          unsigned char* row_ptr = my_out + lane * 64;
+          const int sw = (lane >> 1) & 3;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 q;
+            q.x = pack16(v[8 * j], v[8 * j + 1], p.y_dtype);
+            q.y = pack16(v[8 * j + 2], v[8 * j + 3], p.y_dtype);
+            q.z = pack16(v[8 * j + 4], v[8 * j + 5], p.y_dtype);
+            q.w = pack16(v[8 * j + 6], v[8 * j + 7], p.y_dtype);
+            *reinterpret_cast<uint4*>(row_ptr + ((j ^ sw) << 4)) = q;
+          }
+        } else {
+          unsigned char* row_ptr = my_out + lane * 128;
+          const int sw = lane & 7;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<float4*>(row_ptr + ((j ^ sw) << 4)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (elect_one()) {
+          tma_store_4d(&maps.y, smem_u32(my_out), static_cast<int>(n_first), ow0, oh0 + 2 * quarter, b);
+          tma_store_commit();
+        }
+      }
+      if (++as == kAccStages) { as = 0; aph ^= 1u; }
+    }
+    __syncwarp();
+    if (elect_one()) tma_store_wait_all();
+    __syncwarp();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kStemBuilders) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// Expanded stem weight [N][192 * passes]: column kh * 24 + kw * 3 + c of row n is the codeword of
+// idx[n][c][kh][kw] (the reference's "conv_kcrs" stream), zero elsewhere; lo terms in the second pass.
+__global__ void __launch_bounds__(256)
+stem_expand_kernel(const uint8_t* __restrict__ packed, int bits, int64_t nbytes, const void* __restrict__ codebooks,
+                   int cb_dtype, int entries, int64_t group_rows, int64_t N, int KH, int KW, int fmt, int passes,
+                   uint16_t* __restrict__ out) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= N * kStemK) return;
+  const int64_t n = i / kStemK;
+  const int k = static_cast<int>(i - n * kStemK);
+  const int kh = k / kStemKRow, j = k - kh * kStemKRow;
+  const int kw = j / 3, c = j - kw * 3;
+  float v = 0.0f;
+  if (kh < KH && kw < KW) {
+    const uint32_t idx = get_index(packed, ((n * 3 + c) * KH + kh) * KW + kw, bits, nbytes);
+    if (idx < static_cast<uint32_t>(entries)) v = load_as_float(codebooks, cb_dtype, (n / group_rows) * entries + idx);
+  }
+  uint16_t hi, lo = 0;
+  if (fmt == 0) {
+    hi = __half_as_ushort(__float2half_rn(v));
+  } else {
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    hi = __bfloat16_as_ushort(h);
+    lo = __bfloat16_as_ushort(__float2bfloat16_rn(v - __bfloat162float(h)));
+  }
+  out[n * (kStemK * passes) + k] = hi;
+  if (passes == 2) out[n * (kStemK * passes) + kStemK + k] = lo;
+}
+
+}  // namespace
+
+bool stem_conv_supported(const void* x, int x_dtype, const dimq_wq_weight* w, const dimq_conv_geom* g, const void* y,
+                         int y_dtype, const void* residual) {
+  if (x_dtype != DIMQ_BF16 && x_dtype != DIMQ_F16) return false;
+  if (y_dtype != x_dtype && y_dtype != DIMQ_F32) return false;
+  if (g->groups != 1 || g->in_channels != 3) return false;
+  if (g->stride_h != 2 || g->stride_w != 2 || g->dilation_h != 1 || g->dilation_w != 1) return false;
+  if (g->kernel_h > 8 || g->kernel_w * 3 > kStemKRow) return false;
+  if (g->pad_h < 0 || g->pad_w < 0 || g->pad_h > 8 || g->pad_w > 8) return false;
+  if (g->out_channels % 16 != 0 || g->out_channels > 128) return false;
+  const int64_t W = g->in_w, H = g->in_h;
+  if (g->x_stride[1] != 1 || g->x_stride[3] != 3 || g->x_stride[2] != W * 3 || g->x_stride[0] != H * W * 3) return false;
+  const int64_t OC = g->out_channels, OW = g->out_w, OH = g->out_h;
+  if (g->y_stride[1] != 1 || g->y_stride[3] != OC || g->y_stride[2] != OW * OC || g->y_stride[0] != OH * OW * OC) return false;
+  const int64_t es = y_dtype == DIMQ_F32 ? 4 : 2;
+  // the window is a TMA box over [B][H][W * 3]: 16-byte aligned base and row pitch
+  if (!aligned(x, 16) || (W * 6) % 16 != 0 || !aligned(y, 16) || (OC * es) % 16 != 0) return false;
+  if (residual != nullptr && !aligned(residual, 16)) return false;
+  if (w->bits != 2 && w->bits != 3 && w->bits != 4 && w->bits != 8) return false;
+  return g->batch >= 1 && OW >= 1 && OH >= 1;
+}
+
+int64_t stem_conv_workspace_bytes(int x_dtype, const dimq_wq_weight* w, const dimq_conv_geom* g) {
+  return static_cast<int64_t>(g->out_channels) * kStemK * 2 * passes_for(x_dtype, w);
+}
+
+int launch_stem_conv(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
+                     const void* residual, void* y, int y_dtype, const dimq_conv_geom* g, int epilogue, void* workspace,
+                     int64_t workspace_bytes, cudaStream_t st) {
+  if (!stem_conv_supported(x, x_dtype, w, g, y, y_dtype, residual)) return DIMQ_ERR_UNSUPPORTED;
+  if (workspace == nullptr || workspace_bytes < stem_conv_workspace_bytes(x_dtype, w, g)) return DIMQ_ERR_SCRATCH_TOO_SMALL;
+  if (!aligned(workspace, 16)) return DIMQ_ERR_ALIGNMENT;
+  EncodeTiledFn encode = encode_tiled();
+  if (encode == nullptr) return DIMQ_ERR_DRIVER;
+  StemParams p;
+  memset(&p, 0, sizeof(p));
+  StemMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  const int fmt = x_dtype == DIMQ_BF16 ? 1 : 0;
+  p.x = x;
+  p.bias = bias;
+  p.bias_dtype = bias_dtype;
+  p.residual = residual;
+  p.y_dtype = y_dtype;
+  p.N = g->out_channels;
+  p.H = g->in_h; p.W = g->in_w; p.OH = g->out_h; p.OW = g->out_w; p.Bn = g->batch;
+  p.KH = g->kernel_h; p.KW = g->kernel_w; p.pad_h = g->pad_h; p.pad_w = g->pad_w;
+  p.tiles_w = (p.OW + kStemTW - 1) / kStemTW;
+  p.tiles_h = (p.OH + kStemTH - 1) / kStemTH;
+  const int64_t m_tiles = static_cast<int64_t>(p.tiles_w) * p.tiles_h * p.Bn;
+  if (m_tiles >= 0x7FFFFFFF) return DIMQ_ERR_TOO_LARGE;
+  p.m_tiles = static_cast<int>(m_tiles);
+  p.passes = passes_for(x_dtype, w);
+  p.b_bytes = static_cast<uint32_t>(p.N) * kStemK * 2 * p.passes;
+  p.idesc = tc::make_idesc_f16(fmt, fmt, kBM, static_cast<int>(p.N));
+  p.epilogue = epilogue;
+  const int64_t ktot = static_cast<int64_t>(kStemK) * p.passes;
+  const cuuint64_t bdims[2] = {static_cast<cuuint64_t>(ktot), static_cast<cuuint64_t>(p.N)};
+  const cuuint64_t bstr[1] = {static_cast<cuuint64_t>(ktot) * 2};
+  const cuuint32_t bbox[2] = {kBK, static_cast<cuuint32_t>(p.N)};
+  const cuuint32_t estr[2] = {1, 1};
+  if (encode(&maps.b, fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, workspace, bdims,
+             bstr, bbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return DIMQ_ERR_DRIVER;
+  const cuuint64_t xdims[3] = {static_cast<cuuint64_t>(p.W) * 3, static_cast<cuuint64_t>(p.H), static_cast<cuuint64_t>(p.Bn)};
+  const cuuint64_t xstr[2] = {static_cast<cuuint64_t>(p.W) * 6, static_cast<cuuint64_t>(p.H) * p.W * 6};
+  const cuuint32_t xbox[3] = {kStemWinPitch, kStemWinRows, 1};
+  const cuuint32_t xes[3] = {1, 1, 1};
+  if (encode(&maps.x, fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+             const_cast<void*>(x), xdims, xstr, xbox, xes, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return DIMQ_ERR_DRIVER;
+  const cuuint64_t odims[4] = {static_cast<cuuint64_t>(p.N), static_cast<cuuint64_t>(p.OW), static_cast<cuuint64_t>(p.OH),
+                               static_cast<cuuint64_t>(p.Bn)};
+  const cuuint32_t obox[4] = {32, kStemTW, 2, 1};
+  if (!out_map(encode, &maps.y, y, y_dtype, 4, odims, obox)) return DIMQ_ERR_DRIVER;
+  const int64_t n_w = p.N * 3 * p.KH * p.KW;
+  const int64_t total = p.N * kStemK;
+  stem_expand_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(
+      w->packed, w->bits, (n_w * w->bits + 7) / 8, w->codebooks, w->cb_dtype, w->entries, w->group_rows, p.N, p.KH, p.KW,
+      fmt, p.passes, static_cast<uint16_t*>(workspace));
+  int rc = launch_status();
+  if (rc != DIMQ_OK) return rc;
+  const int es = y_dtype == DIMQ_F32 ? 4 : 2;
+  const size_t smem = 1024 + 2 * kStemABytes + p.b_bytes + kHeaderBytes + 1024 + 4 * 32 * 32 * es + 2 * kStemWinStride;
+  if (smem > kSmemMax) return DIMQ_ERR_UNSUPPORTED;
+  const int grid = p.m_tiles < kNumSMs ? p.m_tiles : kNumSMs;
+  cudaError_t e;
+  if (es == 2) {
+    e = cudaFuncSetAttribute(lut_stem_conv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    lut_stem_conv_kernel<2><<<grid, kStemThreads, smem, st>>>(maps, p);
+  } else {
+    e = cudaFuncSetAttribute(lut_stem_conv_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    lut_stem_conv_kernel<4><<<grid, kStemThreads, smem, st>>>(maps, p);
+  }
+  return launch_status();
+}
+
 // ---- implicit-GEMM convolution ------------------------------------------------------------------------
 
 bool conv_dense_supported(const void* x, int x_dtype, const dimq_wq_weight* w, const dimq_conv_geom* g, const void* y,

@@ -647,12 +647,14 @@ def dimq_conv2d_wq(x: torch.Tensor, packed_weight: torch.Tensor, codebooks: torc
         if residual.dtype != out_dtype or residual.shape != y.shape or residual.stride() != y.stride():
             raise RuntimeError("residual must match the output shape, dtype and memory format")
         res = residual
-    if algo in (None, "expand") and packed_khwc is not None:
-        # many output pixels: expand the re-ordered indices once to a 16-bit weight in scratch and run
-        # the dense implicit-GEMM kernel ("expand" forces that form at any size)
+    if algo in (None, "expand"):
+        # Many output pixels: expand the indices once to a 16-bit weight in scratch and run a dense
+        # tensor-core kernel - the implicit GEMM over the re-ordered indices (packed_khwc), or the stem
+        # kernel for a 3-channel stride-2 convolution.  "expand" forces that form at any size.
         need = C.c_int64(0)
         if algo == "expand":
-            numel_k = numel // g.out_channels
+            # the larger of the two layouts: [OC][KH*KW*IC] and the stem's [OC][192]
+            numel_k = max(numel // g.out_channels, 192)
             _lib.check(_lib.lib().dimq_expand_workspace_bytes(_lib.dtype_code(xc, "x"), C.byref(w),
                                                               C.c_int64(g.out_channels), C.c_int64(numel_k),
                                                               C.byref(need)), "expand_workspace_bytes")
@@ -670,8 +672,6 @@ def dimq_conv2d_wq(x: torch.Tensor, packed_weight: torch.Tensor, codebooks: torc
             _lib.LAUNCH_COUNT[0] += 1  # the expansion and the convolution
             del keep
             return y
-    if algo == "expand":
-        raise RuntimeError("conv2d_wq: algo='expand' needs packed_khwc (see conv_prepack)")
     with torch.cuda.device(x.device):
         st = _lib.lib().dimq_conv2d_wq(_lib.ptr(xc), _lib.dtype_code(xc, "x"), C.byref(w), _lib.ptr(b), b_dt,
                                        _lib.ptr(res), _lib.ptr(y), _lib.dtype_code(y, "y"), C.byref(g),

@@ -253,9 +253,9 @@ class DIMQResNet18(nn.Module):
     """ResNet-18 forward over packed DIMQ layers, channels_last bf16 activations.
 
     3x3 / 1x1 convolutions with a multiple of 64 input channels run as tensor-core implicit GEMMs with
-    bias + ReLU (+ residual) in the epilogue.  The 7x7 stem (3 input channels) is lowered to a GEMM
-    over an explicit im2col matrix (K = 147 padded to 192) and runs through the LUT GEMM; max-pool and
-    the global average pool are PyTorch ops.
+    bias + ReLU (+ residual) in the epilogue; the 7x7 stem (3 input channels) through the stem kernel,
+    which builds its patch rows in shared memory; the max-pool is a dimq_b200 kernel, the global
+    average pool a PyTorch op.
     """
 
     def __init__(self, checkpoint: dict[str, Any], *, act_dtype: torch.dtype = torch.bfloat16,
@@ -272,26 +272,19 @@ class DIMQResNet18(nn.Module):
             self.convs[name.replace(".", "__")] = DIMQConv2d.from_export_layer(layer, out_dtype=act_dtype)
         fc = checkpoint["layers"]["fc"]
         self.fc = DIMQLinear.from_export_layer(fc, out_dtype=torch.float32)
-        # stem: indices re-ordered to (kh, kw, c) and padded from K = 147 to 192 columns
+        # stem (7x7, stride 2, 3 input channels): its own tensor-core kernel builds the patches in shared
+        # memory; bias + ReLU fused
         stem = checkpoint["layers"]["conv1"]
+        self.stem = DIMQConv2d.from_export_layer(stem, out_dtype=act_dtype, epilogue="relu")
         oc, ic, kh, kw = stem["weight_shape"]
-        khwc = ops.conv_prepack(stem["packed_weight"], stem["weight_shape"], 8)
-        idx = ops.unpack_bits(khwc, oc * ic * kh * kw, 8).view(oc, kh * kw * ic)
         self.stem_k = kh * kw * ic
-        self.stem_kp = (self.stem_k + 63) // 64 * 64
-        padded = torch.zeros(oc, self.stem_kp, dtype=torch.uint8, device=idx.device)
-        padded[:, : self.stem_k] = idx
-        self.stem = DIMQLinear(ops.pack_bits(padded, 8), stem["codebook"], None, None, oc, self.stem_kp, stem["bias"],
-                               bits=8, out_dtype=act_dtype, epilogue="relu")
 
     def _conv(self, name: str):
         return self.convs[name.replace(".", "__")]
 
     def _stem(self, images: torch.Tensor) -> torch.Tensor:
-        b = images.shape[0]
-        cols, (oh, ow) = ops.im2col(images.to(self.act_dtype), (64, 3, 7, 7), (2, 2), (3, 3), padded_k=self.stem_kp)
-        y = self.stem(cols)                                        # [B*OH*OW, 64], bias + ReLU fused
-        return y.view(b, oh, ow, -1).permute(0, 3, 1, 2)           # logical NCHW over NHWC storage
+        x = images.to(self.act_dtype).contiguous(memory_format=torch.channels_last)   # NCHW images -> NHWC
+        return self.stem(x)
 
     def forward(self, images: torch.Tensor) -> torch.Tensor:
         x = self._stem(images)

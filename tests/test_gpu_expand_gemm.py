@@ -325,3 +325,84 @@ def test_resnet_layer_geometries_at_batch_256(ops, layer):
     max_abs, rel = float(diff.abs().max()), float(diff.norm() / want.norm())
     print(f"ResNet layer {layer} at batch {b}: max_abs={max_abs:.3e} rel_l2={rel:.3e}")
     assert max_abs <= MAX_ABS and rel <= REL_L2 and ops.last_device_status() == 0
+
+
+# ---- stem convolution (3 input channels, stride 2) -----------------------------------------------------
+
+STEM_CASES = [
+    # batch, H, W, OC, k, pad, bits
+    (2, 224, 224, 64, 7, 3, 8),      # the ResNet stem
+    (3, 37, 40, 64, 7, 3, 8),        # odd height, 20 output columns: ragged tiles on every side
+    (2, 64, 48, 32, 3, 1, 4),        # 3x3, 32 channels
+    (1, 30, 56, 128, 5, 2, 4),       # 5x5, 128 channels
+    (2, 9, 24, 16, 7, 0, 3),         # no padding, 16 channels, map smaller than a tile
+]
+
+
+@pytest.mark.parametrize("case", STEM_CASES)
+@pytest.mark.parametrize("mode", ["bf16_cb", "fp16_cb_two_terms"])
+def test_stem_conv_fp32_out(ops, case, mode):
+    b, h, w, oc, k, pad, bits = case
+    rng = np.random.default_rng(sum(case))
+    cw = make_weight(oc, 3 * k * k, bits, seed=oc + k, std=(2.0 / (3 * k * k)) ** 0.5,
+                     cb_dtype="bf16" if mode == "bf16_cb" else np.float16)
+    cb_t = torch.bfloat16 if mode == "bf16_cb" else torch.float16
+    x = bf16_round(rng.standard_normal((b, 3, h, w)).astype(np.float32))
+    bias = rng.standard_normal(oc).astype(np.float32)
+    wshape = (oc, 3, k, k)
+    want = _conv_oracle(x, cw, bits, wshape, bias, 2, pad, 1)
+    x_cl = _cuda(x, torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    got = ops.dimq_conv2d_wq(x_cl, _cuda(cw["packed"]), _cuda(cw["codebooks"], cb_t), _cuda(bias), wshape, (2, 2),
+                             (pad, pad), (1, 1), 1, bits=bits, algo="expand")
+    assert ops.last_device_status() == 0
+    assert got.is_contiguous(memory_format=torch.channels_last) and got.dtype == torch.float32
+    max_abs, rel = o.parity_metrics(got.cpu().numpy(), want)
+    assert max_abs <= MAX_ABS and rel <= REL_L2, (case, mode, max_abs, rel)
+
+
+def test_stem_conv_needs_16_byte_rows_else_the_direct_kernel_runs(ops):
+    """The stem kernel fetches its input windows with TMA, which wants 16-byte aligned image rows
+    (W * 6 bytes): other widths are refused when forced and take the direct kernel automatically."""
+    b, h, w, oc = 5, 37, 45, 64
+    rng = np.random.default_rng(8)
+    cw = make_weight(oc, 147, 8, seed=3, std=(2.0 / 147) ** 0.5, cb_dtype="bf16")
+    x = bf16_round(rng.standard_normal((b, 3, h, w)).astype(np.float32))
+    want = _conv_oracle(x, cw, 8, (oc, 3, 7, 7), None, 2, 3, 1)
+    x_cl = _cuda(x, torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    args = (_cuda(cw["packed"]), _cuda(cw["codebooks"], torch.bfloat16), None, (oc, 3, 7, 7), (2, 2), (3, 3), (1, 1), 1)
+    with pytest.raises(RuntimeError):
+        ops.dimq_conv2d_wq(x_cl, *args, bits=8, algo="expand")
+    got = ops.dimq_conv2d_wq(x_cl, *args, bits=8)
+    max_abs, rel = o.parity_metrics(got.cpu().numpy(), want)
+    assert max_abs <= MAX_ABS and rel <= REL_L2 and ops.last_device_status() == 0
+
+
+def test_stem_conv_auto_relu_bf16_out_and_nonfinite_neighbours(ops):
+    """Automatic choice at the ResNet stem's size with bias + ReLU and bf16 output; and an infinite pixel
+    must poison only the outputs whose 7x7 window contains it (the patch rows carry one extra pixel per
+    kernel row, which is cleared)."""
+    from dimq_b200 import _lib
+
+    b, h, w, oc = 4, 224, 224, 64
+    rng = np.random.default_rng(5)
+    cw = make_weight(oc, 147, 8, seed=1, std=(2.0 / 147) ** 0.5, cb_dtype="bf16")
+    x = bf16_round(rng.standard_normal((b, 3, h, w)).astype(np.float32))
+    bias = rng.standard_normal(oc).astype(np.float32)
+    want = np.maximum(_conv_oracle(x, cw, 8, (oc, 3, 7, 7), bias, 2, 3, 1), 0)
+    x_cl = _cuda(x, torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    args = (_cuda(cw["packed"]), _cuda(cw["codebooks"], torch.bfloat16), _cuda(bias), (oc, 3, 7, 7), (2, 2), (3, 3), (1, 1), 1)
+    before = _lib.LAUNCH_COUNT[0]
+    got = ops.dimq_conv2d_wq(x_cl, *args, bits=8, out_dtype=torch.bfloat16, epilogue="relu")
+    assert _lib.LAUNCH_COUNT[0] - before == 2          # weight expansion + stem kernel
+    max_abs, rel = o.parity_metrics(got.float().cpu().numpy(), want)
+    assert max_abs <= MAX_ABS_16 and rel <= REL_L2_16, (max_abs, rel)
+    x_inf = x_cl.clone()
+    x_inf[1, 0, 100, 101] = float("inf")                # input pixel (100, 101) of image 1
+    got_inf = ops.dimq_conv2d_wq(x_inf, *args, bits=8).cpu()
+    bad = ~torch.isfinite(got_inf)
+    rows = [oh for oh in range(112) if 0 <= 100 - (2 * oh - 3) < 7]
+    cols = [ow for ow in range(112) if 0 <= 101 - (2 * ow - 3) < 7]
+    expect = torch.zeros_like(bad)
+    expect[1, :, rows[0]:rows[-1] + 1, cols[0]:cols[-1] + 1] = True
+    assert not (bad & ~expect).any()                    # nothing outside the windows that contain the pixel
+    assert ops.last_device_status() == 0

@@ -132,3 +132,16 @@ def test_gather_logits_two_gloo_ranks(tmp_path):
     outs = [p.communicate(timeout=120)[0] for p in procs]
     assert all(p.returncode == 0 for p in procs), outs
     assert all("ok" in o for o in outs)
+
+
+def test_default_build_has_no_diagnostics(lib):
+    """The shipped library neither reads diagnostic switches from the environment nor takes a device
+    pointer from it: the counters and role-skipping switches exist only in the -DDIMQ_B200_DIAG build."""
+    from dimq_b200 import _lib
+
+    assert not hasattr(lib, "dimq_diag_configure")
+    blob = _lib.LIB_PATH.read_bytes()
+    for name in (b"DIMQ_B200_PROFILE_PTR", b"DIMQ_B200_TC_DEBUG", b"DIMQ_B200_TC_REP"):
+        assert name not in blob, name
+    sources = "".join(p.read_text() for p in (ROOT / "dimq_b200" / "csrc").iterdir())
+    assert sources.count("getenv(") == 1 and 'getenv("DIMQ_B200_TC_EPI")' in sources
