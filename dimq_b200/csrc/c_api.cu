@@ -56,6 +56,15 @@ using namespace dimq;
 
 #ifdef DIMQ_B200_DIAG
 namespace dimq { void diag_configure(int dbg, int rep, unsigned long long* prof, int64_t prof_words); }
+namespace dimq { void dense_diag_configure(int mode); void stem_diag_prof(unsigned long long* prof); }
+extern "C" __attribute__((visibility("default"))) int dimq_diag_stem_prof(void* prof) {
+  stem_diag_prof(static_cast<unsigned long long*>(prof));
+  return DIMQ_OK;
+}
+extern "C" __attribute__((visibility("default"))) int dimq_diag_dense(int mode) {
+  dense_diag_configure(mode);
+  return DIMQ_OK;
+}
 // Diagnostics build only (not declared in the public header).
 extern "C" __attribute__((visibility("default"))) int dimq_diag_configure(int dbg, int rep, void* prof, int64_t prof_words) {
   diag_configure(dbg, rep, static_cast<unsigned long long*>(prof), prof_words);

@@ -53,6 +53,7 @@ int scratch_address(unsigned char** out) {
 }  // namespace
 
 bool conv_tc_supported(const void* x, int x_dtype, const dimq_wq_weight* w, const dimq_conv_geom* g, int y_dtype);
+int check_wq_weight(const dimq_wq_weight* w, int64_t out_rows);
 
 }  // namespace dimq
 
@@ -68,6 +69,13 @@ extern "C" int dimq_conv2d_wq_static(const void* x, int x_dtype, const dimq_wq_w
   int rc = dimq_conv_out_size(&g);
   if (rc != DIMQ_OK) return rc;
   if (g.out_h != geom->out_h || g.out_w != geom->out_w) return DIMQ_ERR_BAD_SHAPE;
+  // every argument check dimq_conv2d_wq would make comes first, so that a negative return code means
+  // that nothing was launched and the shared array was not touched
+  if (!valid_dtype(x_dtype) || !valid_dtype(y_dtype)) return DIMQ_ERR_BAD_DTYPE;
+  if (bias != nullptr && !valid_dtype(bias_dtype)) return DIMQ_ERR_BAD_DTYPE;
+  if (epilogue < DIMQ_EPI_NONE || epilogue > DIMQ_EPI_ADD_RELU) return DIMQ_ERR_UNSUPPORTED;
+  rc = check_wq_weight(w, g.out_channels);
+  if (rc != DIMQ_OK) return rc;
   const int64_t numel = static_cast<int64_t>(g.out_channels) * g.in_channels_per_group * g.kernel_h * g.kernel_w;
   const int64_t bytes = (numel * w->bits + 7) / 8;
   if (bytes > static_cast<int64_t>(kStaticScratchBytes)) return DIMQ_ERR_SCRATCH_TOO_SMALL;

@@ -63,7 +63,17 @@ struct DenseParams {
   int tw, th, tb, tiles_w, tiles_h;
   int OW, OH, Bn;
   int stride, pad_h, pad_w, dil_h, dil_w, KW, c_blocks;
+#ifdef DIMQ_B200_DIAG
+  int diag;
+#endif
 };
+
+#ifdef DIMQ_B200_DIAG
+// diagnostics build: 1 = the producer skips the weight-tile copies, 2 = skips the activation-tile copies
+// (timing experiments: results are wrong)
+static int g_dense_diag = 0;
+static unsigned long long* g_stem_prof = nullptr;
+#endif
 
 struct DenseMaps {
   CUtensorMap a[4];   // activations; conv: one map per (row, column) parity of a stride-2 input
@@ -126,24 +136,58 @@ __device__ __forceinline__ void finish_row(float (&v)[32], const float* __restri
   }
 }
 
-template <bool RES>
-__device__ __forceinline__ void finish_row_epi(float (&v)[32], const float* bias_s, const float (&res)[32], int epilogue) {
-  switch (epilogue) {
-    case DIMQ_EPI_RELU: finish_row<DIMQ_EPI_RELU, RES>(v, bias_s, res); break;
-    case DIMQ_EPI_GELU: finish_row<DIMQ_EPI_GELU, RES>(v, bias_s, res); break;
-    case kEpiGelu16: finish_row<kEpiGelu16, RES>(v, bias_s, res); break;
-    case DIMQ_EPI_ADD_RELU: finish_row<DIMQ_EPI_ADD_RELU, RES>(v, bias_s, res); break;
-    default: finish_row<DIMQ_EPI_NONE, RES>(v, bias_s, res); break;
+// The same with the activation chosen at run time (warp-uniform).  Plain compares in order of
+// frequency, not a switch: the jump table of a switch cost the epilogue 240 cycles per call.  For
+// 16-bit outputs a ReLU that comes last is left to the conversion (cvt.rn.relu): returns true then.
+template <int ES, bool RES>
+__device__ __forceinline__ bool finish_row_epi(float (&v)[32], const float* bias_s, const float (&res)[32], int epilogue) {
+  const bool relu_last = epilogue == DIMQ_EPI_ADD_RELU || (epilogue == DIMQ_EPI_RELU && !RES);
+  if (epilogue == DIMQ_EPI_NONE || (ES == 2 && relu_last)) {
+    finish_row<DIMQ_EPI_NONE, RES>(v, bias_s, res);
+    return ES == 2 && relu_last;
+  }
+  if (epilogue == DIMQ_EPI_RELU) finish_row<DIMQ_EPI_RELU, RES>(v, bias_s, res);
+  else if (epilogue == DIMQ_EPI_ADD_RELU) finish_row<DIMQ_EPI_ADD_RELU, RES>(v, bias_s, res);
+  else if (ES == 2) finish_row<kEpiGelu16, RES>(v, bias_s, res);
+  else finish_row<DIMQ_EPI_GELU, RES>(v, bias_s, res);
+  return false;
+}
+
+// two floats -> one packed pair of 16-bit numbers (lo in the low half), optionally clamped at zero
+template <bool BF16, bool RELU>
+__device__ __forceinline__ uint32_t cvt_pair16(float lo, float hi) {
+  uint32_t d;
+  if (BF16) {
+    if (RELU) asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    else asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  } else {
+    if (RELU) asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  }
+  return d;
+}
+
+// 32 values of one row as 16-bit numbers into a [32 rows][64 bytes] staging tile with the 64-byte swizzle
+// (16-byte piece j of row r sits at piece j ^ ((r >> 1) & 3) = j ^ sw).
+template <bool BF16, bool RELU>
+__device__ __forceinline__ void stage_row16(const float (&v)[32], unsigned char* row_ptr, int sw) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = cvt_pair16<BF16, RELU>(v[8 * j + 2 * i], v[8 * j + 2 * i + 1]);
+    *reinterpret_cast<uint4*>(row_ptr + ((j ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
 
-__device__ __forceinline__ uint32_t pack16(float lo, float hi, int y_dtype) {
+__device__ __forceinline__ void stage_row16_any(const float (&v)[32], unsigned char* row_ptr, int sw, int y_dtype, bool relu) {
   if (y_dtype == DIMQ_BF16) {
-    const __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<const uint32_t*>(&t);
+    if (relu) stage_row16<true, true>(v, row_ptr, sw);
+    else stage_row16<true, false>(v, row_ptr, sw);
+  } else {
+    if (relu) stage_row16<false, true>(v, row_ptr, sw);
+    else stage_row16<false, false>(v, row_ptr, sw);
   }
-  const __half2 t = __floats2half2_rn(lo, hi);
-  return *reinterpret_cast<const uint32_t*>(&t);
 }
 
 // 32 residual values of one row: `p` points at the first of them (16-byte aligned), `valid` of them exist
@@ -183,7 +227,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // [stages: A 16 KB | B bn*128 B (all 1024-aligned)] [header] [bias slices] [staging tiles]
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // rounded up to 1024 bytes in the shared window; plain pointer arithmetic on the array keeps the
+  // accesses below in the shared state space (no generic loads and stores)
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const uint32_t stage_bytes = kABytes + p.b_bytes;
   const uint32_t n_st = static_cast<uint32_t>(p.stages);
   DenseHeader* hdr = reinterpret_cast<DenseHeader*>(smem + n_st * stage_bytes);
@@ -236,6 +282,15 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
           const uint32_t dst_b = dst_a + kABytes;
           const int kcol_b = (pass * p.k_blocks + kb) * kBK;
           if (!p.conv) {
+#ifdef DIMQ_B200_DIAG
+            if (p.diag != 0) {
+              if (elect_one()) {
+                mbar_arrive_expect_tx(full, p.diag == 1 ? kABytes : p.b_bytes);
+                if (p.diag == 1) tma_load_2d(dst_a, &maps.a[0], full, kb * kBK, m_blk * kBM);
+                else tma_load_2d(dst_b, &maps.b, full, kcol_b, n_blk * p.bn);
+              }
+            } else
+#endif
             if (elect_one()) {
               mbar_arrive_expect_tx(full, stage_bytes);
               tma_load_2d(dst_a, &maps.a[0], full, kb * kBK, m_blk * kBM);
@@ -340,6 +395,14 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
         c2 = ((m_blk / p.tiles_w) % p.tiles_h) * p.th + (p0 / p.tw) % p.th;
         c3 = (m_blk / (p.tiles_w * p.tiles_h)) * p.tb + p0 / (p.tw * p.th);
       }
+      // bias slices of this warp's chunks (at most four), one feature per lane, fetched before the wait for
+      // the accumulator so that the global-memory latency is off the critical path
+      float bj[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int64_t nb = static_cast<int64_t>(n_blk) * p.bn + (sub + 2 * i) * 32 + lane;
+        bj[i] = (p.bias != nullptr && sub + 2 * i < n_chunks && nb < p.N) ? load_as_float(p.bias, p.bias_dtype, nb) : 0.0f;
+      }
       // tcgen05.ld is warp-collective: the whole warp proceeds or the whole warp gives up
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->d_full[as]), aph, abort_flag, 0x1500u | as))) { ok = false; break; }
       tc_fence_after();
@@ -354,9 +417,10 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
         uint32_t r[32];
         __syncwarp();
         tmem_ld32(d_tmem + c * 32, r);
-        // bias slice of this chunk, one feature per lane, while the load is in flight
-        const float bj = (p.bias != nullptr && n_first + lane < p.N) ? load_as_float(p.bias, p.bias_dtype, n_first + lane) : 0.0f;
-        my_bias[lane] = bj;
+        {
+          const int i = (c - sub) >> 1;
+          my_bias[lane] = i == 0 ? bj[0] : i == 1 ? bj[1] : i == 2 ? bj[2] : bj[3];
+        }
         tmem_ld_wait();
         if (c + 2 >= n_chunks) {
           // every column this warp reads of the buffer is in registers: hand it back to the MMA warp
@@ -372,6 +436,7 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
         float res[32];
         const int64_t left = p.N - n_first;
         const int valid = left >= 32 ? 32 : static_cast<int>(left);
+        bool relu_cvt;
         if (p.residual != nullptr) {
           if (row_off >= 0)
             load_residual<ES>(static_cast<const char*>(p.residual) + (row_off + n_first) * ES, p.y_dtype, valid, res);
@@ -379,26 +444,16 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
 #pragma unroll
             for (int j = 0; j < 32; ++j) res[j] = 0.0f;
           }
-          finish_row_epi<true>(v, my_bias, res, (p.epilogue == DIMQ_EPI_GELU && ES == 2) ? kEpiGelu16 : p.epilogue);
+          relu_cvt = finish_row_epi<ES, true>(v, my_bias, res, p.epilogue);
         } else {
-          finish_row_epi<false>(v, my_bias, res, (p.epilogue == DIMQ_EPI_GELU && ES == 2) ? kEpiGelu16 : p.epilogue);
+          relu_cvt = finish_row_epi<ES, false>(v, my_bias, res, p.epilogue);
         }
         // the previous store of this warp must have finished reading the staging tile
         if (elect_one()) tma_store_wait_read();
         __syncwarp();
         if (ES == 2) {
           // [32 rows][64 bytes], 64-byte swizzle: 16-byte piece j of row r sits at piece j ^ ((r >> 1) & 3)
-          unsigned char* row_ptr = my_out + lane * 64;
-          const int sw = (lane >> 1) & 3;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint4 q;
-            q.x = pack16(v[8 * j], v[8 * j + 1], p.y_dtype);
-            q.y = pack16(v[8 * j + 2], v[8 * j + 3], p.y_dtype);
-            q.z = pack16(v[8 * j + 4], v[8 * j + 5], p.y_dtype);
-            q.w = pack16(v[8 * j + 6], v[8 * j + 7], p.y_dtype);
-            *reinterpret_cast<uint4*>(row_ptr + ((j ^ sw) << 4)) = q;
-          }
+          stage_row16_any(v, my_out + lane * 64, (lane >> 1) & 3, p.y_dtype, relu_cvt);
         } else {
           // [32 rows][128 bytes], 128-byte swizzle: piece j of row r sits at piece j ^ (r & 7)
           unsigned char* row_ptr = my_out + lane * 128;
@@ -560,6 +615,9 @@ int launch_dense(DenseMaps& maps, DenseParams& p, const void* scratch, int64_t K
   p.epilogue = epilogue;
   p.k_blocks = static_cast<int>(K / kBK);
   p.b_bytes = static_cast<uint32_t>(p.bn) * kBK * 2;
+#ifdef DIMQ_B200_DIAG
+  p.diag = g_dense_diag;
+#endif
   const int fmt = x_dtype == DIMQ_BF16 ? 1 : 0;
   p.idesc = tc::make_idesc_f16(fmt, fmt, kBM, p.bn);
   const cuuint64_t bdims[2] = {static_cast<cuuint64_t>(K * p.passes), static_cast<cuuint64_t>(p.N)};
@@ -613,6 +671,10 @@ int passes_for(int x_dtype, const dimq_wq_weight* w) { return (x_dtype == DIMQ_B
 }  // namespace
 
 int read_dense_status(uint32_t* status) { return tc::read_and_clear_device_status(status); }
+#ifdef DIMQ_B200_DIAG
+void dense_diag_configure(int mode) { g_dense_diag = mode; }
+void stem_diag_prof(unsigned long long* prof) { g_stem_prof = prof; }   // 16 words per SM, or null
+#endif
 
 // ---- GEMM ----------------------------------------------------------------------------------------
 
@@ -680,8 +742,10 @@ int launch_linear_wq_dense(const void* x, int x_dtype, const dimq_wq_weight* w, 
 // of a 16 x 8 output tile (NHWC, 6 bytes per pixel) is copied into shared memory, builder warps cut it into
 // the 128 patch rows of the A operand (K-major, 128-byte swizzle) and the MMA warp multiplies them with the
 // expanded weight, which stays resident in shared memory for the whole kernel.
-//   k = kh * 24 + kw * 3 + c   (kw * 3 + c < KW * 3 <= 24, kh < KH <= 8; the rest of the 192 columns is zero)
-// so the 24 values of one kernel row of a patch are 24 consecutive input elements.
+//   k = kh * 24 + lead + kw * 3 + c   (lead = pad_w & 1, lead + KW * 3 <= 24, kh < KH <= 8; the rest of the
+//   192 columns is zero)
+// so the 24 slots of one kernel row of a patch are 24 consecutive input elements, and the lead slot makes
+// that run start on a 4-byte boundary of the window whatever the padding.
 // Warp roles (448 threads): warps 0-7 build A tiles (double-buffered), warp 8 issues the MMAs, warps 9-12 are
 // the epilogue (bias / activation / residual, swizzled staging, one TMA store per 32 pixels x 32 channels),
 // warp 13 fetches the input windows (one TMA box per tile, zero fill outside the image).
@@ -700,6 +764,7 @@ constexpr int kStemWinPitch = 144;
 constexpr uint32_t kStemABytes = kBM * kStemK * 2;           // 48 KB per A buffer
 constexpr uint32_t kStemWinBytes = kStemWinRows * kStemWinPitch * 2;   // 6336: what one TMA box delivers
 constexpr uint32_t kStemWinStride = (kStemWinBytes + 127u) & ~127u;      // a TMA box must land on a 128-byte boundary
+constexpr int kStemWinBufs = 6;   // window ring (2..6 slots, as shared memory allows): the copies run several tiles ahead of the patch cutting (TMA latency)
 
 struct StemParams {
   const void* x;            // NHWC 16-bit input, 3 channels
@@ -712,6 +777,12 @@ struct StemParams {
   int KH, KW, pad_h, pad_w;
   int tiles_w, tiles_h, m_tiles;
   int passes;
+  int win_bufs;             // slots of the window ring in use
+  int lead;                 // pad_w & 1: patch rows start one element early so that they are word-aligned in the window
+#ifdef DIMQ_B200_DIAG
+  int diag;                 // timing experiments (results are wrong): 4 = no patch cutting, 8 = no MMAs, 16 = no output stores, 32 = no window copies
+  unsigned long long* prof; // 16 cycle counters per CTA, or null
+#endif
   uint32_t b_bytes;         // N * 384 * passes
   uint32_t idesc;
   int epilogue;
@@ -724,21 +795,35 @@ struct StemMaps {
 };
 
 struct StemHeader {
-  uint64_t a_full[2], a_empty[2], d_full[2], d_empty[2], b_full, win_full[2], win_empty[2];
+  uint64_t a_full[2], a_empty[2], d_full[2], d_empty[2], b_full, win_full[kStemWinBufs], win_empty[kStemWinBufs];
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
 };
+
+#ifdef DIMQ_B200_DIAG
+#define STEM_CLK(v) const long long v = clock64()
+#define STEM_ACC(slot, since) do { if (p.prof != nullptr && lane == 0) acc_[slot] += static_cast<unsigned long long>(clock64() - (since)); } while (0)
+#define STEM_ACC_DECL unsigned long long acc_[8] = {0ull, 0ull, 0ull, 0ull, 0ull, 0ull, 0ull, 0ull}
+#define STEM_FLUSH(first, n) do { if (p.prof != nullptr && lane == 0) for (int q_ = 0; q_ < (n); ++q_) p.prof[blockIdx.x * 32 + (first) + q_] = acc_[q_]; } while (0)
+#else
+#define STEM_CLK(v)
+#define STEM_ACC(slot, since)
+#define STEM_ACC_DECL
+#define STEM_FLUSH(first, n)
+#endif
 
 template <int ES>
 __global__ void __launch_bounds__(kStemThreads, 1)
 lut_stem_conv_kernel(const __grid_constant__ StemMaps maps, const StemParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  // [A0 | A1 (48 KB each)] [B: passes x 3 k blocks of N x 128 B] [header] [bias slices] [staging] [windows]
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // [A0 | A1 (48 KB each)] [B: passes x 3 k blocks of N x 128 B] [header] [bias, one copy per epilogue warp] [staging] [windows]
+  // rounded up to 1024 bytes in the shared window; plain pointer arithmetic on the array keeps the
+  // accesses below in the shared state space (no generic loads and stores)
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* b_tile = smem + 2 * kStemABytes;
   StemHeader* hdr = reinterpret_cast<StemHeader*>(b_tile + p.b_bytes);
   float* bias_area = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(hdr) + kHeaderBytes);
-  unsigned char* staging = reinterpret_cast<unsigned char*>(bias_area) + 1024;   // 1024-aligned
+  unsigned char* staging = reinterpret_cast<unsigned char*>(bias_area) + 2048;   // 1024-aligned
   constexpr uint32_t kStagingBytes = 32u * 32u * ES;
   unsigned char* windows = staging + 4 * kStagingBytes;
 
@@ -752,6 +837,8 @@ lut_stem_conv_kernel(const __grid_constant__ StemMaps maps, const StemParams p) 
       mbar_init(smem_u32(&hdr->a_empty[s]), 1);
       mbar_init(smem_u32(&hdr->d_full[s]), 1);
       mbar_init(smem_u32(&hdr->d_empty[s]), 4);
+    }
+    for (int s = 0; s < kStemWinBufs; ++s) {
       mbar_init(smem_u32(&hdr->win_full[s]), 1);
       mbar_init(smem_u32(&hdr->win_empty[s]), kStemBuilders);
     }
@@ -775,11 +862,25 @@ lut_stem_conv_kernel(const __grid_constant__ StemMaps maps, const StemParams p) 
   const uint32_t tmem_base = hdr->tmem_base;
   volatile uint32_t* abort_flag = &hdr->abort_flag;
 
-  auto tile_origin = [&](int t, int& b, int& oh0, int& ow0) {
-    ow0 = (t % p.tiles_w) * kStemTW;
-    oh0 = ((t / p.tiles_w) % p.tiles_h) * kStemTH;
-    b = t / (p.tiles_w * p.tiles_h);
+  // Tile t = (image b, tile row, tile column); a CTA walks t = blockIdx.x, + gridDim.x, ... and keeps the three
+  // indices by carrying instead of dividing.
+  struct TileWalk {
+    int tw, th, b, d_w, d_h, d_b, tiles_w, tiles_h;
+    __device__ __forceinline__ void start(int t, int step, int tiles_w_, int tiles_h_) {
+      tiles_w = tiles_w_; tiles_h = tiles_h_;
+      tw = t % tiles_w; th = (t / tiles_w) % tiles_h; b = t / (tiles_w * tiles_h);
+      d_w = step % tiles_w; d_h = (step / tiles_w) % tiles_h; d_b = step / (tiles_w * tiles_h);
+    }
+    __device__ __forceinline__ void next() {
+      tw += d_w;
+      th += d_h;
+      if (tw >= tiles_w) { tw -= tiles_w; ++th; }
+      b += d_b;
+      if (th >= tiles_h) { th -= tiles_h; ++b; }
+    }
   };
+  TileWalk walk;
+  walk.start(blockIdx.x, gridDim.x, p.tiles_w, p.tiles_h);
 
   if (warp == kStemBuilders + 5) {
     // ===================== window producer =====================
@@ -787,12 +888,26 @@ lut_stem_conv_kernel(const __grid_constant__ StemMaps maps, const StemParams p) 
     // before pixel 2 ow0 - pad_w; rows and elements outside the image arrive as zeros.
     uint32_t buf = 0, phase = 0;
     bool ok = true;
+    STEM_ACC_DECL;
+    STEM_CLK(t_all);
     for (int t = blockIdx.x; t < p.m_tiles && ok; t += gridDim.x) {
-      int b, oh0, ow0;
-      tile_origin(t, b, oh0, ow0);
+      const int b = walk.b, oh0 = walk.th * kStemTH, ow0 = walk.tw * kStemTW;
+      walk.next();
+      STEM_CLK(t_w);
+#ifdef DIMQ_B200_DIAG
+      if (p.diag & 64) {
+        if (!__all_sync(0xFFFFFFFFu, mbar_wait_relaxed(smem_u32(&hdr->win_empty[buf]), phase ^ 1u, abort_flag, 0x2600u | buf))) { ok = false; break; }
+      } else
+#endif
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->win_empty[buf]), phase ^ 1u, abort_flag, 0x2600u | buf))) { ok = false; break; }
+      STEM_ACC(1, t_w);
       const int e0 = (2 * ow0 - p.pad_w) * 3;
       const int x_al = e0 & ~7;                      // round down to 8 elements (also right for negatives)
+#ifdef DIMQ_B200_DIAG
+      if (p.diag & 32) {
+        if (elect_one()) mbar_arrive(smem_u32(&hdr->win_full[buf]));
+      } else
+#endif
       if (elect_one()) {
         const uint32_t full = smem_u32(&hdr->win_full[buf]);
         mbar_arrive_expect_tx(full, kStemWinBytes);
@@ -803,64 +918,82 @@ lut_stem_conv_kernel(const __grid_constant__ StemMaps maps, const StemParams p) 
             : "memory");
       }
       __syncwarp();
-      if (++buf == 2) { buf = 0; phase ^= 1u; }
+      if (++buf == static_cast<uint32_t>(p.win_bufs)) { buf = 0; phase ^= 1u; }
     }
+    STEM_ACC(0, t_all);
+    STEM_FLUSH(14, 2);
     if (!ok && lane == 0) {   // gave up: let the copy still in flight land before the CTA exits
-      for (int s2 = 0; s2 < 2; ++s2)
+      for (int s2 = 0; s2 < p.win_bufs; ++s2)
         for (uint32_t it = 0; it < kSpinLimit; ++it)
           if (mbar_try_wait(smem_u32(&hdr->win_full[s2]), 0u) || mbar_try_wait(smem_u32(&hdr->win_full[s2]), 1u)) break;
     }
     __syncwarp();
   } else if (warp < kStemBuilders) {
     // ===================== patch builders =====================
-    uint32_t buf = 0, phase = 0;
+    uint32_t buf = 0, phase = 0, wbuf = 0, wphase = 0;   // A buffer / window ring positions
     bool ok = true;
-    const int n_chunks = p.KH * 3;                   // 16-byte pieces of a patch row that carry data
-    const int row_elems = p.KW * 3;                  // values of one kernel row
+    // Thread -> (patch row, kernel rows of one parity).  The 24 slots of kernel row kh are the window
+    // elements from one before pixel 2 ow - pad_w (pad_w odd) or from that pixel (pad_w even): a word-aligned
+    // run of 12 words, so a piece is four plain 32-bit loads.  Slots outside the KW * 3 values belong to
+    // neighbouring pixels: their weights are zero, but a non-finite value there must not reach the product,
+    // so they are cleared with masks computed once.
+    const int row = tid & (kBM - 1), half = tid >> 7;
+    const int oh_l = row >> 4, ow_l = row & 15;
+    uint32_t mask[12];
+#pragma unroll
+    for (int m = 0; m < 12; ++m) {
+      const int s0 = 2 * m - p.lead, s1 = 2 * m + 1 - p.lead;
+      mask[m] = ((s0 >= 0 && s0 < p.KW * 3) ? 0x0000FFFFu : 0u) | ((s1 >= 0 && s1 < p.KW * 3) ? 0xFFFF0000u : 0u);
+    }
+    STEM_ACC_DECL;
+    STEM_CLK(t_all);
     for (int t = blockIdx.x; t < p.m_tiles && ok; t += gridDim.x) {
-      int b, oh0, ow0;
-      tile_origin(t, b, oh0, ow0);
-      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->win_full[buf]), phase, abort_flag, 0x2700u | buf))) { ok = false; break; }
+      const int ow0 = walk.tw * kStemTW;
+      walk.next();
+      STEM_CLK(t_w1);
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->win_full[wbuf]), wphase, abort_flag, 0x2700u | wbuf))) { ok = false; break; }
+      STEM_ACC(1, t_w1);
+      STEM_CLK(t_w2);
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->a_empty[buf]), phase ^ 1u, abort_flag, 0x2100u | buf))) { ok = false; break; }
-      // patch rows: piece (row, chunk) = 8 consecutive elements of kernel row chunk / 3.  The patch of
-      // output column j starts at window element off + 6 j, off = distance of pixel 2 ow0 - pad_w from
-      // the box start; when off is odd the eight elements straddle five words and are funnel-shifted
+      STEM_ACC(2, t_w2);
+      STEM_CLK(t_cut);
       const int e0 = (2 * ow0 - p.pad_w) * 3;
-      const int off = e0 - (e0 & ~7);
-      const uint32_t sh = (off & 1) ? 16u : 0u;
-      unsigned char* a_tile = smem + buf * kStemABytes;
-      const uint32_t* win32 = reinterpret_cast<const uint32_t*>(windows + buf * kStemWinStride);
-      for (int i = tid; i < kBM * n_chunks; i += kStemBuilders * 32) {
-        const int row = i & (kBM - 1), chunk = i >> 7;
-        const int kh = chunk / 3, part = chunk - kh * 3;
-        const int oh_l = row >> 4, ow_l = row & 15;
-        const uint32_t* src = win32 + (2 * oh_l + kh) * (kStemWinPitch / 2) + ((off + 6 * ow_l + 8 * part) >> 1);
-        uint32_t w5[5];
+      const int off = e0 - (e0 & ~7);                  // distance of the first pixel from the box start; off - lead is even
+      unsigned char* a_tile = smem + buf * kStemABytes + row * 128;
+      const uint32_t* win32 = reinterpret_cast<const uint32_t*>(windows + wbuf * kStemWinStride) +
+                              2 * oh_l * (kStemWinPitch / 2) + ((off - p.lead) >> 1) + 3 * ow_l;
+#ifdef DIMQ_B200_DIAG
+      if (!(p.diag & 4))
+#endif
+      for (int kh = half; kh < p.KH; kh += 2) {
+        const uint32_t* src = win32 + kh * (kStemWinPitch / 2);
+        uint32_t w12[12];
 #pragma unroll
-        for (int m = 0; m < 5; ++m) w5[m] = src[m];   // the fifth word may belong to the next row: it is shifted out when sh == 0
-        uint32_t q4[4];
+        for (int m = 0; m < 12; ++m) w12[m] = src[m] & mask[m];
 #pragma unroll
-        for (int m = 0; m < 4; ++m) q4[m] = __funnelshift_r(w5[m], w5[m + 1], sh);
-        // elements past the kernel row's KW * 3 values belong to the next pixel: their weights are zero,
-        // but a non-finite value there must not reach the product, so they are cleared
-        const int valid = row_elems - 8 * part;
-#pragma unroll
-        for (int m = 0; m < 4; ++m) {
-          if (valid <= 2 * m) q4[m] = 0u;
-          else if (valid == 2 * m + 1) q4[m] &= 0xFFFFu;
+        for (int part = 0; part < 3; ++part) {
+          const int chunk = kh * 3 + part;
+          *reinterpret_cast<uint4*>(a_tile + (chunk >> 3) * (kBM * 128) + (((chunk & 7) ^ (row & 7)) << 4)) =
+              make_uint4(w12[4 * part], w12[4 * part + 1], w12[4 * part + 2], w12[4 * part + 3]);
         }
-        const uint4 q = make_uint4(q4[0], q4[1], q4[2], q4[3]);
-        const int kb = chunk >> 3, c = chunk & 7;
-        *reinterpret_cast<uint4*>(a_tile + kb * (kBM * 128) + row * 128 + ((c ^ (row & 7)) << 4)) = q;
       }
+      STEM_ACC(3, t_cut);
+      STEM_CLK(t_fence);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(smem_u32(&hdr->a_full[buf]));
-        mbar_arrive(smem_u32(&hdr->win_empty[buf]));
+        mbar_arrive(smem_u32(&hdr->win_empty[wbuf]));
       }
+      STEM_ACC(4, t_fence);
       if (++buf == 2) { buf = 0; phase ^= 1u; }
+      if (++wbuf == static_cast<uint32_t>(p.win_bufs)) { wbuf = 0; wphase ^= 1u; }
     }
+    STEM_ACC(0, t_all);
+    if (warp == 0) STEM_FLUSH(0, 4);
+#ifdef DIMQ_B200_DIAG
+    if (warp == 0 && p.prof != nullptr && lane == 0) p.prof[blockIdx.x * 32 + 16] = acc_[4];
+#endif
   } else if (warp == kStemBuilders) {
     // ===================== MMA issuer =====================
     bool ok = true;
@@ -874,12 +1007,26 @@ lut_stem_conv_kernel(const __grid_constant__ StemMaps maps, const StemParams p) 
     uint32_t buf = 0, phase = 0, as = 0, aph = 0;
     const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem));
     const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(b_tile));
+    STEM_ACC_DECL;
+    STEM_CLK(t_all);
     for (int t = blockIdx.x; t < p.m_tiles && ok; t += gridDim.x) {
+      STEM_CLK(t_w1);
+#ifdef DIMQ_B200_DIAG
+      if (p.diag & 64) {
+        if (!__all_sync(0xFFFFFFFFu, mbar_wait_relaxed(smem_u32(&hdr->d_empty[as]), aph ^ 1u, abort_flag, 0x2300u | as))) { ok = false; break; }
+      } else
+#endif
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->d_empty[as]), aph ^ 1u, abort_flag, 0x2300u | as))) { ok = false; break; }
+      STEM_ACC(1, t_w1);
+      STEM_CLK(t_w2);
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->a_full[buf]), phase, abort_flag, 0x2400u | buf))) { ok = false; break; }
+      STEM_ACC(2, t_w2);
       tc_fence_after();
       if (elect_one()) {
         const uint32_t d_tmem = tmem_base + as * kAccCols;
+#ifdef DIMQ_B200_DIAG
+        if (!(p.diag & 8))
+#endif
         for (int kb = 0; kb < 3 * p.passes; ++kb) {
           const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((buf * kStemABytes + (kb % 3) * (kBM * 128)) >> 4);
           const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((kb * kb_bytes) >> 4);
@@ -895,44 +1042,55 @@ lut_stem_conv_kernel(const __grid_constant__ StemMaps maps, const StemParams p) 
       if (++buf == 2) { buf = 0; phase ^= 1u; }
       if (++as == kAccStages) { as = 0; aph ^= 1u; }
     }
+    STEM_ACC(0, t_all);
+    STEM_FLUSH(4, 3);
   } else {
     // ===================== epilogue =====================
     const int quarter = warp & 3;          // TMEM lanes [32 quarter, +32): tile rows 2 quarter, 2 quarter + 1
     const int ew = warp - (kStemBuilders + 1);
-    float* my_bias = bias_area + ew * 32;
+    float* my_bias = bias_area + ew * 128;   // all N <= 128 bias values, read from global memory once
     unsigned char* my_out = staging + ew * kStagingBytes;
     const int n_chunks = static_cast<int>((p.N + 31) / 32);
+    for (int j = lane; j < 128; j += 32) my_bias[j] = (p.bias != nullptr && j < p.N) ? load_as_float(p.bias, p.bias_dtype, j) : 0.0f;
+    __syncwarp();
     uint32_t as = 0, aph = 0;
     bool ok = true;
+    STEM_ACC_DECL;
+    STEM_CLK(t_all);
     for (int t = blockIdx.x; t < p.m_tiles && ok; t += gridDim.x) {
-      int b, oh0, ow0;
-      tile_origin(t, b, oh0, ow0);
+      const int b = walk.b, oh0 = walk.th * kStemTH, ow0 = walk.tw * kStemTW;
+      walk.next();
       const int pj = quarter * 32 + lane;
       const int oh = oh0 + (pj >> 4), ow = ow0 + (pj & 15);
       int64_t row_off = -1;
-      if (oh < p.OH && ow < p.OW) row_off = ((static_cast<int64_t>(b) * p.OH + oh) * p.OW + ow) * p.N;
+      if (p.residual != nullptr && oh < p.OH && ow < p.OW) row_off = ((static_cast<int64_t>(b) * p.OH + oh) * p.OW + ow) * p.N;
+      STEM_CLK(t_w1);
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->d_full[as]), aph, abort_flag, 0x2500u | as))) { ok = false; break; }
+      STEM_ACC(1, t_w1);
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * kAccCols;
       for (int c = 0; c < n_chunks; ++c) {
         const int64_t n_first = static_cast<int64_t>(c) * 32;
         uint32_t r[32];
         __syncwarp();
+        STEM_CLK(t_ld);
         tmem_ld32(d_tmem + c * 32, r);
-        my_bias[lane] = (p.bias != nullptr && n_first + lane < p.N) ? load_as_float(p.bias, p.bias_dtype, n_first + lane) : 0.0f;
         tmem_ld_wait();
+        STEM_ACC(7, t_ld);
         if (c + 1 == n_chunks) {
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&hdr->d_empty[as]));
         }
-        __syncwarp();
         float v[32], res[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
         const int64_t left = p.N - n_first;
         const int valid = left >= 32 ? 32 : static_cast<int>(left);
-        const int epi = (p.epilogue == DIMQ_EPI_GELU && ES == 2) ? kEpiGelu16 : p.epilogue;
+        bool relu_cvt = false;
+#ifdef DIMQ_B200_DIAG
+        if (!(p.diag & 128))
+#endif
         if (p.residual != nullptr) {
           if (row_off >= 0)
             load_residual<ES>(static_cast<const char*>(p.residual) + (row_off + n_first) * ES, p.y_dtype, valid, res);
@@ -940,24 +1098,18 @@ lut_stem_conv_kernel(const __grid_constant__ StemMaps maps, const StemParams p) 
 #pragma unroll
             for (int j = 0; j < 32; ++j) res[j] = 0.0f;
           }
-          finish_row_epi<true>(v, my_bias, res, epi);
+          relu_cvt = finish_row_epi<ES, true>(v, my_bias + c * 32, res, p.epilogue);
         } else {
-          finish_row_epi<false>(v, my_bias, res, epi);
+          relu_cvt = finish_row_epi<ES, false>(v, my_bias + c * 32, res, p.epilogue);
         }
+        STEM_ACC(2, t_ld);
+        STEM_CLK(t_rd);
         if (elect_one()) tma_store_wait_read();
         __syncwarp();
+        STEM_ACC(3, t_rd);
+        STEM_CLK(t_sts);
         if (ES == 2) {
-          unsigned char* row_ptr = my_out + lane * 64;
-          const int sw = (lane >> 1) & 3;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint4 q;
-            q.x = pack16(v[8 * j], v[8 * j + 1], p.y_dtype);
-            q.y = pack16(v[8 * j + 2], v[8 * j + 3], p.y_dtype);
-            q.z = pack16(v[8 * j + 4], v[8 * j + 5], p.y_dtype);
-            q.w = pack16(v[8 * j + 6], v[8 * j + 7], p.y_dtype);
-            *reinterpret_cast<uint4*>(row_ptr + ((j ^ sw) << 4)) = q;
-          }
+          stage_row16_any(v, my_out + lane * 64, (lane >> 1) & 3, p.y_dtype, relu_cvt);
         } else {
           unsigned char* row_ptr = my_out + lane * 128;
           const int sw = lane & 7;
@@ -965,15 +1117,29 @@ lut_stem_conv_kernel(const __grid_constant__ StemMaps maps, const StemParams p) 
           for (int j = 0; j < 8; ++j)
             *reinterpret_cast<float4*>(row_ptr + ((j ^ sw) << 4)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
         }
+        STEM_ACC(4, t_sts);
+        STEM_CLK(t_fence);
         fence_proxy_async_smem();
         __syncwarp();
+        STEM_ACC(5, t_fence);
+        STEM_CLK(t_issue);
+#ifdef DIMQ_B200_DIAG
+        if (!(p.diag & 16))
+#endif
         if (elect_one()) {
           tma_store_4d(&maps.y, smem_u32(my_out), static_cast<int>(n_first), ow0, oh0 + 2 * quarter, b);
           tma_store_commit();
         }
+        __syncwarp();
+        STEM_ACC(6, t_issue);
       }
       if (++as == kAccStages) { as = 0; aph ^= 1u; }
     }
+    STEM_ACC(0, t_all);
+    if (ew == 0) STEM_FLUSH(7, 7);
+#ifdef DIMQ_B200_DIAG
+    if (ew == 0 && p.prof != nullptr && lane == 0) p.prof[blockIdx.x * 32 + 17] = acc_[7];
+#endif
     __syncwarp();
     if (elect_one()) tma_store_wait_all();
     __syncwarp();
@@ -987,20 +1153,20 @@ lut_stem_conv_kernel(const __grid_constant__ StemMaps maps, const StemParams p) 
   }
 }
 
-// Expanded stem weight [N][192 * passes]: column kh * 24 + kw * 3 + c of row n is the codeword of
+// Expanded stem weight [N][192 * passes]: column kh * 24 + lead + kw * 3 + c of row n is the codeword of
 // idx[n][c][kh][kw] (the reference's "conv_kcrs" stream), zero elsewhere; lo terms in the second pass.
 __global__ void __launch_bounds__(256)
 stem_expand_kernel(const uint8_t* __restrict__ packed, int bits, int64_t nbytes, const void* __restrict__ codebooks,
-                   int cb_dtype, int entries, int64_t group_rows, int64_t N, int KH, int KW, int fmt, int passes,
-                   uint16_t* __restrict__ out) {
+                   int cb_dtype, int entries, int64_t group_rows, int64_t N, int KH, int KW, int lead, int fmt,
+                   int passes, uint16_t* __restrict__ out) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
   if (i >= N * kStemK) return;
   const int64_t n = i / kStemK;
   const int k = static_cast<int>(i - n * kStemK);
-  const int kh = k / kStemKRow, j = k - kh * kStemKRow;
+  const int kh = k / kStemKRow, j = k - kh * kStemKRow - lead;
   const int kw = j / 3, c = j - kw * 3;
   float v = 0.0f;
-  if (kh < KH && kw < KW) {
+  if (kh < KH && j >= 0 && kw < KW) {
     const uint32_t idx = get_index(packed, ((n * 3 + c) * KH + kh) * KW + kw, bits, nbytes);
     if (idx < static_cast<uint32_t>(entries)) v = load_as_float(codebooks, cb_dtype, (n / group_rows) * entries + idx);
   }
@@ -1024,7 +1190,7 @@ bool stem_conv_supported(const void* x, int x_dtype, const dimq_wq_weight* w, co
   if (y_dtype != x_dtype && y_dtype != DIMQ_F32) return false;
   if (g->groups != 1 || g->in_channels != 3) return false;
   if (g->stride_h != 2 || g->stride_w != 2 || g->dilation_h != 1 || g->dilation_w != 1) return false;
-  if (g->kernel_h > 8 || g->kernel_w * 3 > kStemKRow) return false;
+  if (g->kernel_h > 8 || g->kernel_w * 3 + (g->pad_w & 1) > kStemKRow) return false;   // one lead slot when pad_w is odd
   if (g->pad_h < 0 || g->pad_w < 0 || g->pad_h > 8 || g->pad_w > 8) return false;
   if (g->out_channels % 16 != 0 || g->out_channels > 128) return false;
   const int64_t W = g->in_w, H = g->in_h;
@@ -1064,6 +1230,7 @@ int launch_stem_conv(const void* x, int x_dtype, const dimq_wq_weight* w, const 
   p.N = g->out_channels;
   p.H = g->in_h; p.W = g->in_w; p.OH = g->out_h; p.OW = g->out_w; p.Bn = g->batch;
   p.KH = g->kernel_h; p.KW = g->kernel_w; p.pad_h = g->pad_h; p.pad_w = g->pad_w;
+  p.lead = g->pad_w & 1;
   p.tiles_w = (p.OW + kStemTW - 1) / kStemTW;
   p.tiles_h = (p.OH + kStemTH - 1) / kStemTH;
   const int64_t m_tiles = static_cast<int64_t>(p.tiles_w) * p.tiles_h * p.Bn;
@@ -1098,12 +1265,19 @@ int launch_stem_conv(const void* x, int x_dtype, const dimq_wq_weight* w, const 
   const int64_t total = p.N * kStemK;
   stem_expand_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(
       w->packed, w->bits, (n_w * w->bits + 7) / 8, w->codebooks, w->cb_dtype, w->entries, w->group_rows, p.N, p.KH, p.KW,
-      fmt, p.passes, static_cast<uint16_t*>(workspace));
+      p.lead, fmt, p.passes, static_cast<uint16_t*>(workspace));
   int rc = launch_status();
   if (rc != DIMQ_OK) return rc;
   const int es = y_dtype == DIMQ_F32 ? 4 : 2;
-  const size_t smem = 1024 + 2 * kStemABytes + p.b_bytes + kHeaderBytes + 1024 + 4 * 32 * 32 * es + 2 * kStemWinStride;
-  if (smem > kSmemMax) return DIMQ_ERR_UNSUPPORTED;
+#ifdef DIMQ_B200_DIAG
+  p.diag = g_dense_diag;
+  p.prof = g_stem_prof;
+#endif
+  const size_t smem_fixed = 1024 + 2 * kStemABytes + p.b_bytes + kHeaderBytes + 2048 + 4 * 32 * 32 * es;
+  if (smem_fixed + 2 * kStemWinStride > kSmemMax) return DIMQ_ERR_UNSUPPORTED;
+  p.win_bufs = static_cast<int>((kSmemMax - smem_fixed) / kStemWinStride);
+  if (p.win_bufs > kStemWinBufs) p.win_bufs = kStemWinBufs;
+  const size_t smem = smem_fixed + p.win_bufs * kStemWinStride;
   const int grid = p.m_tiles < kNumSMs ? p.m_tiles : kNumSMs;
   cudaError_t e;
   if (es == 2) {

@@ -385,7 +385,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 linear_wq_tc_kernel(const __grid_constant__ TmapSet tmaps, const TcParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // [x stages (1024-aligned)] [header] [tables]
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // rounded up to 1024 bytes in the shared window; plain pointer arithmetic on the array keeps the
+  // accesses below in the shared state space (no generic loads and stores)
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* x_stage = smem;
   const uint32_t n_xs = static_cast<uint32_t>(p.x_stages);
   SharedHeader* hdr = reinterpret_cast<SharedHeader*>(smem + n_xs * p.x_stage_bytes);
