@@ -17,8 +17,12 @@
 // Tile: 128 activation rows (UMMA M, one TMEM lane each) x up to 256 weight rows (UMMA N = 256 is the
 // shape whose four MMAs per 64-k block run at the tensor pipe's full rate: measured 589 cycles per
 // block, commit included, against 512 ideal; N = 192 needs 573 cycles for 3/4 of the work).
-// Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2-9 epilogue
-// (two per TMEM lane quarter, alternating 32-column chunks).  Persistent grid, one CTA per SM.
+// Warp roles (384 threads): warp 0 fetches the tiles (for convolutions only the activation tiles of the even
+// k blocks, warp 11 those of the odd ones and warp 10 the weight tiles: with one producer warp the issue of a
+// stage's two copies plus the tap arithmetic took 680 cycles per 64-k block and starved the MMA warp),
+// warp 1 MMA issuer + TMEM owner,
+// warps 2-9 epilogue (two per TMEM lane quarter, alternating 32-column chunks).  Persistent grid, one CTA
+// per SM.
 // The accumulator is y-oriented (lane = output row m, column = output feature n): an epilogue thread
 // holds 32 consecutive features of one row, adds bias / activation / residual, writes them as 16-byte
 // vectors into a swizzled staging tile and one TMA store per 32 x 32 chunk writes y.
@@ -38,7 +42,7 @@ constexpr int kAccStages = 2;
 constexpr int kAccCols = 256;    // TMEM columns per accumulator buffer
 constexpr int kTmemCols = 512;
 constexpr int kEpiWarps = 8;
-constexpr int kThreads = (2 + kEpiWarps) * 32;
+constexpr int kThreads = (2 + kEpiWarps + 2) * 32;   // activation producer, MMA issuer, epilogue warps, weight producer, second activation producer
 constexpr uint32_t kABytes = kBM * kBK * 2;   // 16 KB
 constexpr int kHeaderBytes = 1024;
 constexpr int kBiasBytes = kEpiWarps * 128;
@@ -65,6 +69,7 @@ struct DenseParams {
   int stride, pad_h, pad_w, dil_h, dil_w, KW, c_blocks;
 #ifdef DIMQ_B200_DIAG
   int diag;
+  unsigned long long* prof;   // 32 cycle counters per CTA, or null
 #endif
 };
 
@@ -80,6 +85,18 @@ struct DenseMaps {
   CUtensorMap b;      // expanded weights [N][passes * K]
   CUtensorMap y;      // output, boxes of 32 features x 32 rows / pixels
 };
+
+#ifdef DIMQ_B200_DIAG
+#define STEM_CLK(v) const long long v = clock64()
+#define STEM_ACC(slot, since) do { if (p.prof != nullptr && lane == 0) acc_[slot] += static_cast<unsigned long long>(clock64() - (since)); } while (0)
+#define STEM_ACC_DECL unsigned long long acc_[8] = {0ull, 0ull, 0ull, 0ull, 0ull, 0ull, 0ull, 0ull}
+#define STEM_FLUSH(first, n) do { if (p.prof != nullptr && lane == 0) for (int q_ = 0; q_ < (n); ++q_) p.prof[blockIdx.x * 32 + (first) + q_] = acc_[q_]; } while (0)
+#else
+#define STEM_CLK(v)
+#define STEM_ACC(slot, since)
+#define STEM_ACC_DECL
+#define STEM_FLUSH(first, n)
+#endif
 
 struct DenseHeader {
   uint64_t full[kMaxStages], empty[kMaxStages];
@@ -243,7 +260,7 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
   const int total_kb = p.k_blocks * p.passes;
 
   if (tid == 0) {
-    for (int s = 0; s < kMaxStages; ++s) { mbar_init(smem_u32(&hdr->full[s]), 1); mbar_init(smem_u32(&hdr->empty[s]), 1); }
+    for (int s = 0; s < kMaxStages; ++s) { mbar_init(smem_u32(&hdr->full[s]), p.conv ? 2 : 1); mbar_init(smem_u32(&hdr->empty[s]), 1); }   // full: one arrival per producer warp
     for (int s = 0; s < kAccStages; ++s) { mbar_init(smem_u32(&hdr->d_full[s]), 1); mbar_init(smem_u32(&hdr->d_empty[s]), kEpiWarps); }
     hdr->abort_flag = 0u;
     fence_barrier_init();
@@ -261,46 +278,80 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
   const uint32_t tmem_base = hdr->tmem_base;
   volatile uint32_t* abort_flag = &hdr->abort_flag;
 
-  if (warp == 0) {
-    // ===================== TMA producer (whole warp loops, one elected lane issues) =====================
+  if (warp == 0 || (warp >= 2 + kEpiWarps && p.conv)) {
+    // ===================== TMA producers (whole warp loops, one elected lane issues) =====================
+    // Convolutions: warp 0 fetches the activation tiles, the last warp the weight tiles; each arms a stage's
+    // barrier with its own bytes, so a stage is full when both copies have landed, and the issue cost of a
+    // stage (tap arithmetic included) is split over two warps.  GEMM: warp 0 issues both copies of a stage
+    // back to back, which keeps them in stage order in the copy queue (measured 2-6 % faster there).
+    // A 4-D activation copy costs its issuing warp about 400 cycles, so in a convolution two warps take
+    // the even and the odd k blocks of the sequence.
+    const bool is_a = warp != 2 + kEpiWarps;
+    const uint32_t a_par = warp == 0 ? 0u : 1u;
+    const uint32_t my_bytes = !p.conv ? stage_bytes : is_a ? kABytes : p.b_bytes;
     uint32_t stage = 0, phase = 0, issued = 0;
     bool ok = true;
+    STEM_ACC_DECL;
+    STEM_CLK(t_all);
+#ifdef DIMQ_B200_DIAG
+    const bool skip = (is_a && (p.diag & 2)) || (!is_a && (p.diag & 1));
+#endif
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       const int n_blk = t % p.n_tiles, m_blk = t / p.n_tiles;
       int ow0 = 0, oh0 = 0, b0 = 0;
-      if (p.conv) {
+      if (p.conv && is_a) {
         ow0 = (m_blk % p.tiles_w) * p.tw;
         oh0 = ((m_blk / p.tiles_w) % p.tiles_h) * p.th;
         b0 = (m_blk / (p.tiles_w * p.tiles_h)) * p.tb;
       }
       for (int pass = 0; pass < p.passes && ok; ++pass) {
-        int tap = 0, cb = 0;
+        // convolution: k block kb = (tap (kh, kw), channel block cb); the tap's input offset is kept by carrying
+        int kh = 0, kw = 0, cb = 0;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->empty[stage]), phase ^ 1u, abort_flag, 0x1100u | stage))) { ok = false; break; }
+          if (p.conv && is_a && (issued & 1u) != a_par) {   // the other activation producer's k block
+            ++issued;
+            if (++stage == n_st) { stage = 0; phase ^= 1u; }
+            if (++cb == p.c_blocks) {
+              cb = 0;
+              if (++kw == p.KW) { kw = 0; ++kh; }
+            }
+            continue;
+          }
+          STEM_CLK(t_w);
+          if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->empty[stage]), phase ^ 1u, abort_flag, (is_a ? 0x1100u : 0x1600u) | stage))) { ok = false; break; }
+          STEM_ACC(1, t_w);
+          STEM_CLK(t_is);
           const uint32_t full = smem_u32(&hdr->full[stage]);
           const uint32_t dst_a = smem_u32(smem + stage * stage_bytes);
-          const uint32_t dst_b = dst_a + kABytes;
-          const int kcol_b = (pass * p.k_blocks + kb) * kBK;
-          if (!p.conv) {
 #ifdef DIMQ_B200_DIAG
-            if (p.diag != 0) {
-              if (elect_one()) {
-                mbar_arrive_expect_tx(full, p.diag == 1 ? kABytes : p.b_bytes);
-                if (p.diag == 1) tma_load_2d(dst_a, &maps.a[0], full, kb * kBK, m_blk * kBM);
-                else tma_load_2d(dst_b, &maps.b, full, kcol_b, n_blk * p.bn);
-              }
-            } else
-#endif
+          if (!p.conv && (p.diag & 3) != 0) {
             if (elect_one()) {
-              mbar_arrive_expect_tx(full, stage_bytes);
+              if ((p.diag & 3) == 3) mbar_arrive(full);
+              else {
+                mbar_arrive_expect_tx(full, (p.diag & 3) == 1 ? kABytes : p.b_bytes);
+                if ((p.diag & 3) == 1) tma_load_2d(dst_a, &maps.a[0], full, kb * kBK, m_blk * kBM);
+                else tma_load_2d(dst_a + kABytes, &maps.b, full, (pass * p.k_blocks + kb) * kBK, n_blk * p.bn);
+              }
+            }
+          } else if (skip) {
+            if (elect_one()) mbar_arrive(full);
+          } else
+#endif
+          if (!is_a) {
+            if (elect_one()) {
+              mbar_arrive_expect_tx(full, my_bytes);
+              tma_load_2d(dst_a + kABytes, &maps.b, full, (pass * p.k_blocks + kb) * kBK, n_blk * p.bn);
+            }
+          } else if (!p.conv) {
+            if (elect_one()) {
+              mbar_arrive_expect_tx(full, my_bytes);
               tma_load_2d(dst_a, &maps.a[0], full, kb * kBK, m_blk * kBM);
-              tma_load_2d(dst_b, &maps.b, full, kcol_b, n_blk * p.bn);
+              tma_load_2d(dst_a + kABytes, &maps.b, full, (pass * p.k_blocks + kb) * kBK, n_blk * p.bn);
             }
           } else {
-            // tap (kh, kw), channels [64 cb, 64 cb + 64): input pixel = stride * out + tap offset.  With
-            // stride 2 the input is addressed through one tensor map per (row, column) parity, so the box
-            // stays dense; taps that fall outside the image read the zero fill.
-            const int kh = tap / p.KW, kw = tap - kh * p.KW;
+            // input pixel = stride * out + tap offset.  With stride 2 the input is addressed through one
+            // tensor map per (row, column) parity, so the box stays dense; taps that fall outside the image
+            // read the zero fill.
             const int dy = kh * p.dil_h - p.pad_h, dx = kw * p.dil_w - p.pad_w;
             int map = 0, hy = oh0 + dy, wx = ow0 + dx;
             if (p.stride == 2) {
@@ -310,18 +361,24 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
               wx = ow0 + ((dx - px) >> 1);
             }
             if (elect_one()) {
-              mbar_arrive_expect_tx(full, stage_bytes);
+              mbar_arrive_expect_tx(full, my_bytes);
               tma_load_4d(dst_a, &maps.a[map], full, cb * kBK, wx, hy, b0);
-              tma_load_2d(dst_b, &maps.b, full, kcol_b, n_blk * p.bn);
             }
-            if (++cb == p.c_blocks) { cb = 0; ++tap; }
+            if (++cb == p.c_blocks) {
+              cb = 0;
+              if (++kw == p.KW) { kw = 0; ++kh; }
+            }
           }
           __syncwarp();
+          STEM_ACC(2, t_is);
           ++issued;
           if (++stage == n_st) { stage = 0; phase ^= 1u; }
         }
       }
     }
+    STEM_ACC(0, t_all);
+    if (warp == 0) STEM_FLUSH(0, 3);
+    else if (!is_a) STEM_FLUSH(10, 3);
     if (!ok && lane == 0) {
       // gave up: wait (bounded) for the copies still in flight so that none lands after the CTA has exited
       const uint32_t n_back = issued < n_st ? issued : n_st;
@@ -339,16 +396,26 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
     bool ok = true;
     const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem));
     const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(smem + kABytes));
+    STEM_ACC_DECL;
+    STEM_CLK(t_all);
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      STEM_CLK(t_w1);
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->d_empty[as]), aph ^ 1u, abort_flag, 0x1200u | as))) { ok = false; break; }
+      STEM_ACC(1, t_w1);
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + as * kAccCols;
       for (int kb = 0; kb < total_kb; ++kb) {
+        STEM_CLK(t_w2);
         if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->full[stage]), phase, abort_flag, 0x1300u | stage))) { ok = false; break; }
+        STEM_ACC(2, t_w2);
+        STEM_CLK(t_is);
         tc_fence_after();
         if (elect_one()) {
           const uint64_t off = static_cast<uint64_t>(stage * (stage_bytes >> 4));
           const uint64_t a_desc = a_desc0 + off, b_desc = b_desc0 + off;
+#ifdef DIMQ_B200_DIAG
+          if (!(p.diag & 8))
+#endif
 #pragma unroll
           for (int j = 0; j < kBK / 16; ++j)   // 16 k = 32 bytes inside the swizzled row (encoded >> 4)
             mma_f16_ss(d_tmem, a_desc + static_cast<uint64_t>(2 * j), b_desc + static_cast<uint64_t>(2 * j), p.idesc,
@@ -356,6 +423,7 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
           mma_commit(smem_u32(&hdr->empty[stage]));   // frees the stage when these MMAs have read it
         }
         __syncwarp();
+        STEM_ACC(3, t_is);
         if (++stage == n_st) { stage = 0; phase ^= 1u; }
       }
       if (!ok) break;
@@ -363,7 +431,9 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
       __syncwarp();
       if (++as == kAccStages) { as = 0; aph ^= 1u; }
     }
-  } else {
+    STEM_ACC(0, t_all);
+    STEM_FLUSH(4, 4);
+  } else if (warp < 2 + kEpiWarps) {   // the last warp has no work in a GEMM: it must not fall into this branch
     // ===================== epilogue =====================
     const int quarter = warp & 3;          // TMEM lanes [32 quarter, 32 quarter + 32) = rows of the tile
     const int sub = (warp - 2) >> 2;       // which of the two warps of this quarter: chunks sub, sub + 2, ...
@@ -373,6 +443,8 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
     const int n_chunks = p.bn / 32;
     uint32_t as = 0, aph = 0;
     bool ok = true;
+    STEM_ACC_DECL;
+    STEM_CLK(t_all);
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       const int n_blk = t % p.n_tiles, m_blk = t / p.n_tiles;
       // where this thread's output row lives (for the residual); the store itself goes through TMA
@@ -404,7 +476,9 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
         bj[i] = (p.bias != nullptr && sub + 2 * i < n_chunks && nb < p.N) ? load_as_float(p.bias, p.bias_dtype, nb) : 0.0f;
       }
       // tcgen05.ld is warp-collective: the whole warp proceeds or the whole warp gives up
+      STEM_CLK(t_w1);
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->d_full[as]), aph, abort_flag, 0x1500u | as))) { ok = false; break; }
+      STEM_ACC(1, t_w1);
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * kAccCols;
       if (sub >= n_chunks) {
@@ -464,6 +538,9 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
         }
         fence_proxy_async_smem();
         __syncwarp();
+#ifdef DIMQ_B200_DIAG
+        if (!(p.diag & 16))
+#endif
         if (elect_one()) {
           if (p.conv) tma_store_4d(&maps.y, smem_u32(my_out), static_cast<int>(n_first), c1, c2, c3);
           else tma_store_2d(&maps.y, smem_u32(my_out), static_cast<int>(n_first), c1);
@@ -472,6 +549,8 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
       }
       if (++as == kAccStages) { as = 0; aph ^= 1u; }
     }
+    STEM_ACC(0, t_all);
+    if (ew == 0) STEM_FLUSH(8, 2);
     __syncwarp();
     if (elect_one()) tma_store_wait_all();
     __syncwarp();
@@ -617,6 +696,7 @@ int launch_dense(DenseMaps& maps, DenseParams& p, const void* scratch, int64_t K
   p.b_bytes = static_cast<uint32_t>(p.bn) * kBK * 2;
 #ifdef DIMQ_B200_DIAG
   p.diag = g_dense_diag;
+  p.prof = g_stem_prof;
 #endif
   const int fmt = x_dtype == DIMQ_BF16 ? 1 : 0;
   p.idesc = tc::make_idesc_f16(fmt, fmt, kBM, p.bn);
@@ -800,17 +880,24 @@ struct StemHeader {
   volatile uint32_t abort_flag;
 };
 
-#ifdef DIMQ_B200_DIAG
-#define STEM_CLK(v) const long long v = clock64()
-#define STEM_ACC(slot, since) do { if (p.prof != nullptr && lane == 0) acc_[slot] += static_cast<unsigned long long>(clock64() - (since)); } while (0)
-#define STEM_ACC_DECL unsigned long long acc_[8] = {0ull, 0ull, 0ull, 0ull, 0ull, 0ull, 0ull, 0ull}
-#define STEM_FLUSH(first, n) do { if (p.prof != nullptr && lane == 0) for (int q_ = 0; q_ < (n); ++q_) p.prof[blockIdx.x * 32 + (first) + q_] = acc_[q_]; } while (0)
-#else
-#define STEM_CLK(v)
-#define STEM_ACC(slot, since)
-#define STEM_ACC_DECL
-#define STEM_FLUSH(first, n)
-#endif
+
+// Tile t = (image b, tile row, tile column); a CTA walks t = blockIdx.x, + gridDim.x, ... and keeps the three
+// indices by carrying instead of dividing.
+struct TileWalk {
+  int tw, th, b, d_w, d_h, d_b, tiles_w, tiles_h;
+  __device__ __forceinline__ void start(int t, int step, int tiles_w_, int tiles_h_) {
+    tiles_w = tiles_w_; tiles_h = tiles_h_;
+    tw = t % tiles_w; th = (t / tiles_w) % tiles_h; b = t / (tiles_w * tiles_h);
+    d_w = step % tiles_w; d_h = (step / tiles_w) % tiles_h; d_b = step / (tiles_w * tiles_h);
+  }
+  __device__ __forceinline__ void next() {
+    tw += d_w;
+    th += d_h;
+    if (tw >= tiles_w) { tw -= tiles_w; ++th; }
+    b += d_b;
+    if (th >= tiles_h) { th -= tiles_h; ++b; }
+  }
+};
 
 template <int ES>
 __global__ void __launch_bounds__(kStemThreads, 1)
@@ -862,23 +949,6 @@ lut_stem_conv_kernel(const __grid_constant__ StemMaps maps, const StemParams p) 
   const uint32_t tmem_base = hdr->tmem_base;
   volatile uint32_t* abort_flag = &hdr->abort_flag;
 
-  // Tile t = (image b, tile row, tile column); a CTA walks t = blockIdx.x, + gridDim.x, ... and keeps the three
-  // indices by carrying instead of dividing.
-  struct TileWalk {
-    int tw, th, b, d_w, d_h, d_b, tiles_w, tiles_h;
-    __device__ __forceinline__ void start(int t, int step, int tiles_w_, int tiles_h_) {
-      tiles_w = tiles_w_; tiles_h = tiles_h_;
-      tw = t % tiles_w; th = (t / tiles_w) % tiles_h; b = t / (tiles_w * tiles_h);
-      d_w = step % tiles_w; d_h = (step / tiles_w) % tiles_h; d_b = step / (tiles_w * tiles_h);
-    }
-    __device__ __forceinline__ void next() {
-      tw += d_w;
-      th += d_h;
-      if (tw >= tiles_w) { tw -= tiles_w; ++th; }
-      b += d_b;
-      if (th >= tiles_h) { th -= tiles_h; ++b; }
-    }
-  };
   TileWalk walk;
   walk.start(blockIdx.x, gridDim.x, p.tiles_w, p.tiles_h);
 
