@@ -1,6 +1,7 @@
 // Dense helper of the whole-model harness: (residual add +) LayerNorm over 16-bit rows.
 // One warp per row, the row held in registers (8 elements per 16-byte load), statistics in fp32.
 // Memory-bound: every element is read once and written once.
+#include <type_traits>
 #include "common.cuh"
 
 namespace dimq {
@@ -257,9 +258,10 @@ max_pool_nhwc_kernel(const T* __restrict__ x, T* __restrict__ y, int B, int H, i
   const int64_t pix = i / cv;
   const int ow = static_cast<int>(pix % OW), oh = static_cast<int>((pix / OW) % OH);
   const int b = static_cast<int>(pix / (static_cast<int64_t>(OW) * OH));
-  float m[8];
-#pragma unroll
-  for (int e = 0; e < 8; ++e) m[e] = -INFINITY;
+  // packed 16-bit maxima, two channels per instruction (no conversions); -inf in both halves to start
+  using T2 = typename std::conditional<std::is_same<T, __nv_bfloat16>::value, __nv_bfloat162, __half2>::type;
+  const uint32_t ninf = std::is_same<T, __nv_bfloat16>::value ? 0xFF80FF80u : 0xFC00FC00u;
+  uint32_t m[4] = {ninf, ninf, ninf, ninf};
   for (int dy = 0; dy < k; ++dy) {
     const int ih = oh * stride + dy - pad;
     if (ih < 0 || ih >= H) continue;
@@ -267,15 +269,15 @@ max_pool_nhwc_kernel(const T* __restrict__ x, T* __restrict__ y, int B, int H, i
       const int iw = ow * stride + dx - pad;
       if (iw < 0 || iw >= W) continue;
       const uint4 q = __ldg(reinterpret_cast<const uint4*>(x + ((static_cast<int64_t>(b) * H + ih) * W + iw) * C) + c8);
-      const T* e8 = reinterpret_cast<const T*>(&q);
+      const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-      for (int e = 0; e < 8; ++e) m[e] = fmaxf(m[e], to_float<T>(e8[e]));
+      for (int e = 0; e < 4; ++e) {
+        const T2 r = __hmax2(*reinterpret_cast<const T2*>(&m[e]), *reinterpret_cast<const T2*>(&w4[e]));
+        m[e] = *reinterpret_cast<const uint32_t*>(&r);
+      }
     }
   }
-  uint4 out;
-  T* o = reinterpret_cast<T*>(&out);
-#pragma unroll
-  for (int e = 0; e < 8; ++e) o[e] = from_float<T>(m[e]);
+  const uint4 out = make_uint4(m[0], m[1], m[2], m[3]);
   reinterpret_cast<uint4*>(y + ((static_cast<int64_t>(b) * OH + oh) * OW + ow) * C)[c8] = out;
 }
 

@@ -289,6 +289,9 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
     const bool is_a = warp != 2 + kEpiWarps;
     const uint32_t a_par = warp == 0 ? 0u : 1u;
     const uint32_t my_bytes = !p.conv ? stage_bytes : is_a ? kABytes : p.b_bytes;
+    // programmatic dependent launch: the expansion kernel before this one in the stream must have finished
+    // before the first weight tile is read (the activations were complete before that kernel started)
+    if (!is_a || !p.conv) asm volatile("griddepcontrol.wait;" ::: "memory");
     uint32_t stage = 0, phase = 0, issued = 0;
     bool ok = true;
     STEM_ACC_DECL;
@@ -573,6 +576,9 @@ template <int BITS>
 __global__ void __launch_bounds__(256)
 lut_expand_kernel(const uint8_t* __restrict__ packed, const void* __restrict__ codebooks, int cb_dtype, int entries,
                   int64_t group_rows, int64_t rows, int64_t K, int fmt, int passes, uint16_t* __restrict__ out) {
+  // the GEMM that follows in the stream is launched as a programmatic dependent: its prologue may start now,
+  // and it waits (griddepcontrol.wait) before it reads what this kernel writes
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int64_t units_per_row = K / 32;
   const int64_t u = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
   if (u >= rows * units_per_row) return;
@@ -683,6 +689,27 @@ int expand(const dimq_wq_weight* w, const uint8_t* packed, int64_t rows, int64_t
 }
 
 // Shared tail of the GEMM and the convolution launchers: weight map, shared-memory budget, launch.
+// Launch as a programmatic dependent of the kernel before it in the stream (the weight expansion): the
+// prologue (barriers, TMEM, tensor-map prefetch, the first activation copies) overlaps that kernel's tail
+// and the launch latency; the kernel itself waits before it reads the expanded weight.
+template <typename Kern, typename Maps, typename Params>
+cudaError_t launch_dependent(Kern kern, int grid, int threads, size_t smem, cudaStream_t st, const Maps& maps, const Params& p) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(static_cast<unsigned>(threads));
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+#ifdef DIMQ_B200_DIAG
+  if (g_dense_diag & 1024) cfg.numAttrs = 0;   // timing experiment: plain stream order
+#endif
+  return cudaLaunchKernelEx(&cfg, kern, maps, p);
+}
+
 int launch_dense(DenseMaps& maps, DenseParams& p, const void* scratch, int64_t K, int x_dtype, const void* bias,
                  int bias_dtype, const void* residual, int y_dtype, int epilogue, cudaStream_t st) {
   EncodeTiledFn encode = encode_tiled();
@@ -724,12 +751,13 @@ int launch_dense(DenseMaps& maps, DenseParams& p, const void* scratch, int64_t K
   if (es == 2) {
     e = cudaFuncSetAttribute(lut_dense_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
-    lut_dense_tc_kernel<2><<<grid, kThreads, smem, st>>>(maps, p);
+    e = launch_dependent(lut_dense_tc_kernel<2>, grid, kThreads, smem, st, maps, p);
   } else {
     e = cudaFuncSetAttribute(lut_dense_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
-    lut_dense_tc_kernel<4><<<grid, kThreads, smem, st>>>(maps, p);
+    e = launch_dependent(lut_dense_tc_kernel<4>, grid, kThreads, smem, st, maps, p);
   }
+  if (e != cudaSuccess) return static_cast<int>(e);
   return launch_status();
 }
 
@@ -1067,6 +1095,7 @@ lut_stem_conv_kernel(const __grid_constant__ StemMaps maps, const StemParams p) 
   } else if (warp == kStemBuilders) {
     // ===================== MMA issuer =====================
     bool ok = true;
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // the expanded weight is written by the kernel before this one
     if (elect_one()) {
       mbar_arrive_expect_tx(smem_u32(&hdr->b_full), p.b_bytes);
       for (int kb = 0; kb < 3 * p.passes; ++kb)
@@ -1229,6 +1258,7 @@ __global__ void __launch_bounds__(256)
 stem_expand_kernel(const uint8_t* __restrict__ packed, int bits, int64_t nbytes, const void* __restrict__ codebooks,
                    int cb_dtype, int entries, int64_t group_rows, int64_t N, int KH, int KW, int lead, int fmt,
                    int passes, uint16_t* __restrict__ out) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // see lut_expand_kernel
   const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
   if (i >= N * kStemK) return;
   const int64_t n = i / kStemK;
@@ -1353,12 +1383,13 @@ int launch_stem_conv(const void* x, int x_dtype, const dimq_wq_weight* w, const 
   if (es == 2) {
     e = cudaFuncSetAttribute(lut_stem_conv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
-    lut_stem_conv_kernel<2><<<grid, kStemThreads, smem, st>>>(maps, p);
+    e = launch_dependent(lut_stem_conv_kernel<2>, grid, kStemThreads, smem, st, maps, p);
   } else {
     e = cudaFuncSetAttribute(lut_stem_conv_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
-    lut_stem_conv_kernel<4><<<grid, kStemThreads, smem, st>>>(maps, p);
+    e = launch_dependent(lut_stem_conv_kernel<4>, grid, kStemThreads, smem, st, maps, p);
   }
+  if (e != cudaSuccess) return static_cast<int>(e);
   return launch_status();
 }
 
