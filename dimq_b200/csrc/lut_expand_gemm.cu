@@ -38,6 +38,7 @@ using namespace tc;
 constexpr int kBM = 128;         // activation rows (output pixels) per tile
 constexpr int kBK = 64;          // k per pipeline stage: 128 bytes of 16-bit elements
 constexpr int kMaxStages = 8;
+constexpr int kPairBlockCycles = 675, kSingleBlockCycles = 750;   // per 64-k block of a 256-wide tile (measured: a pair is ~10 % faster per block)
 constexpr int kAccStages = 2;
 constexpr int kAccCols = 256;    // TMEM columns per accumulator buffer
 constexpr int kTmemCols = 512;
@@ -67,6 +68,7 @@ struct DenseParams {
   int tw, th, tb, tiles_w, tiles_h;
   int OW, OH, Bn;
   int stride, pad_h, pad_w, dil_h, dil_w, KW, c_blocks;
+  int pair;                 // 1: CTA pairs (cta_group::2), GEMM only; m_tiles then counts 256-row pairs of blocks
 #ifdef DIMQ_B200_DIAG
   int diag;
   unsigned long long* prof;   // 32 cycle counters per CTA, or null
@@ -238,8 +240,53 @@ __device__ __forceinline__ void load_residual(const void* p, int y_dtype, int va
   }
 }
 
-// ES = bytes per output element (2: bf16 / fp16, 4: fp32)
-template <int ES>
+// CTA-pair helpers (cta_group::2): the two CTAs of a cluster work on one 256 x 256 tile.  Each loads its own
+// 128 activation rows and its own half (128 rows) of the weight tile, and counts the bytes on the LEADER's
+// (cluster rank 0) stage barrier; the leader issues M = 256 MMAs that read both CTAs' shared memory and write
+// both CTAs' tensor memory; its commits arrive on the barriers of both CTAs (multicast).  Per CTA a 64-k block
+// then needs 32 KB from L2 instead of 48 KB.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {   // the same shared address in CTA `rank` of the cluster
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void remote_arrive(uint32_t bar_cluster) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
+// TMA tile copy into this CTA's shared memory whose bytes are counted on a barrier of the cluster (no multicast)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap, uint32_t bar_cluster, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void mma_f16_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {   // one arrival on `bar` in both CTAs of the pair
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(static_cast<uint16_t>(3)) : "memory");
+}
+
+// ES = bytes per output element (2: bf16 / fp16, 4: fp32); PAIR: CTA pairs (GEMM only, bn = 256)
+template <int ES, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -256,12 +303,15 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
-  const int num_tiles = p.m_tiles * p.n_tiles;
+  const int num_tiles = p.m_tiles * p.n_tiles;   // PAIR: m_tiles counts 256-row pairs of blocks
   const int total_kb = p.k_blocks * p.passes;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const int tile0 = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int tile_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
   if (tid == 0) {
     for (int s = 0; s < kMaxStages; ++s) { mbar_init(smem_u32(&hdr->full[s]), p.conv ? 2 : 1); mbar_init(smem_u32(&hdr->empty[s]), 1); }   // full: one arrival per producer warp
-    for (int s = 0; s < kAccStages; ++s) { mbar_init(smem_u32(&hdr->d_full[s]), 1); mbar_init(smem_u32(&hdr->d_empty[s]), kEpiWarps); }
+    for (int s = 0; s < kAccStages; ++s) { mbar_init(smem_u32(&hdr->d_full[s]), 1); mbar_init(smem_u32(&hdr->d_empty[s]), PAIR ? 2 * kEpiWarps : kEpiWarps); }
     hdr->abort_flag = 0u;
     fence_barrier_init();
     prefetch_tensormap(&maps.a[0]);
@@ -269,12 +319,18 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
     prefetch_tensormap(&maps.y);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&hdr->tmem_base), kTmemCols);
-    tmem_relinquish();
+    if constexpr (PAIR) {   // one warp of each CTA of the pair: the same columns in both tensor memories
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&hdr->tmem_base)), "r"(kTmemCols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      tmem_alloc(smem_u32(&hdr->tmem_base), kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if constexpr (PAIR) cluster_sync_all();   // the peer's barriers are initialised before anything signals them
   const uint32_t tmem_base = hdr->tmem_base;
   volatile uint32_t* abort_flag = &hdr->abort_flag;
 
@@ -299,8 +355,8 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
 #ifdef DIMQ_B200_DIAG
     const bool skip = (is_a && (p.diag & 2)) || (!is_a && (p.diag & 1));
 #endif
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-      const int n_blk = t % p.n_tiles, m_blk = t / p.n_tiles;
+    for (int t = tile0; t < num_tiles && ok; t += tile_step) {
+      const int n_blk = t % p.n_tiles, m_blk = PAIR ? 2 * (t / p.n_tiles) + static_cast<int>(rank) : t / p.n_tiles;
       int ow0 = 0, oh0 = 0, b0 = 0;
       if (p.conv && is_a) {
         ow0 = (m_blk % p.tiles_w) * p.tw;
@@ -346,7 +402,15 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
               tma_load_2d(dst_a + kABytes, &maps.b, full, (pass * p.k_blocks + kb) * kBK, n_blk * p.bn);
             }
           } else if (!p.conv) {
-            if (elect_one()) {
+            if constexpr (PAIR) {
+              if (elect_one()) {
+                const uint32_t lead_full = map_to_cta(full, 0);
+                if (rank == 0) mbar_arrive_expect_tx(full, 2 * my_bytes);   // both CTAs' copies of this stage
+                tma_load_2d_pair(dst_a, &maps.a[0], lead_full, kb * kBK, m_blk * kBM);
+                tma_load_2d_pair(dst_a + kABytes, &maps.b, lead_full, (pass * p.k_blocks + kb) * kBK,
+                                 n_blk * p.bn + static_cast<int>(rank) * (p.bn / 2));
+              }
+            } else if (elect_one()) {
               mbar_arrive_expect_tx(full, my_bytes);
               tma_load_2d(dst_a, &maps.a[0], full, kb * kBK, m_blk * kBM);
               tma_load_2d(dst_a + kABytes, &maps.b, full, (pass * p.k_blocks + kb) * kBK, n_blk * p.bn);
@@ -395,13 +459,14 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
     __syncwarp();
   } else if (warp == 1) {
     // ===================== MMA issuer (whole warp loops, one elected lane issues) =====================
+    // PAIR: only the leader CTA issues; its MMAs and commits act on both CTAs
     uint32_t stage = 0, phase = 0, as = 0, aph = 0;
-    bool ok = true;
+    bool ok = !PAIR || rank == 0;
     const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem));
     const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(smem + kABytes));
     STEM_ACC_DECL;
     STEM_CLK(t_all);
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+    for (int t = tile0; t < num_tiles && ok; t += tile_step) {
       STEM_CLK(t_w1);
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->d_empty[as]), aph ^ 1u, abort_flag, 0x1200u | as))) { ok = false; break; }
       STEM_ACC(1, t_w1);
@@ -420,17 +485,27 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
           if (!(p.diag & 8))
 #endif
 #pragma unroll
-          for (int j = 0; j < kBK / 16; ++j)   // 16 k = 32 bytes inside the swizzled row (encoded >> 4)
-            mma_f16_ss(d_tmem, a_desc + static_cast<uint64_t>(2 * j), b_desc + static_cast<uint64_t>(2 * j), p.idesc,
-                       (kb | j) ? 1u : 0u);
-          mma_commit(smem_u32(&hdr->empty[stage]));   // frees the stage when these MMAs have read it
+          for (int j = 0; j < kBK / 16; ++j) {  // 16 k = 32 bytes inside the swizzled row (encoded >> 4)
+            if constexpr (PAIR)
+              mma_f16_ss_pair(d_tmem, a_desc + static_cast<uint64_t>(2 * j), b_desc + static_cast<uint64_t>(2 * j), p.idesc,
+                              (kb | j) ? 1u : 0u);
+            else
+              mma_f16_ss(d_tmem, a_desc + static_cast<uint64_t>(2 * j), b_desc + static_cast<uint64_t>(2 * j), p.idesc,
+                         (kb | j) ? 1u : 0u);
+          }
+          // frees the stage (in both CTAs of a pair) when these MMAs have read it
+          if constexpr (PAIR) mma_commit_pair(smem_u32(&hdr->empty[stage]));
+          else mma_commit(smem_u32(&hdr->empty[stage]));
         }
         __syncwarp();
         STEM_ACC(3, t_is);
         if (++stage == n_st) { stage = 0; phase ^= 1u; }
       }
       if (!ok) break;
-      if (elect_one()) mma_commit(smem_u32(&hdr->d_full[as]));
+      if (elect_one()) {
+        if constexpr (PAIR) mma_commit_pair(smem_u32(&hdr->d_full[as]));
+        else mma_commit(smem_u32(&hdr->d_full[as]));
+      }
       __syncwarp();
       if (++as == kAccStages) { as = 0; aph ^= 1u; }
     }
@@ -448,8 +523,8 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
     bool ok = true;
     STEM_ACC_DECL;
     STEM_CLK(t_all);
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-      const int n_blk = t % p.n_tiles, m_blk = t / p.n_tiles;
+    for (int t = tile0; t < num_tiles && ok; t += tile_step) {
+      const int n_blk = t % p.n_tiles, m_blk = PAIR ? 2 * (t / p.n_tiles) + static_cast<int>(rank) : t / p.n_tiles;
       // where this thread's output row lives (for the residual); the store itself goes through TMA
       int64_t row_off = -1;    // element offset of [row][0] in y, or -1 when the row is outside the tensor
       int c1 = 0, c2 = 0, c3 = 0;   // TMA store coordinates of this warp's 32 rows
@@ -487,7 +562,10 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
       if (sub >= n_chunks) {
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&hdr->d_empty[as]));
+        if (lane == 0) {
+          if constexpr (PAIR) remote_arrive(map_to_cta(smem_u32(&hdr->d_empty[as]), 0));
+          else mbar_arrive(smem_u32(&hdr->d_empty[as]));
+        }
       }
       for (int c = sub; c < n_chunks; c += 2) {
         const int64_t n_first = static_cast<int64_t>(n_blk) * p.bn + c * 32;
@@ -503,7 +581,10 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
           // every column this warp reads of the buffer is in registers: hand it back to the MMA warp
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&hdr->d_empty[as]));
+          if (lane == 0) {
+            if constexpr (PAIR) remote_arrive(map_to_cta(smem_u32(&hdr->d_empty[as]), 0));   // the leader's MMA warp waits for both CTAs
+            else mbar_arrive(smem_u32(&hdr->d_empty[as]));
+          }
         }
         __syncwarp();
         if (n_first >= p.N) continue;        // chunk beyond the last feature (warp-uniform)
@@ -562,9 +643,13 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
   // ---- teardown -----------------------------------------------------------------
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();   // neither CTA leaves, or frees tensor memory, while the peer may still use it
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if constexpr (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    else
+      tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
@@ -693,19 +778,27 @@ int expand(const dimq_wq_weight* w, const uint8_t* packed, int64_t rows, int64_t
 // prologue (barriers, TMEM, tensor-map prefetch, the first activation copies) overlaps that kernel's tail
 // and the launch latency; the kernel itself waits before it reads the expanded weight.
 template <typename Kern, typename Maps, typename Params>
-cudaError_t launch_dependent(Kern kern, int grid, int threads, size_t smem, cudaStream_t st, const Maps& maps, const Params& p) {
+cudaError_t launch_dependent(Kern kern, int grid, int threads, size_t smem, cudaStream_t st, const Maps& maps, const Params& p,
+                             int cluster = 1) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(grid));
   cfg.blockDim = dim3(static_cast<unsigned>(threads));
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (cluster > 1) {   // CTA pairs: consecutive CTAs of the grid form a cluster
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = static_cast<unsigned>(cluster);
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+  }
 #ifdef DIMQ_B200_DIAG
-  if (g_dense_diag & 1024) cfg.numAttrs = 0;   // timing experiment: plain stream order
+  if ((g_dense_diag & 1024) && cluster == 1) cfg.numAttrs = 0;   // timing experiment: plain stream order
 #endif
   return cudaLaunchKernelEx(&cfg, kern, maps, p);
 }
@@ -720,16 +813,17 @@ int launch_dense(DenseMaps& maps, DenseParams& p, const void* scratch, int64_t K
   p.y_dtype = y_dtype;
   p.epilogue = epilogue;
   p.k_blocks = static_cast<int>(K / kBK);
-  p.b_bytes = static_cast<uint32_t>(p.bn) * kBK * 2;
+  const bool pair = p.pair != 0;   // CTA pairs: each CTA stages half of the 256 weight rows of a tile
+  p.b_bytes = static_cast<uint32_t>(pair ? p.bn / 2 : p.bn) * kBK * 2;
 #ifdef DIMQ_B200_DIAG
   p.diag = g_dense_diag;
   p.prof = g_stem_prof;
 #endif
   const int fmt = x_dtype == DIMQ_BF16 ? 1 : 0;
-  p.idesc = tc::make_idesc_f16(fmt, fmt, kBM, p.bn);
+  p.idesc = tc::make_idesc_f16(fmt, fmt, pair ? 2 * kBM : kBM, p.bn);
   const cuuint64_t bdims[2] = {static_cast<cuuint64_t>(K * p.passes), static_cast<cuuint64_t>(p.N)};
   const cuuint64_t bstr[1] = {static_cast<cuuint64_t>(K * p.passes) * 2};
-  const cuuint32_t bbox[2] = {kBK, static_cast<cuuint32_t>(p.bn)};
+  const cuuint32_t bbox[2] = {kBK, static_cast<cuuint32_t>(pair ? p.bn / 2 : p.bn)};
   const cuuint32_t estr[2] = {1, 1};
   if (encode(&maps.b, fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
              const_cast<void*>(scratch), bdims, bstr, bbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -748,14 +842,25 @@ int launch_dense(DenseMaps& maps, DenseParams& p, const void* scratch, int64_t K
   if (tiles >= 0x7FFFFFFF) return DIMQ_ERR_TOO_LARGE;
   const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
   cudaError_t e;
-  if (es == 2) {
-    e = cudaFuncSetAttribute(lut_dense_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (pair) {
+    const int clusters = static_cast<int>(tiles < kNumSMs / 2 ? tiles : kNumSMs / 2);
+    if (es == 2) {
+      e = cudaFuncSetAttribute(lut_dense_tc_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      if (e != cudaSuccess) return static_cast<int>(e);
+      e = launch_dependent(lut_dense_tc_kernel<2, true>, 2 * clusters, kThreads, smem, st, maps, p, 2);
+    } else {
+      e = cudaFuncSetAttribute(lut_dense_tc_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      if (e != cudaSuccess) return static_cast<int>(e);
+      e = launch_dependent(lut_dense_tc_kernel<4, true>, 2 * clusters, kThreads, smem, st, maps, p, 2);
+    }
+  } else if (es == 2) {
+    e = cudaFuncSetAttribute(lut_dense_tc_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
-    e = launch_dependent(lut_dense_tc_kernel<2>, grid, kThreads, smem, st, maps, p);
+    e = launch_dependent(lut_dense_tc_kernel<2, false>, grid, kThreads, smem, st, maps, p);
   } else {
-    e = cudaFuncSetAttribute(lut_dense_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    e = cudaFuncSetAttribute(lut_dense_tc_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
-    e = launch_dependent(lut_dense_tc_kernel<4>, grid, kThreads, smem, st, maps, p);
+    e = launch_dependent(lut_dense_tc_kernel<4, false>, grid, kThreads, smem, st, maps, p);
   }
   if (e != cudaSuccess) return static_cast<int>(e);
   return launch_status();
@@ -808,6 +913,21 @@ int64_t dense_workspace_bytes(int x_dtype, const dimq_wq_weight* w, int64_t N, i
   return N * K * 2 * passes_for(x_dtype, w);
 }
 
+// CTA pairs pay when the single-CTA tiling is the 128 x 256 one and the pair tiling's waves (74 clusters) at its
+// per-block cost come out ahead of the single-CTA waves (148 CTAs) at theirs.
+bool pair_pays(int m_blocks, int64_t N, int64_t k_total, int bn) {
+#ifdef DIMQ_B200_DIAG
+  if (g_dense_diag & 2048) return bn == 256;    // timing experiments: always / never
+  if (g_dense_diag & 4096) return false;
+#endif
+  if (bn != 256) return false;
+  const int64_t n_tiles = (N + 255) / 256;
+  const int64_t single = static_cast<int64_t>(m_blocks) * n_tiles, pairs = static_cast<int64_t>((m_blocks + 1) / 2) * n_tiles;
+  const int64_t waves_single = (single + kNumSMs - 1) / kNumSMs, waves_pair = (pairs + kNumSMs / 2 - 1) / (kNumSMs / 2);
+  (void)k_total;
+  return waves_pair * kPairBlockCycles < waves_single * kSingleBlockCycles;
+}
+
 int launch_linear_wq_dense(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
                            const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K, int epilogue,
                            void* workspace, int64_t workspace_bytes, cudaStream_t st) {
@@ -826,6 +946,12 @@ int launch_linear_wq_dense(const void* x, int x_dtype, const dimq_wq_weight* w, 
   p.m_tiles = static_cast<int>((M + kBM - 1) / kBM);
   p.bn = choose_bn(p.m_tiles, N);
   p.n_tiles = static_cast<int>((N + p.bn - 1) / p.bn);
+  if (pair_pays(p.m_tiles, N, K * p.passes, p.bn)) {
+    p.pair = 1;
+    p.bn = 256;
+    p.m_tiles = (p.m_tiles + 1) / 2;
+    p.n_tiles = static_cast<int>((N + 255) / 256);
+  }
   const CUtensorMapDataType dt = x_dtype == DIMQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const cuuint64_t adims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
   const cuuint64_t astr[1] = {static_cast<cuuint64_t>(K) * 2};

@@ -296,6 +296,37 @@ def test_vit_layer_shapes_at_batch_128(ops, k, n):
     assert max_abs <= MAX_ABS and rel <= REL_L2 and ops.last_device_status() == 0
 
 
+@pytest.mark.parametrize("mode", ["bf16_cb_fp32_out", "fp16_cb_two_terms_fp32_out", "bf16_cb_residual_gelu_bf16_out"])
+def test_linear_shapes_of_the_cta_pair_tiling(ops, mode):
+    """75 activation blocks (the last one ragged) x 5 weight tiles of 256 rows: the tile count at which the
+    large-M path forms CTA pairs (256 x 256 tiles, cta_group::2); the last pair has a single block.  Codebooks in
+    the activations' format and not (hi + lo terms), and the fused epilogue with a 16-bit output."""
+    m, k, n = 9500, 512, 1280
+    two = mode.startswith("fp16")
+    cw = make_weight(n, k, 4, seed=21, group_rows=128, cb_dtype=np.float16 if two else "bf16")
+    gen = torch.Generator().manual_seed(5)
+    x = torch.randn(m, k, generator=gen).to(torch.bfloat16)
+    bias = torch.randn(n, generator=gen).to(torch.bfloat16)
+    idx = o.unpack_bits(cw["packed"], n * k, 4).reshape(n, k)
+    w_hat = torch.from_numpy(o.dequantize(idx, cw["codebooks"], 128))
+    lin = F.linear(x.float(), w_hat, bias.float())
+    cb = _cuda(cw["codebooks"], torch.float16 if two else torch.bfloat16)
+    if mode.endswith("bf16_out"):
+        res = torch.randn(m, n, generator=gen).to(torch.bfloat16)
+        want = F.gelu(lin) + res.float()
+        got = ops.dimq_linear_wq(x.cuda(), _cuda(cw["packed"]), cb, bias.cuda(), n, k, bits=4, group_rows=128,
+                                 out_dtype=torch.bfloat16, epilogue="gelu", residual=res.cuda()).float().cpu()
+        tol_abs, tol_rel = MAX_ABS_16, REL_L2_16
+    else:
+        want = lin
+        got = ops.dimq_linear_wq(x.cuda(), _cuda(cw["packed"]), cb, bias.cuda(), n, k, bits=4, group_rows=128).cpu()
+        tol_abs, tol_rel = MAX_ABS, REL_L2
+    diff = got - want
+    max_abs, rel = float(diff.abs().max()), float(diff.norm() / want.norm())
+    print(f"pair tiling {mode}: max_abs={max_abs:.3e} rel_l2={rel:.3e}")
+    assert max_abs <= tol_abs and rel <= tol_rel and ops.last_device_status() == 0
+
+
 RESNET_LAYERS = [
     # C, H, OC, k, stride (ResNet-18's distinct quantised 4-bit convolutions with >= 64 input channels)
     (64, 56, 64, 3, 1), (64, 56, 128, 3, 2), (64, 56, 128, 1, 2), (128, 28, 128, 3, 1), (128, 28, 256, 3, 2),
