@@ -47,7 +47,9 @@ def hard_quantize_weight(w: torch.Tensor, centers: torch.Tensor, chunk_size: int
     """``(values like w, idx int64 like w)`` — nearest centre, ties to the lowest index.
 
     ``chunk_size`` is accepted for signature compatibility; the kernel needs no
-    chunking and the result does not depend on it.
+    chunking and the result does not depend on it.  At most 256 centres (indices of one
+    byte): the reference (quant/dimq.py:197-221) also takes larger codebooks and stores
+    int16 indices for them; this backend raises ``RuntimeError`` there.
     """
     if centers.numel() == 0:
         raise ValueError("centers must be non-empty")
