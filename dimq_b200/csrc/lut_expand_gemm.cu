@@ -68,6 +68,7 @@ struct DenseParams {
   int tw, th, tb, tiles_w, tiles_h;
   int OW, OH, Bn;
   int stride, pad_h, pad_w, dil_h, dil_w, KW, c_blocks;
+  int b_res;                // convolution: the whole expanded weight (one tile wide) stays in shared memory
   int pair;                 // 1: CTA pairs (cta_group::2), GEMM only; m_tiles then counts 256-row pairs of blocks
 #ifdef DIMQ_B200_DIAG
   int diag;
@@ -103,6 +104,7 @@ struct DenseMaps {
 struct DenseHeader {
   uint64_t full[kMaxStages], empty[kMaxStages];
   uint64_t d_full[kAccStages], d_empty[kAccStages];
+  uint64_t b_res_full;              // convolution with a resident weight: all its tiles have landed
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
 };
@@ -294,9 +296,12 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
   // rounded up to 1024 bytes in the shared window; plain pointer arithmetic on the array keeps the
   // accesses below in the shared state space (no generic loads and stores)
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  const uint32_t stage_bytes = kABytes + p.b_bytes;
+  // b_res: [stages: A 16 KB] [the weight: k blocks x bn*128 B] [header] ...
+  const uint32_t stage_bytes = p.b_res ? kABytes : kABytes + p.b_bytes;
   const uint32_t n_st = static_cast<uint32_t>(p.stages);
-  DenseHeader* hdr = reinterpret_cast<DenseHeader*>(smem + n_st * stage_bytes);
+  unsigned char* b_resident = smem + n_st * stage_bytes;
+  DenseHeader* hdr = reinterpret_cast<DenseHeader*>(
+      b_resident + (p.b_res ? static_cast<uint32_t>(p.k_blocks * p.passes) * p.b_bytes : 0u));
   float* bias_area = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(hdr) + kHeaderBytes);
   unsigned char* staging = reinterpret_cast<unsigned char*>(bias_area) + kBiasBytes;   // 1024-aligned
   constexpr uint32_t kStagingBytes = 32u * 32u * ES;
@@ -310,8 +315,9 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
   const int tile_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
   if (tid == 0) {
-    for (int s = 0; s < kMaxStages; ++s) { mbar_init(smem_u32(&hdr->full[s]), p.conv ? 2 : 1); mbar_init(smem_u32(&hdr->empty[s]), 1); }   // full: one arrival per producer warp
+    for (int s = 0; s < kMaxStages; ++s) { mbar_init(smem_u32(&hdr->full[s]), p.conv && !p.b_res ? 2 : 1); mbar_init(smem_u32(&hdr->empty[s]), 1); }   // full: one arrival per producer warp
     for (int s = 0; s < kAccStages; ++s) { mbar_init(smem_u32(&hdr->d_full[s]), 1); mbar_init(smem_u32(&hdr->d_empty[s]), PAIR ? 2 * kEpiWarps : kEpiWarps); }
+    mbar_init(smem_u32(&hdr->b_res_full), 1);
     hdr->abort_flag = 0u;
     fence_barrier_init();
     prefetch_tensormap(&maps.a[0]);
@@ -350,6 +356,17 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
     if (!is_a || !p.conv) asm volatile("griddepcontrol.wait;" ::: "memory");
     uint32_t stage = 0, phase = 0, issued = 0;
     bool ok = true;
+    if (!is_a && p.b_res) {
+      // resident weight: every k block's tile once, one barrier for all of them; no per-stage weight copies
+      if (elect_one()) {
+        const uint32_t bar = smem_u32(&hdr->b_res_full);
+        mbar_arrive_expect_tx(bar, static_cast<uint32_t>(total_kb) * p.b_bytes);
+        for (int kb = 0; kb < total_kb; ++kb)
+          tma_load_2d(smem_u32(b_resident + static_cast<uint32_t>(kb) * p.b_bytes), &maps.b, bar, kb * kBK, 0);
+      }
+      __syncwarp();
+      ok = false;   // skips the stage loop below (nothing was given up: the status word stays clear)
+    }
     STEM_ACC_DECL;
     STEM_CLK(t_all);
 #ifdef DIMQ_B200_DIAG
@@ -446,7 +463,7 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
     STEM_ACC(0, t_all);
     if (warp == 0) STEM_FLUSH(0, 3);
     else if (!is_a) STEM_FLUSH(10, 3);
-    if (!ok && lane == 0) {
+    if (!ok && lane == 0 && !(!is_a && p.b_res)) {
       // gave up: wait (bounded) for the copies still in flight so that none lands after the CTA has exited
       const uint32_t n_back = issued < n_st ? issued : n_st;
       uint32_t s = stage, ph = phase;
@@ -463,7 +480,8 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
     uint32_t stage = 0, phase = 0, as = 0, aph = 0;
     bool ok = !PAIR || rank == 0;
     const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem));
-    const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(smem + kABytes));
+    const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(p.b_res ? b_resident : smem + kABytes));
+    if (p.b_res && ok && !__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->b_res_full), 0u, abort_flag, 0x1A00u))) ok = false;
     STEM_ACC_DECL;
     STEM_CLK(t_all);
     for (int t = tile0; t < num_tiles && ok; t += tile_step) {
@@ -480,7 +498,8 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
         tc_fence_after();
         if (elect_one()) {
           const uint64_t off = static_cast<uint64_t>(stage * (stage_bytes >> 4));
-          const uint64_t a_desc = a_desc0 + off, b_desc = b_desc0 + off;
+          const uint64_t a_desc = a_desc0 + off;
+          const uint64_t b_desc = b_desc0 + (p.b_res ? static_cast<uint64_t>(static_cast<uint32_t>(kb) * (p.b_bytes >> 4)) : off);
 #ifdef DIMQ_B200_DIAG
           if (!(p.diag & 8))
 #endif
@@ -832,12 +851,27 @@ int launch_dense(DenseMaps& maps, DenseParams& p, const void* scratch, int64_t K
     return DIMQ_ERR_DRIVER;
   const int es = y_dtype == DIMQ_F32 ? 4 : 2;
   const size_t fixed = 1024 + kHeaderBytes + kBiasBytes + static_cast<size_t>(kEpiWarps) * 32 * 32 * es;
-  const size_t stage_bytes = kABytes + p.b_bytes;
-  int stages = static_cast<int>((kSmemMax - fixed) / stage_bytes);
+  // a convolution whose expanded weight is one tile wide and fits beside at least four activation stages keeps
+  // it in shared memory: the copy unit then moves 128 rows per 64-k block instead of 128 + bn
+  size_t stage_bytes = kABytes + p.b_bytes;
+  size_t resident = 0;
+  p.b_res = 0;
+  if (p.conv && !pair && p.n_tiles == 1) {
+    const size_t need = static_cast<size_t>(p.k_blocks) * p.passes * p.b_bytes;
+    if (fixed + need + 4 * kABytes <= kSmemMax && need < (1u << 20)) {
+      p.b_res = 1;
+      resident = need;
+      stage_bytes = kABytes;
+    }
+  }
+#ifdef DIMQ_B200_DIAG
+  if ((g_dense_diag & 16384) && p.b_res) { p.b_res = 0; resident = 0; stage_bytes = kABytes + p.b_bytes; }
+#endif
+  int stages = static_cast<int>((kSmemMax - fixed - resident) / stage_bytes);
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 3) return DIMQ_ERR_UNSUPPORTED;
   p.stages = stages;
-  const size_t smem = fixed + stages * stage_bytes;
+  const size_t smem = fixed + resident + stages * stage_bytes;
   const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
   if (tiles >= 0x7FFFFFFF) return DIMQ_ERR_TOO_LARGE;
   const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
@@ -1565,6 +1599,13 @@ int launch_conv2d_wq_dense(const void* x, int x_dtype, const dimq_wq_weight* w, 
       if (score > best_score) { best_score = score; best_tw = tw; best_th = th; best_tb = tb; }
     }
   }
+#ifdef DIMQ_B200_DIAG
+  if (g_dense_diag >> 16) {   // timing experiments: forced tile shape, log2(tw) | log2(th) << 4 in bits 16..23
+    best_tw = 1 << ((g_dense_diag >> 16) & 15);
+    best_th = 1 << ((g_dense_diag >> 20) & 15);
+    best_tb = kBM / (best_tw * best_th);
+  }
+#endif
   DenseParams p;
   memset(&p, 0, sizeof(p));
   DenseMaps maps;
