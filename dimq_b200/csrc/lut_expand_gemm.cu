@@ -15,14 +15,14 @@
 // GEMM's time) and the main loop is a plain two-operand TMA -> MMA pipeline.
 //
 // Tile: 128 activation rows (UMMA M, one TMEM lane each) x up to 256 weight rows (UMMA N = 256 is the
-// shape whose four MMAs per 64-k block run at the tensor pipe's full rate: measured 589 cycles per
-// block, commit included, against 512 ideal; N = 192 needs 573 cycles for 3/4 of the work).
+// shape whose four MMAs per 64-k block fill the tensor pipe: 512 cycles per block; narrower shapes pay
+// about 240 cycles of wait / elect / commit per block beside 48-64 cycles per MMA).  For a GEMM whose tile
+// counts favour it, two CTAs of a cluster share a 256 x 256 tile (cta_group::2, see the helpers below).
 // Warp roles (384 threads): warp 0 fetches the tiles (for convolutions only the activation tiles of the even
-// k blocks, warp 11 those of the odd ones and warp 10 the weight tiles: with one producer warp the issue of a
-// stage's two copies plus the tap arithmetic took 680 cycles per 64-k block and starved the MMA warp),
-// warp 1 MMA issuer + TMEM owner,
-// warps 2-9 epilogue (two per TMEM lane quarter, alternating 32-column chunks).  Persistent grid, one CTA
-// per SM.
+// k blocks, warp 11 those of the odd ones and warp 10 the weight tiles - once, when the whole weight fits in
+// shared memory: with one producer warp the issue of a stage's two copies plus the tap arithmetic took 680
+// cycles per 64-k block and starved the MMA warp), warp 1 MMA issuer + TMEM owner, warps 2-9 epilogue (two
+// per TMEM lane quarter, alternating 32-column chunks).  Persistent grid, one CTA per SM.
 // The accumulator is y-oriented (lane = output row m, column = output feature n): an epilogue thread
 // holds 32 consecutive features of one row, adds bias / activation / residual, writes them as 16-byte
 // vectors into a swizzled staging tile and one TMA store per 32 x 32 chunk writes y.
