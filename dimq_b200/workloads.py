@@ -148,10 +148,13 @@ class DIMQViT(nn.Module):
         g = cfg["image"] // p
         # patch embedding (dense bf16): a stride-p conv is a GEMM over flattened (c, kh, kw) patches
         patches = images.to(self.act_dtype).view(b, 3, g, p, g, p).permute(0, 2, 4, 1, 3, 5).reshape(b * g * g, 3 * p * p)
-        x = torch.addmm(self._t("patch_embed.bias"), patches, self._t("patch_embed.weight").view(hid, -1).t())
-        x = torch.cat([self._t("cls_token").expand(b, -1, -1), x.view(b, g * g, hid)], dim=1) + self._t("pos_embed")
-        x = x.contiguous()
-        t = x.shape[1]
+        emb = torch.addmm(self._t("patch_embed.bias"), patches, self._t("patch_embed.weight").view(hid, -1).t())
+        # tokens = [cls | patches] + pos_embed, written in place (one pass instead of a cat and an add)
+        t = g * g + 1
+        pos = self._t("pos_embed")
+        x = torch.empty(b, t, hid, dtype=self.act_dtype, device=images.device)
+        x[:, :1] = self._t("cls_token") + pos[:, :1]
+        torch.add(emb.view(b, g * g, hid), pos[:, 1:], out=x[:, 1:])
         if self.fuse_epilogues:
             for i in range(cfg["layers"]):
                 pre = f"blocks.{i}."
