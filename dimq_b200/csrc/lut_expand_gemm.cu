@@ -18,11 +18,12 @@
 // shape whose four MMAs per 64-k block fill the tensor pipe: 512 cycles per block; narrower shapes pay
 // about 240 cycles of wait / elect / commit per block beside 48-64 cycles per MMA).  For a GEMM whose tile
 // counts favour it, two CTAs of a cluster share a 256 x 256 tile (cta_group::2, see the helpers below).
-// Warp roles (384 threads): warp 0 fetches the tiles (for convolutions only the activation tiles of the even
-// k blocks, warp 11 those of the odd ones and warp 10 the weight tiles - once, when the whole weight fits in
-// shared memory: with one producer warp the issue of a stage's two copies plus the tap arithmetic took 680
-// cycles per 64-k block and starved the MMA warp), warp 1 MMA issuer + TMEM owner, warps 2-9 epilogue (two
-// per TMEM lane quarter, alternating 32-column chunks).  Persistent grid, one CTA per SM.
+// Warp roles (384 threads): warps 0, 10 and 11 fetch the tiles - a warp gets through one copy instruction in
+// ~330 cycles whatever its size, so the copies are spread: in a GEMM the three take the k blocks in turn (both
+// copies of a block from one warp); in a convolution warp 0 takes the activation tiles of the even k blocks,
+// warp 11 those of the odd ones and warp 10 the weight tiles (once, when the whole weight fits in shared
+// memory) - warp 1 MMA issuer + TMEM owner, warps 2-9 epilogue (two per TMEM lane quarter, alternating
+// 32-column chunks).  Persistent grid, one CTA per SM.
 // The accumulator is y-oriented (lane = output row m, column = output feature n): an epilogue thread
 // holds 32 consecutive features of one row, adds bias / activation / residual, writes them as 16-byte
 // vectors into a swizzled staging tile and one TMA store per 32 x 32 chunk writes y.
@@ -38,7 +39,7 @@ using namespace tc;
 constexpr int kBM = 128;         // activation rows (output pixels) per tile
 constexpr int kBK = 64;          // k per pipeline stage: 128 bytes of 16-bit elements
 constexpr int kMaxStages = 8;
-constexpr int kPairBlockCycles = 675, kSingleBlockCycles = 750;   // per 64-k block of a 256-wide tile (measured: a pair is ~10 % faster per block)
+constexpr int kPairBlockCycles = 630, kSingleBlockCycles = 750;   // per 64-k block of a 256-wide tile (measured: a pair is ~15 % faster per block)
 constexpr int kAccStages = 2;
 constexpr int kAccCols = 256;    // TMEM columns per accumulator buffer
 constexpr int kTmemCols = 512;
@@ -340,7 +341,7 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
   const uint32_t tmem_base = hdr->tmem_base;
   volatile uint32_t* abort_flag = &hdr->abort_flag;
 
-  if (warp == 0 || (warp >= 2 + kEpiWarps && p.conv)) {
+  if (warp == 0 || warp >= 2 + kEpiWarps) {
     // ===================== TMA producers (whole warp loops, one elected lane issues) =====================
     // Convolutions: warp 0 fetches the activation tiles, the last warp the weight tiles; each arms a stage's
     // barrier with its own bytes, so a stage is full when both copies have landed, and the issue cost of a
@@ -348,12 +349,22 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
     // back to back, which keeps them in stage order in the copy queue (measured 2-6 % faster there).
     // A 4-D activation copy costs its issuing warp about 400 cycles, so in a convolution two warps take
     // the even and the odd k blocks of the sequence.
+    // GEMM: the three producer warps take the k blocks of the sequence in turn (both copies of a block from
+    // one warp, back to back): a warp gets through one copy instruction in ~330 cycles whatever its size
+    // (measured alone: 64, 128 or 256 rows per copy, 1-D or 2-D, all 334-363 cycles per copy and warp, and
+    // N warps issue N times as many), so one warp issuing two copies per block held a block at ~750 cycles.
     const bool is_a = warp != 2 + kEpiWarps;
     const uint32_t a_par = warp == 0 ? 0u : 1u;
+    const uint32_t gemm_turn = warp == 0 ? 0u : static_cast<uint32_t>(warp - (1 + kEpiWarps));   // 0, 1, 2
+    uint32_t turn = 0;
     const uint32_t my_bytes = !p.conv ? stage_bytes : is_a ? kABytes : p.b_bytes;
     // programmatic dependent launch: the expansion kernel before this one in the stream must have finished
     // before the first weight tile is read (the activations were complete before that kernel started)
     if (!is_a || !p.conv) asm volatile("griddepcontrol.wait;" ::: "memory");
+    uint32_t n_turns = 3;
+#ifdef DIMQ_B200_DIAG
+    if (p.diag & 32768) n_turns = 1;   // timing experiments: warp 0 issues every block's copies
+#endif
     uint32_t stage = 0, phase = 0, issued = 0;
     bool ok = true;
     if (!is_a && p.b_res) {
@@ -384,6 +395,15 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
         // convolution: k block kb = (tap (kh, kw), channel block cb); the tap's input offset is kept by carrying
         int kh = 0, kw = 0, cb = 0;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!p.conv) {
+            const bool mine = turn == gemm_turn;
+            if (++turn == n_turns) turn = 0;
+            if (!mine) {   // another producer warp's k block
+              ++issued;
+              if (++stage == n_st) { stage = 0; phase ^= 1u; }
+              continue;
+            }
+          }
           if (p.conv && is_a && (issued & 1u) != a_par) {   // the other activation producer's k block
             ++issued;
             if (++stage == n_st) { stage = 0; phase ^= 1u; }
@@ -413,12 +433,7 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
             if (elect_one()) mbar_arrive(full);
           } else
 #endif
-          if (!is_a) {
-            if (elect_one()) {
-              mbar_arrive_expect_tx(full, my_bytes);
-              tma_load_2d(dst_a + kABytes, &maps.b, full, (pass * p.k_blocks + kb) * kBK, n_blk * p.bn);
-            }
-          } else if (!p.conv) {
+          if (!p.conv) {
             if constexpr (PAIR) {
               if (elect_one()) {
                 const uint32_t lead_full = map_to_cta(full, 0);
@@ -430,6 +445,11 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
             } else if (elect_one()) {
               mbar_arrive_expect_tx(full, my_bytes);
               tma_load_2d(dst_a, &maps.a[0], full, kb * kBK, m_blk * kBM);
+              tma_load_2d(dst_a + kABytes, &maps.b, full, (pass * p.k_blocks + kb) * kBK, n_blk * p.bn);
+            }
+          } else if (!is_a) {
+            if (elect_one()) {
+              mbar_arrive_expect_tx(full, my_bytes);
               tma_load_2d(dst_a + kABytes, &maps.b, full, (pass * p.k_blocks + kb) * kBK, n_blk * p.bn);
             }
           } else {
