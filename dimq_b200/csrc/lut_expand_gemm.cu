@@ -18,12 +18,11 @@
 // shape whose four MMAs per 64-k block fill the tensor pipe: 512 cycles per block; narrower shapes pay
 // about 240 cycles of wait / elect / commit per block beside 48-64 cycles per MMA).  For a GEMM whose tile
 // counts favour it, two CTAs of a cluster share a 256 x 256 tile (cta_group::2, see the helpers below).
-// Warp roles (384 threads): warps 0, 10 and 11 fetch the tiles - a warp gets through one copy instruction in
-// ~330 cycles whatever its size, so the copies are spread: in a GEMM the three take the k blocks in turn (both
-// copies of a block from one warp); in a convolution warp 0 takes the activation tiles of the even k blocks,
-// warp 11 those of the odd ones and warp 10 the weight tiles (once, when the whole weight fits in shared
-// memory) - warp 1 MMA issuer + TMEM owner, warps 2-9 epilogue (two per TMEM lane quarter, alternating
-// 32-column chunks).  Persistent grid, one CTA per SM.
+// Warp roles (448 threads): warp 0 and warps 10-13 fetch the tiles.  A warp gets through one copy instruction
+// in ~330 cycles whatever its size (a 4-D box: ~555), so the producers take the k blocks of the CTA's sequence
+// in turn, the owner of a block issuing both of its copies (never more producers than ring stages).  Warp 1 MMA
+// issuer + TMEM owner, warps 2-9 epilogue (two per TMEM lane quarter, alternating 32-column chunks).
+// Persistent grid, one CTA per SM.
 // The accumulator is y-oriented (lane = output row m, column = output feature n): an epilogue thread
 // holds 32 consecutive features of one row, adds bias / activation / residual, writes them as 16-byte
 // vectors into a swizzled staging tile and one TMA store per 32 x 32 chunk writes y.
@@ -44,7 +43,8 @@ constexpr int kAccStages = 2;
 constexpr int kAccCols = 256;    // TMEM columns per accumulator buffer
 constexpr int kTmemCols = 512;
 constexpr int kEpiWarps = 8;
-constexpr int kThreads = (2 + kEpiWarps + 2) * 32;   // activation producer, MMA issuer, epilogue warps, weight producer, second activation producer
+constexpr int kProducers = 5;                         // warp 0 and the four warps after the epilogue warps
+constexpr int kThreads = (1 + kProducers + kEpiWarps) * 32;
 constexpr uint32_t kABytes = kBM * kBK * 2;   // 16 KB
 constexpr int kHeaderBytes = 1024;
 constexpr int kBiasBytes = kEpiWarps * 128;
@@ -69,6 +69,7 @@ struct DenseParams {
   int tw, th, tb, tiles_w, tiles_h;
   int OW, OH, Bn;
   int stride, pad_h, pad_w, dil_h, dil_w, KW, c_blocks;
+  int kps;                  // 64-k blocks per ring stage (1 or 2): narrow tiles amortise the per-stage wait / commit over 8 MMAs
   int b_res;                // convolution: the whole expanded weight (one tile wide) stays in shared memory
   int pair;                 // 1: CTA pairs (cta_group::2), GEMM only; m_tiles then counts 256-row pairs of blocks
 #ifdef DIMQ_B200_DIAG
@@ -298,7 +299,8 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
   // accesses below in the shared state space (no generic loads and stores)
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   // b_res: [stages: A 16 KB] [the weight: k blocks x bn*128 B] [header] ...
-  const uint32_t stage_bytes = p.b_res ? kABytes : kABytes + p.b_bytes;
+  const uint32_t sub_bytes = p.b_res ? kABytes : kABytes + p.b_bytes;   // one 64-k block of a stage: A tile, then B tile
+  const uint32_t stage_bytes = static_cast<uint32_t>(p.kps) * sub_bytes;
   const uint32_t n_st = static_cast<uint32_t>(p.stages);
   unsigned char* b_resident = smem + n_st * stage_bytes;
   DenseHeader* hdr = reinterpret_cast<DenseHeader*>(
@@ -316,7 +318,7 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
   const int tile_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
   if (tid == 0) {
-    for (int s = 0; s < kMaxStages; ++s) { mbar_init(smem_u32(&hdr->full[s]), p.conv && !p.b_res ? 2 : 1); mbar_init(smem_u32(&hdr->empty[s]), 1); }   // full: one arrival per producer warp
+    for (int s = 0; s < kMaxStages; ++s) { mbar_init(smem_u32(&hdr->full[s]), 1); mbar_init(smem_u32(&hdr->empty[s]), 1); }   // full: one arrival per producer warp
     for (int s = 0; s < kAccStages; ++s) { mbar_init(smem_u32(&hdr->d_full[s]), 1); mbar_init(smem_u32(&hdr->d_empty[s]), PAIR ? 2 * kEpiWarps : kEpiWarps); }
     mbar_init(smem_u32(&hdr->b_res_full), 1);
     hdr->abort_flag = 0u;
@@ -343,31 +345,25 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
 
   if (warp == 0 || warp >= 2 + kEpiWarps) {
     // ===================== TMA producers (whole warp loops, one elected lane issues) =====================
-    // Convolutions: warp 0 fetches the activation tiles, the last warp the weight tiles; each arms a stage's
-    // barrier with its own bytes, so a stage is full when both copies have landed, and the issue cost of a
-    // stage (tap arithmetic included) is split over two warps.  GEMM: warp 0 issues both copies of a stage
-    // back to back, which keeps them in stage order in the copy queue (measured 2-6 % faster there).
-    // A 4-D activation copy costs its issuing warp about 400 cycles, so in a convolution two warps take
-    // the even and the odd k blocks of the sequence.
-    // GEMM: the three producer warps take the k blocks of the sequence in turn (both copies of a block from
-    // one warp, back to back): a warp gets through one copy instruction in ~330 cycles whatever its size
-    // (measured alone: 64, 128 or 256 rows per copy, 1-D or 2-D, all 334-363 cycles per copy and warp, and
-    // N warps issue N times as many), so one warp issuing two copies per block held a block at ~750 cycles.
-    const bool is_a = warp != 2 + kEpiWarps;
-    const uint32_t a_par = warp == 0 ? 0u : 1u;
-    const uint32_t gemm_turn = warp == 0 ? 0u : static_cast<uint32_t>(warp - (1 + kEpiWarps));   // 0, 1, 2
-    uint32_t turn = 0;
-    const uint32_t my_bytes = !p.conv ? stage_bytes : is_a ? kABytes : p.b_bytes;
-    // programmatic dependent launch: the expansion kernel before this one in the stream must have finished
-    // before the first weight tile is read (the activations were complete before that kernel started)
-    if (!is_a || !p.conv) asm volatile("griddepcontrol.wait;" ::: "memory");
-    uint32_t n_turns = 3;
+    // The producer warps take the k blocks of the CTA's sequence in turn; the owner of a block arms its stage
+    // and issues both copies, back to back.  A warp gets through one copy instruction in ~330 cycles whatever
+    // its size (measured alone: 64, 128 or 256 rows per copy, 1-D or 2-D, 334-363 cycles per copy and warp;
+    // a 4-D box 554; N warps issue N times as many), so one warp issuing two copies per block held a GEMM
+    // block at ~750 cycles and a convolution block, tap arithmetic included, at ~850.
+    const uint32_t my_turn = warp == 0 ? 0u : static_cast<uint32_t>(warp - (1 + kEpiWarps));   // 0 .. kProducers - 1
+    // No more producers than stages: a warp's successive blocks must be at most one ring revolution apart, or its
+    // parity wait on a stage's `empty` barrier could be satisfied by the completion before the one it needs (five
+    // producers over a four-stage ring overwrote live stages and ended in "unspecified launch failure").
+    uint32_t n_turns = n_st < static_cast<uint32_t>(kProducers) ? n_st : static_cast<uint32_t>(kProducers), turn = 0;
 #ifdef DIMQ_B200_DIAG
     if (p.diag & 32768) n_turns = 1;   // timing experiments: warp 0 issues every block's copies
 #endif
+    // programmatic dependent launch: the expansion kernel before this one in the stream must have finished
+    // before the first weight tile is read (the activations were complete before that kernel started)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     uint32_t stage = 0, phase = 0, issued = 0;
     bool ok = true;
-    if (!is_a && p.b_res) {
+    if (p.b_res && my_turn == 1) {
       // resident weight: every k block's tile once, one barrier for all of them; no per-stage weight copies
       if (elect_one()) {
         const uint32_t bar = smem_u32(&hdr->b_res_full);
@@ -376,114 +372,92 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
           tma_load_2d(smem_u32(b_resident + static_cast<uint32_t>(kb) * p.b_bytes), &maps.b, bar, kb * kBK, 0);
       }
       __syncwarp();
-      ok = false;   // skips the stage loop below (nothing was given up: the status word stays clear)
     }
     STEM_ACC_DECL;
     STEM_CLK(t_all);
-#ifdef DIMQ_B200_DIAG
-    const bool skip = (is_a && (p.diag & 2)) || (!is_a && (p.diag & 1));
-#endif
     for (int t = tile0; t < num_tiles && ok; t += tile_step) {
       const int n_blk = t % p.n_tiles, m_blk = PAIR ? 2 * (t / p.n_tiles) + static_cast<int>(rank) : t / p.n_tiles;
       int ow0 = 0, oh0 = 0, b0 = 0;
-      if (p.conv && is_a) {
+      if (p.conv) {
         ow0 = (m_blk % p.tiles_w) * p.tw;
         oh0 = ((m_blk / p.tiles_w) % p.tiles_h) * p.th;
         b0 = (m_blk / (p.tiles_w * p.tiles_h)) * p.tb;
       }
+      int g = 0, sub = 0;      // k block of the tile (over all passes), position inside the current stage
+      bool mine = false;
+      uint32_t full = 0, dst = 0;
       for (int pass = 0; pass < p.passes && ok; ++pass) {
         // convolution: k block kb = (tap (kh, kw), channel block cb); the tap's input offset is kept by carrying
         int kh = 0, kw = 0, cb = 0;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!p.conv) {
-            const bool mine = turn == gemm_turn;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++g) {
+          if (sub == 0) {   // a new stage: its owner waits for it and arms it with the bytes of all its blocks
+            mine = turn == my_turn;
             if (++turn == n_turns) turn = 0;
-            if (!mine) {   // another producer warp's k block
-              ++issued;
-              if (++stage == n_st) { stage = 0; phase ^= 1u; }
-              continue;
+            if (mine) {
+              STEM_CLK(t_w);
+              if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->empty[stage]), phase ^ 1u, abort_flag, 0x1100u | stage))) { ok = false; break; }
+              STEM_ACC(1, t_w);
+              full = smem_u32(&hdr->full[stage]);
+              dst = smem_u32(smem + stage * stage_bytes);
+              const int left = total_kb - g;
+              const uint32_t bytes = static_cast<uint32_t>(left < p.kps ? left : p.kps) * sub_bytes;
+              if (elect_one()) {
+                if constexpr (PAIR) { if (rank == 0) mbar_arrive_expect_tx(full, 2 * bytes); }   // both CTAs' copies
+                else mbar_arrive_expect_tx(full, bytes);
+              }
+              __syncwarp();
             }
           }
-          if (p.conv && is_a && (issued & 1u) != a_par) {   // the other activation producer's k block
+          if (mine) {
+            STEM_CLK(t_is);
+            const uint32_t dst_a = dst + static_cast<uint32_t>(sub) * sub_bytes;
+            const int kcol_b = g * kBK;
+            if (!p.conv) {
+              if constexpr (PAIR) {
+                if (elect_one()) {
+                  const uint32_t lead_full = map_to_cta(full, 0);
+                  tma_load_2d_pair(dst_a, &maps.a[0], lead_full, kb * kBK, m_blk * kBM);
+                  tma_load_2d_pair(dst_a + kABytes, &maps.b, lead_full, kcol_b, n_blk * p.bn + static_cast<int>(rank) * (p.bn / 2));
+                }
+              } else if (elect_one()) {
+                tma_load_2d(dst_a, &maps.a[0], full, kb * kBK, m_blk * kBM);
+                tma_load_2d(dst_a + kABytes, &maps.b, full, kcol_b, n_blk * p.bn);
+              }
+            } else {
+              // input pixel = stride * out + tap offset.  With stride 2 the input is addressed through one
+              // tensor map per (row, column) parity, so the box stays dense; taps that fall outside the image
+              // read the zero fill.
+              const int dy = kh * p.dil_h - p.pad_h, dx = kw * p.dil_w - p.pad_w;
+              int map = 0, hy = oh0 + dy, wx = ow0 + dx;
+              if (p.stride == 2) {
+                const int py = dy & 1, px = dx & 1;
+                map = py * 2 + px;
+                hy = oh0 + ((dy - py) >> 1);
+                wx = ow0 + ((dx - px) >> 1);
+              }
+              if (elect_one()) {
+                tma_load_4d(dst_a, &maps.a[map], full, cb * kBK, wx, hy, b0);
+                if (!p.b_res) tma_load_2d(dst_a + kABytes, &maps.b, full, kcol_b, n_blk * p.bn);
+              }
+            }
+            __syncwarp();
+            STEM_ACC(2, t_is);
+          }
+          if (++sub == p.kps || g + 1 == total_kb) {   // the stage is complete (a tile's last stage may hold one block)
+            sub = 0;
             ++issued;
             if (++stage == n_st) { stage = 0; phase ^= 1u; }
-            if (++cb == p.c_blocks) {
-              cb = 0;
-              if (++kw == p.KW) { kw = 0; ++kh; }
-            }
-            continue;
           }
-          STEM_CLK(t_w);
-          if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->empty[stage]), phase ^ 1u, abort_flag, (is_a ? 0x1100u : 0x1600u) | stage))) { ok = false; break; }
-          STEM_ACC(1, t_w);
-          STEM_CLK(t_is);
-          const uint32_t full = smem_u32(&hdr->full[stage]);
-          const uint32_t dst_a = smem_u32(smem + stage * stage_bytes);
-#ifdef DIMQ_B200_DIAG
-          if (!p.conv && (p.diag & 3) != 0) {
-            if (elect_one()) {
-              if ((p.diag & 3) == 3) mbar_arrive(full);
-              else {
-                mbar_arrive_expect_tx(full, (p.diag & 3) == 1 ? kABytes : p.b_bytes);
-                if ((p.diag & 3) == 1) tma_load_2d(dst_a, &maps.a[0], full, kb * kBK, m_blk * kBM);
-                else tma_load_2d(dst_a + kABytes, &maps.b, full, (pass * p.k_blocks + kb) * kBK, n_blk * p.bn);
-              }
-            }
-          } else if (skip) {
-            if (elect_one()) mbar_arrive(full);
-          } else
-#endif
-          if (!p.conv) {
-            if constexpr (PAIR) {
-              if (elect_one()) {
-                const uint32_t lead_full = map_to_cta(full, 0);
-                if (rank == 0) mbar_arrive_expect_tx(full, 2 * my_bytes);   // both CTAs' copies of this stage
-                tma_load_2d_pair(dst_a, &maps.a[0], lead_full, kb * kBK, m_blk * kBM);
-                tma_load_2d_pair(dst_a + kABytes, &maps.b, lead_full, (pass * p.k_blocks + kb) * kBK,
-                                 n_blk * p.bn + static_cast<int>(rank) * (p.bn / 2));
-              }
-            } else if (elect_one()) {
-              mbar_arrive_expect_tx(full, my_bytes);
-              tma_load_2d(dst_a, &maps.a[0], full, kb * kBK, m_blk * kBM);
-              tma_load_2d(dst_a + kABytes, &maps.b, full, (pass * p.k_blocks + kb) * kBK, n_blk * p.bn);
-            }
-          } else if (!is_a) {
-            if (elect_one()) {
-              mbar_arrive_expect_tx(full, my_bytes);
-              tma_load_2d(dst_a + kABytes, &maps.b, full, (pass * p.k_blocks + kb) * kBK, n_blk * p.bn);
-            }
-          } else {
-            // input pixel = stride * out + tap offset.  With stride 2 the input is addressed through one
-            // tensor map per (row, column) parity, so the box stays dense; taps that fall outside the image
-            // read the zero fill.
-            const int dy = kh * p.dil_h - p.pad_h, dx = kw * p.dil_w - p.pad_w;
-            int map = 0, hy = oh0 + dy, wx = ow0 + dx;
-            if (p.stride == 2) {
-              const int py = dy & 1, px = dx & 1;
-              map = py * 2 + px;
-              hy = oh0 + ((dy - py) >> 1);
-              wx = ow0 + ((dx - px) >> 1);
-            }
-            if (elect_one()) {
-              mbar_arrive_expect_tx(full, my_bytes);
-              tma_load_4d(dst_a, &maps.a[map], full, cb * kBK, wx, hy, b0);
-            }
-            if (++cb == p.c_blocks) {
-              cb = 0;
-              if (++kw == p.KW) { kw = 0; ++kh; }
-            }
+          if (++cb == p.c_blocks) {
+            cb = 0;
+            if (++kw == p.KW) { kw = 0; ++kh; }
           }
-          __syncwarp();
-          STEM_ACC(2, t_is);
-          ++issued;
-          if (++stage == n_st) { stage = 0; phase ^= 1u; }
         }
       }
     }
     STEM_ACC(0, t_all);
     if (warp == 0) STEM_FLUSH(0, 3);
-    else if (!is_a) STEM_FLUSH(10, 3);
-    if (!ok && lane == 0 && !(!is_a && p.b_res)) {
+    if (!ok && lane == 0) {
       // gave up: wait (bounded) for the copies still in flight so that none lands after the CTA has exited
       const uint32_t n_back = issued < n_st ? issued : n_st;
       uint32_t s = stage, ph = phase;
@@ -510,27 +484,27 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
       STEM_ACC(1, t_w1);
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + as * kAccCols;
-      for (int kb = 0; kb < total_kb; ++kb) {
+      for (int g = 0; g < total_kb; g += p.kps) {
+        const int nblk = total_kb - g < p.kps ? total_kb - g : p.kps;   // 64-k blocks in this stage
         STEM_CLK(t_w2);
         if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->full[stage]), phase, abort_flag, 0x1300u | stage))) { ok = false; break; }
         STEM_ACC(2, t_w2);
         STEM_CLK(t_is);
         tc_fence_after();
         if (elect_one()) {
-          const uint64_t off = static_cast<uint64_t>(stage * (stage_bytes >> 4));
-          const uint64_t a_desc = a_desc0 + off;
-          const uint64_t b_desc = b_desc0 + (p.b_res ? static_cast<uint64_t>(static_cast<uint32_t>(kb) * (p.b_bytes >> 4)) : off);
-#ifdef DIMQ_B200_DIAG
-          if (!(p.diag & 8))
-#endif
+          for (int i = 0; i < nblk; ++i) {
+            const uint64_t off = static_cast<uint64_t>((stage * stage_bytes + static_cast<uint32_t>(i) * sub_bytes) >> 4);
+            const uint64_t a_desc = a_desc0 + off;
+            const uint64_t b_desc = b_desc0 + (p.b_res ? static_cast<uint64_t>(static_cast<uint32_t>(g + i) * (p.b_bytes >> 4)) : off);
 #pragma unroll
-          for (int j = 0; j < kBK / 16; ++j) {  // 16 k = 32 bytes inside the swizzled row (encoded >> 4)
-            if constexpr (PAIR)
-              mma_f16_ss_pair(d_tmem, a_desc + static_cast<uint64_t>(2 * j), b_desc + static_cast<uint64_t>(2 * j), p.idesc,
-                              (kb | j) ? 1u : 0u);
-            else
-              mma_f16_ss(d_tmem, a_desc + static_cast<uint64_t>(2 * j), b_desc + static_cast<uint64_t>(2 * j), p.idesc,
-                         (kb | j) ? 1u : 0u);
+            for (int j = 0; j < kBK / 16; ++j) {  // 16 k = 32 bytes inside the swizzled row (encoded >> 4)
+              if constexpr (PAIR)
+                mma_f16_ss_pair(d_tmem, a_desc + static_cast<uint64_t>(2 * j), b_desc + static_cast<uint64_t>(2 * j), p.idesc,
+                                (g | i | j) ? 1u : 0u);
+              else
+                mma_f16_ss(d_tmem, a_desc + static_cast<uint64_t>(2 * j), b_desc + static_cast<uint64_t>(2 * j), p.idesc,
+                           (g | i | j) ? 1u : 0u);
+            }
           }
           // frees the stage (in both CTAs of a pair) when these MMAs have read it
           if constexpr (PAIR) mma_commit_pair(smem_u32(&hdr->empty[stage]));
@@ -871,23 +845,36 @@ int launch_dense(DenseMaps& maps, DenseParams& p, const void* scratch, int64_t K
     return DIMQ_ERR_DRIVER;
   const int es = y_dtype == DIMQ_F32 ? 4 : 2;
   const size_t fixed = 1024 + kHeaderBytes + kBiasBytes + static_cast<size_t>(kEpiWarps) * 32 * 32 * es;
-  // a convolution whose expanded weight is one tile wide and fits beside at least four activation stages keeps
-  // it in shared memory: the copy unit then moves 128 rows per 64-k block instead of 128 + bn
-  size_t stage_bytes = kABytes + p.b_bytes;
-  size_t resident = 0;
-  p.b_res = 0;
-  if (p.conv && !pair && p.n_tiles == 1) {
-    const size_t need = static_cast<size_t>(p.k_blocks) * p.passes * p.b_bytes;
-    if (fixed + need + 4 * kABytes <= kSmemMax && need < (1u << 20)) {
-      p.b_res = 1;
-      resident = need;
-      stage_bytes = kABytes;
-    }
-  }
+  // Narrow tiles (bn <= 128) put two 64-k blocks into a ring stage: the MMA warp's wait / elect / commit of a
+  // stage costs ~240 cycles beside 48-64 per MMA, so eight MMAs per stage nearly halve its time per block.
+  // A convolution whose expanded weight is one tile wide and fits beside the activation stages keeps it in
+  // shared memory: no per-stage weight copies.
+  p.kps = (!pair && p.bn <= 128) ? 2 : 1;
 #ifdef DIMQ_B200_DIAG
-  if ((g_dense_diag & 16384) && p.b_res) { p.b_res = 0; resident = 0; stage_bytes = kABytes + p.b_bytes; }
+  if (g_dense_diag & 65536) p.kps = 1;   // timing experiments: one block per stage
 #endif
-  int stages = static_cast<int>((kSmemMax - fixed - resident) / stage_bytes);
+  size_t stage_bytes = 0, resident = 0;
+  int stages = 0;
+  for (;;) {
+    p.b_res = 0;
+    resident = 0;
+    size_t sub = kABytes + p.b_bytes;
+    if (p.conv && !pair && p.n_tiles == 1) {
+      const size_t need = static_cast<size_t>(p.k_blocks) * p.passes * p.b_bytes;
+      if (fixed + need + 3 * static_cast<size_t>(p.kps) * kABytes <= kSmemMax && need < (1u << 20)) {
+        p.b_res = 1;
+        resident = need;
+        sub = kABytes;
+      }
+    }
+#ifdef DIMQ_B200_DIAG
+    if ((g_dense_diag & 16384) && p.b_res) { p.b_res = 0; resident = 0; sub = kABytes + p.b_bytes; }
+#endif
+    stage_bytes = static_cast<size_t>(p.kps) * sub;
+    stages = static_cast<int>((kSmemMax - fixed - resident) / stage_bytes);
+    if (stages >= 3 || p.kps == 1) break;
+    p.kps = 1;   // two blocks per stage do not leave three stages: one block per stage
+  }
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 3) return DIMQ_ERR_UNSUPPORTED;
   p.stages = stages;
