@@ -475,6 +475,8 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
     bool ok = !PAIR || rank == 0;
     const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem));
     const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(p.b_res ? b_resident : smem + kABytes));
+    const uint32_t a_lo0 = static_cast<uint32_t>(a_desc0), a_hi = static_cast<uint32_t>(a_desc0 >> 32);
+    const uint32_t b_lo0 = static_cast<uint32_t>(b_desc0), b_hi = static_cast<uint32_t>(b_desc0 >> 32);
     if (p.b_res && ok && !__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&hdr->b_res_full), 0u, abort_flag, 0x1A00u))) ok = false;
     STEM_ACC_DECL;
     STEM_CLK(t_all);
@@ -491,19 +493,23 @@ lut_dense_tc_kernel(const __grid_constant__ DenseMaps maps, const DenseParams p)
         STEM_ACC(2, t_w2);
         STEM_CLK(t_is);
         tc_fence_after();
+        // descriptor low words (start address >> 4, 14 bits: shared addresses stay below 256 KB, so adding offsets
+        // never carries out of the field); the high words never change
+        const uint32_t a_lo = a_lo0 + ((stage * stage_bytes) >> 4);
+        const uint32_t b_lo = p.b_res ? b_lo0 + static_cast<uint32_t>(g) * (p.b_bytes >> 4) : b_lo0 + ((stage * stage_bytes) >> 4);
+        const uint32_t b_step = p.b_res ? p.b_bytes >> 4 : sub_bytes >> 4;
         if (elect_one()) {
-          for (int i = 0; i < nblk; ++i) {
-            const uint64_t off = static_cast<uint64_t>((stage * stage_bytes + static_cast<uint32_t>(i) * sub_bytes) >> 4);
-            const uint64_t a_desc = a_desc0 + off;
-            const uint64_t b_desc = b_desc0 + (p.b_res ? static_cast<uint64_t>(static_cast<uint32_t>(g + i) * (p.b_bytes >> 4)) : off);
 #pragma unroll
-            for (int j = 0; j < kBK / 16; ++j) {  // 16 k = 32 bytes inside the swizzled row (encoded >> 4)
-              if constexpr (PAIR)
-                mma_f16_ss_pair(d_tmem, a_desc + static_cast<uint64_t>(2 * j), b_desc + static_cast<uint64_t>(2 * j), p.idesc,
-                                (g | i | j) ? 1u : 0u);
-              else
-                mma_f16_ss(d_tmem, a_desc + static_cast<uint64_t>(2 * j), b_desc + static_cast<uint64_t>(2 * j), p.idesc,
-                           (g | i | j) ? 1u : 0u);
+          for (int i = 0; i < 2; ++i) {      // kps <= 2
+            if (i < nblk) {
+              const uint32_t al = a_lo + static_cast<uint32_t>(i) * (sub_bytes >> 4), bl = b_lo + static_cast<uint32_t>(i) * b_step;
+#pragma unroll
+              for (int j = 0; j < kBK / 16; ++j) {  // 16 k = 32 bytes inside the swizzled row (encoded >> 4)
+                const uint64_t a_desc = (static_cast<uint64_t>(a_hi) << 32) | (al + 2u * j);
+                const uint64_t b_desc = (static_cast<uint64_t>(b_hi) << 32) | (bl + 2u * j);
+                if constexpr (PAIR) mma_f16_ss_pair(d_tmem, a_desc, b_desc, p.idesc, (g | i | j) ? 1u : 0u);
+                else mma_f16_ss(d_tmem, a_desc, b_desc, p.idesc, (g | i | j) ? 1u : 0u);
+              }
             }
           }
           // frees the stage (in both CTAs of a pair) when these MMAs have read it
