@@ -684,8 +684,34 @@ lut_expand_kernel(const uint8_t* __restrict__ packed, const void* __restrict__ c
   // and it waits (griddepcontrol.wait) before it reads what this kernel writes
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int64_t units_per_row = K / 32;
+  const int64_t total = rows * units_per_row;
   const int64_t u = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
-  if (u >= rows * units_per_row) return;
+  // Up to 16-entry codebooks: the codewords of the groups this block's rows belong to are converted once
+  // into a shared-memory table (hi | lo << 16), so an index costs one shared-memory read instead of a global
+  // read and two conversions.  A block covers at most 256 * 32 / 64 = 128 rows, i.e. at most 129 groups.
+  constexpr bool kTable = BITS <= 4;
+  __shared__ uint32_t tbl[kTable ? 129 * 16 : 1];
+  int64_t g_first = 0;
+  if (kTable) {
+    const int64_t u_first = static_cast<int64_t>(blockIdx.x) * 256;
+    const int64_t u_last = u_first + 255 < total - 1 ? u_first + 255 : total - 1;
+    g_first = (u_first / units_per_row) / group_rows;
+    const int n_groups = static_cast<int>((u_last / units_per_row) / group_rows - g_first) + 1;
+    for (int i = threadIdx.x; i < n_groups * 16; i += 256) {
+      const int e = i & 15;
+      const float c = e < entries ? load_as_float(codebooks, cb_dtype, (g_first + (i >> 4)) * entries + e) : 0.0f;
+      uint32_t v;
+      if (fmt == 0) {
+        v = __half_as_ushort(__float2half_rn(c));
+      } else {
+        const __nv_bfloat16 h = __float2bfloat16_rn(c);
+        v = __bfloat16_as_ushort(h) | (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(c - __bfloat162float(h)))) << 16);
+      }
+      tbl[i] = v;
+    }
+    __syncthreads();
+  }
+  if (u >= total) return;
   const int64_t row = u / units_per_row;
   const int64_t k0 = (u - row * units_per_row) * 32;
   const uint32_t* src = reinterpret_cast<const uint32_t*>(packed + (row * K + k0) * BITS / 8);
@@ -693,6 +719,7 @@ lut_expand_kernel(const uint8_t* __restrict__ packed, const void* __restrict__ c
 #pragma unroll
   for (int i = 0; i < BITS; ++i) w[i] = __ldg(src + i);
   const int64_t cb0 = (row / group_rows) * entries;
+  const uint32_t* my_tbl = tbl + (kTable ? static_cast<int>(row / group_rows - g_first) * 16 : 0);
   uint16_t hi[32], lo[32];
 #pragma unroll
   for (int i = 0; i < 32; ++i) {
@@ -700,14 +727,20 @@ lut_expand_kernel(const uint8_t* __restrict__ packed, const void* __restrict__ c
     uint32_t idx = w[word] >> sh;
     if (sh + BITS > 32) idx |= w[word + 1 < BITS ? word + 1 : word] << (32 - sh);
     idx &= (1u << BITS) - 1u;
-    const float c = idx < static_cast<uint32_t>(entries) ? load_as_float(codebooks, cb_dtype, cb0 + idx) : 0.0f;
-    if (fmt == 0) {
-      hi[i] = __half_as_ushort(__float2half_rn(c));
-      lo[i] = 0;
+    if (kTable) {
+      const uint32_t v = my_tbl[idx];      // entries past the codebook's count hold zero
+      hi[i] = static_cast<uint16_t>(v);
+      lo[i] = static_cast<uint16_t>(v >> 16);
     } else {
-      const __nv_bfloat16 h = __float2bfloat16_rn(c);
-      hi[i] = __bfloat16_as_ushort(h);
-      lo[i] = __bfloat16_as_ushort(__float2bfloat16_rn(c - __bfloat162float(h)));
+      const float c = idx < static_cast<uint32_t>(entries) ? load_as_float(codebooks, cb_dtype, cb0 + idx) : 0.0f;
+      if (fmt == 0) {
+        hi[i] = __half_as_ushort(__float2half_rn(c));
+        lo[i] = 0;
+      } else {
+        const __nv_bfloat16 h = __float2bfloat16_rn(c);
+        hi[i] = __bfloat16_as_ushort(h);
+        lo[i] = __bfloat16_as_ushort(__float2bfloat16_rn(c - __bfloat162float(h)));
+      }
     }
   }
   uint16_t* dst = out + row * (K * passes) + k0;
@@ -1013,7 +1046,18 @@ int launch_linear_wq_dense(const void* x, int x_dtype, const dimq_wq_weight* w, 
   if (!out_map(encode, &maps.y, y, y_dtype, 2, odims, obox)) return DIMQ_ERR_DRIVER;
   int rc = expand(w, w->packed, N, K, x_dtype == DIMQ_BF16 ? 1 : 0, p.passes, workspace, st);
   if (rc != DIMQ_OK) return rc;
-  return launch_dense(maps, p, workspace, K, x_dtype, bias, bias_dtype, residual, y_dtype, epilogue, st);
+  rc = launch_dense(maps, p, workspace, K, x_dtype, bias, bias_dtype, residual, y_dtype, epilogue, st);
+  if (rc > 0 && p.pair) {
+    // the cluster launch was refused (a positive status is the cudaError_t of the launch: e.g. a partition of the
+    // GPU that cannot co-schedule CTA pairs): the same problem on single CTAs, over the weight already expanded
+    (void)cudaGetLastError();
+    p.pair = 0;
+    p.m_tiles = static_cast<int>((M + kBM - 1) / kBM);
+    p.bn = choose_bn(p.m_tiles, N);
+    p.n_tiles = static_cast<int>((N + p.bn - 1) / p.bn);
+    rc = launch_dense(maps, p, workspace, K, x_dtype, bias, bias_dtype, residual, y_dtype, epilogue, st);
+  }
+  return rc;
 }
 
 // ---- stem convolution: 3 input channels, stride 2 ----------------------------------------------------
