@@ -10,8 +10,11 @@ namespace {
 constexpr int kWarpsPerBlock = 8;
 constexpr int kMaxVec = 4;  // 16-byte vectors per lane: rows of up to 32 * 4 * 8 = 1024 elements
 
+// One warp per row.  The row stays in registers as packed 16-bit vectors (converted again in each of the
+// three passes) rather than as floats: the kernel waits on memory latency, so what counts is how many
+// warps - bytes in flight - an SM holds (48 with 40 registers per thread; 32 with the float copy).
 template <typename T>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, 6)
 add_layer_norm_kernel(const T* __restrict__ x, const T* __restrict__ delta, const T* __restrict__ gamma,
                       const T* __restrict__ beta, T* __restrict__ x_out, T* __restrict__ h_out, int64_t rows,
                       int cols, float eps) {
@@ -19,31 +22,27 @@ add_layer_norm_kernel(const T* __restrict__ x, const T* __restrict__ delta, cons
   const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int vecs = cols / 8;  // vectors per row
-  float v[kMaxVec][8];
+  uint4 q[kMaxVec];
+#pragma unroll
+  for (int i = 0; i < kMaxVec; ++i) {
+    const int vi = i * 32 + lane;
+    if (vi < vecs) q[i] = __ldg(reinterpret_cast<const uint4*>(x + row * cols) + vi);
+  }
   float sum = 0.0f;
 #pragma unroll
   for (int i = 0; i < kMaxVec; ++i) {
     const int vi = i * 32 + lane;
     if (vi < vecs) {
-      const uint4 q = __ldg(reinterpret_cast<const uint4*>(x + row * cols) + vi);
-      const T* e = reinterpret_cast<const T*>(&q);
+      T* e = reinterpret_cast<T*>(&q[i]);
       if (delta != nullptr) {
         const uint4 d = __ldg(reinterpret_cast<const uint4*>(delta + row * cols) + vi);
         const T* de = reinterpret_cast<const T*>(&d);
-        uint4 o;
-        T* oe = reinterpret_cast<T*>(&o);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          oe[j] = from_float<T>(to_float<T>(e[j]) + to_float<T>(de[j]));  // the sum is stored in T first
-          v[i][j] = to_float<T>(oe[j]);
-        }
-        reinterpret_cast<uint4*>(x_out + row * cols)[vi] = o;
-      } else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[i][j] = to_float<T>(e[j]);
+        for (int j = 0; j < 8; ++j) e[j] = from_float<T>(to_float<T>(e[j]) + to_float<T>(de[j]));  // the sum is stored in T first
+        reinterpret_cast<uint4*>(x_out + row * cols)[vi] = q[i];
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) sum += v[i][j];
+      for (int j = 0; j < 8; ++j) sum += to_float<T>(e[j]);
     }
   }
 #pragma unroll
@@ -53,8 +52,9 @@ add_layer_norm_kernel(const T* __restrict__ x, const T* __restrict__ delta, cons
 #pragma unroll
   for (int i = 0; i < kMaxVec; ++i) {
     if (i * 32 + lane < vecs) {
+      const T* e = reinterpret_cast<const T*>(&q[i]);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { const float d = v[i][j] - mean; sq = fmaf(d, d, sq); }
+      for (int j = 0; j < 8; ++j) { const float d = to_float<T>(e[j]) - mean; sq = fmaf(d, d, sq); }
     }
   }
 #pragma unroll
@@ -68,10 +68,11 @@ add_layer_norm_kernel(const T* __restrict__ x, const T* __restrict__ delta, cons
       const uint4 b = __ldg(reinterpret_cast<const uint4*>(beta) + vi);
       const T* ge = reinterpret_cast<const T*>(&g);
       const T* be = reinterpret_cast<const T*>(&b);
+      const T* e = reinterpret_cast<const T*>(&q[i]);
       uint4 o;
       T* oe = reinterpret_cast<T*>(&o);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) oe[j] = from_float<T>(fmaf((v[i][j] - mean) * rstd, to_float<T>(ge[j]), to_float<T>(be[j])));
+      for (int j = 0; j < 8; ++j) oe[j] = from_float<T>(fmaf((to_float<T>(e[j]) - mean) * rstd, to_float<T>(ge[j]), to_float<T>(be[j])));
       reinterpret_cast<uint4*>(h_out + row * cols)[vi] = o;
     }
   }
