@@ -338,6 +338,75 @@ extern "C" int dimq_im2col(const void* x, int dtype, const dimq_conv_geom* geom,
   return launch_status();
 }
 
+namespace dimq {
+namespace {
+
+// y[b][p][c] = T(x[b][c][p]) for the 3 channels of an image batch (p = pixel index): NCHW fp32 / 16-bit in,
+// NHWC 16-bit out.  One thread = 8 consecutive pixels: two 16-byte loads per channel plane (one for 16-bit
+// input), three 16-byte stores of the 24 interleaved values.
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(kAuxThreads)
+images_to_nhwc_kernel(const TI* __restrict__ x, TO* __restrict__ y, int64_t batch, int64_t pixels) {
+  const int64_t per_image = pixels / 8;
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * kAuxThreads + threadIdx.x;
+  if (i >= batch * per_image) return;
+  const int64_t b = i / per_image, p0 = (i - b * per_image) * 8;
+  float v[3][8];
+#pragma unroll
+  for (int c = 0; c < 3; ++c) {
+    const TI* src = x + (b * 3 + c) * pixels + p0;
+    if constexpr (sizeof(TI) == 4) {
+      const float4 a = __ldg(reinterpret_cast<const float4*>(src));
+      const float4 d = __ldg(reinterpret_cast<const float4*>(src) + 1);
+      v[c][0] = a.x; v[c][1] = a.y; v[c][2] = a.z; v[c][3] = a.w; v[c][4] = d.x; v[c][5] = d.y; v[c][6] = d.z; v[c][7] = d.w;
+    } else {
+      const uint4 q = __ldg(reinterpret_cast<const uint4*>(src));
+      const TI* h = reinterpret_cast<const TI*>(&q);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[c][j] = to_float<TI>(h[j]);
+    }
+  }
+  __align__(16) TO o[24];
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int c = 0; c < 3; ++c) o[3 * j + c] = from_float<TO>(v[c][j]);
+  uint4* dst = reinterpret_cast<uint4*>(y + (b * pixels + p0) * 3);
+#pragma unroll
+  for (int k = 0; k < 3; ++k) dst[k] = reinterpret_cast<const uint4*>(o)[k];
+}
+
+}  // namespace
+}  // namespace dimq
+
+extern "C" int dimq_images_to_nhwc(const void* x, int x_dtype, void* y, int y_dtype, int64_t batch, int64_t height,
+                                   int64_t width, void* stream) {
+  if (!valid_dtype(x_dtype) || (y_dtype != DIMQ_BF16 && y_dtype != DIMQ_F16)) return DIMQ_ERR_BAD_DTYPE;
+  if (batch < 0 || height <= 0 || width <= 0) return DIMQ_ERR_BAD_SIZE;
+  const int64_t pixels = height * width;
+  if (pixels % 8 != 0) return DIMQ_ERR_UNSUPPORTED;
+  if (batch == 0) return DIMQ_OK;
+  if (x == nullptr || y == nullptr) return DIMQ_ERR_NULL_POINTER;
+  if (!aligned(x, 16) || !aligned(y, 16)) return DIMQ_ERR_ALIGNMENT;
+  const int64_t total = batch * (pixels / 8);
+  const int64_t blocks = (total + kAuxThreads - 1) / kAuxThreads;
+  if (blocks > 0x7FFFFFFFll) return DIMQ_ERR_TOO_LARGE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>(blocks);
+#define DIMQ_IMG(TI, TO) images_to_nhwc_kernel<TI, TO><<<grid, kAuxThreads, 0, st>>>(static_cast<const TI*>(x), static_cast<TO*>(y), batch, pixels)
+  if (y_dtype == DIMQ_BF16) {
+    if (x_dtype == DIMQ_F32) DIMQ_IMG(float, __nv_bfloat16);
+    else if (x_dtype == DIMQ_F16) DIMQ_IMG(__half, __nv_bfloat16);
+    else DIMQ_IMG(__nv_bfloat16, __nv_bfloat16);
+  } else {
+    if (x_dtype == DIMQ_F32) DIMQ_IMG(float, __half);
+    else if (x_dtype == DIMQ_F16) DIMQ_IMG(__half, __half);
+    else DIMQ_IMG(__nv_bfloat16, __half);
+  }
+#undef DIMQ_IMG
+  return launch_status();
+}
+
 extern "C" int dimq_max_pool_nhwc(const void* x, void* y, int dtype, int64_t batch, int64_t height, int64_t width,
                                   int64_t channels, int kernel, int stride, int pad, void* stream) {
   if (dtype != DIMQ_BF16 && dtype != DIMQ_F16) return DIMQ_ERR_BAD_DTYPE;

@@ -733,6 +733,25 @@ def max_pool_nhwc(x: torch.Tensor, kernel: int, stride: int, padding: int) -> to
     return y
 
 
+def images_to_nhwc(images: torch.Tensor, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``images.to(dtype).contiguous(memory_format=torch.channels_last)`` for a contiguous NCHW batch of
+    3-channel images (fp32 / fp16 / bf16) in one pass of 16-byte loads and stores."""
+    require_extension()
+    _require_cuda(images, "images_to_nhwc")
+    if images.dim() != 4 or images.shape[1] != 3 or not images.is_contiguous() or (images.shape[2] * images.shape[3]) % 8:
+        raise RuntimeError("images_to_nhwc expects a contiguous [B, 3, H, W] tensor with H * W a multiple of 8")
+    if dtype not in (torch.bfloat16, torch.float16):
+        raise RuntimeError("images_to_nhwc writes bf16 or fp16")
+    b, _, h, w = images.shape
+    y = torch.empty((b, 3, h, w), dtype=dtype, device=images.device, memory_format=torch.channels_last)
+    with torch.cuda.device(images.device):
+        st = _lib.lib().dimq_images_to_nhwc(_lib.ptr(images), _lib.dtype_code(images, "images"), _lib.ptr(y),
+                                            _lib.dtype_code(y, "y"), C.c_int64(b), C.c_int64(h), C.c_int64(w),
+                                            _lib.stream_ptr(images.device))
+    _lib.check(st, "images_to_nhwc")
+    return y
+
+
 def add_layer_norm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, bias: torch.Tensor,
                    eps: float = 1e-6):
     """``(x + delta, LayerNorm(x + delta))`` over the last dimension (``delta=None``: ``(x, LayerNorm(x))``).

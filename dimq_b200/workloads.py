@@ -286,7 +286,11 @@ class DIMQResNet18(nn.Module):
         return self.convs[name.replace(".", "__")]
 
     def _stem(self, images: torch.Tensor) -> torch.Tensor:
-        x = images.to(self.act_dtype).contiguous(memory_format=torch.channels_last)   # NCHW images -> NHWC
+        if images.is_contiguous() and (images.shape[2] * images.shape[3]) % 8 == 0 and images.dtype in (
+                torch.float32, torch.float16, torch.bfloat16):
+            x = ops.images_to_nhwc(images, self.act_dtype)                                 # NCHW images -> NHWC, one pass
+        else:
+            x = images.to(self.act_dtype).contiguous(memory_format=torch.channels_last)
         return self.stem(x)
 
     def forward(self, images: torch.Tensor) -> torch.Tensor:

@@ -307,6 +307,12 @@ DIMQ_API int dimq_im2col(const void* x, int dtype, const dimq_conv_geom* geom, i
 DIMQ_API int dimq_max_pool_nhwc(const void* x, void* y, int dtype, int64_t batch, int64_t height, int64_t width,
                                 int64_t channels, int kernel, int stride, int pad, void* stream);
 
+/* Image batch NCHW (3 channels, fp32 / fp16 / bf16, contiguous) -> NHWC 16-bit (`y_dtype` bf16 or fp16), the
+ * layout the stem convolution reads; height * width must be a multiple of 8.  Dense helper of the ResNet
+ * harness (in the reference's pipeline: `images.to(dtype).contiguous(memory_format=channels_last)`). */
+DIMQ_API int dimq_images_to_nhwc(const void* x, int x_dtype, void* y, int y_dtype, int64_t batch, int64_t height,
+                                 int64_t width, void* stream);
+
 /* Status word written by the last tensor-core kernel on this thread's device that
  * gave up a bounded wait (0 = none; bit 31 set plus a code naming the waiter otherwise).  Reading it
  * synchronises the device and clears the word. */

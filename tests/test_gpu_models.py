@@ -165,6 +165,20 @@ def test_resnet18_forward_matches_cpu_oracle(cuda_device, fuse):
     assert abs(model.lut_flops(256) - 928.8e9) / 928.8e9 < 0.01   # per-batch work of the reference config
 
 
+@pytest.mark.parametrize("src", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("dst", [torch.bfloat16, torch.float16])
+def test_images_to_nhwc_matches_torch(cuda_device, src, dst):
+    from dimq_b200 import ops
+
+    x = torch.randn(5, 3, 12, 10, generator=torch.Generator().manual_seed(3)).to(src).cuda()
+    got = ops.images_to_nhwc(x, dst)
+    want = x.to(dst).contiguous(memory_format=torch.channels_last)
+    assert got.is_contiguous(memory_format=torch.channels_last) and got.dtype == dst
+    assert torch.equal(got, want)
+    with pytest.raises(RuntimeError):
+        ops.images_to_nhwc(x[:, :, :, :9].contiguous(), dst)     # 12 * 9 pixels: not a multiple of 8
+
+
 def test_im2col_and_max_pool_helpers(cuda_device):
     from dimq_b200 import ops
 
