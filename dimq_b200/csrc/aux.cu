@@ -251,30 +251,50 @@ template <typename T>
 __global__ void __launch_bounds__(kAuxThreads)
 max_pool_nhwc_kernel(const T* __restrict__ x, T* __restrict__ y, int B, int H, int W, int C, int OH, int OW, int k,
                      int stride, int pad) {
-  const int cv = C / 8;
-  const int64_t total = static_cast<int64_t>(B) * OH * OW * cv;
-  const int64_t i = static_cast<int64_t>(blockIdx.x) * kAuxThreads + threadIdx.x;
-  if (i >= total) return;
-  const int c8 = static_cast<int>(i % cv);
-  const int64_t pix = i / cv;
-  const int ow = static_cast<int>(pix % OW), oh = static_cast<int>((pix / OW) % OH);
-  const int b = static_cast<int>(pix / (static_cast<int64_t>(OW) * OH));
+  // grid = (chunks of one image's OH * OW * C / 8 vectors, B): 32-bit index arithmetic only (the kernel was bound
+  // by its instruction count - 64-bit divisions per thread - at half the DRAM rate)
+  const int cv = C / 8, row_v = OW * cv;
+  const int t = static_cast<int>(blockIdx.x) * kAuxThreads + static_cast<int>(threadIdx.x);
+  if (t >= OH * row_v) return;
+  const int oh = t / row_v, r = t - oh * row_v;
+  const int ow = r / cv, c8 = r - ow * cv;
+  const int b = static_cast<int>(blockIdx.y);
   // packed 16-bit maxima, two channels per instruction (no conversions); -inf in both halves to start
   using T2 = typename std::conditional<std::is_same<T, __nv_bfloat16>::value, __nv_bfloat162, __half2>::type;
   const uint32_t ninf = std::is_same<T, __nv_bfloat16>::value ? 0xFF80FF80u : 0xFC00FC00u;
   uint32_t m[4] = {ninf, ninf, ninf, ninf};
-  for (int dy = 0; dy < k; ++dy) {
-    const int ih = oh * stride + dy - pad;
-    if (ih < 0 || ih >= H) continue;
-    for (int dx = 0; dx < k; ++dx) {
-      const int iw = ow * stride + dx - pad;
-      if (iw < 0 || iw >= W) continue;
-      const uint4 q = __ldg(reinterpret_cast<const uint4*>(x + ((static_cast<int64_t>(b) * H + ih) * W + iw) * C) + c8);
-      const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
+  const uint4* img = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(b) * H * W * C);   // 32-bit offsets inside an image
+  auto take = [&](const uint4& q) {
+    const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const T2 r = __hmax2(*reinterpret_cast<const T2*>(&m[e]), *reinterpret_cast<const T2*>(&w4[e]));
-        m[e] = *reinterpret_cast<const uint32_t*>(&r);
+    for (int e = 0; e < 4; ++e) {
+      const T2 r = __hmax2(*reinterpret_cast<const T2*>(&m[e]), *reinterpret_cast<const T2*>(&w4[e]));
+      m[e] = *reinterpret_cast<const uint32_t*>(&r);
+    }
+  };
+  if (k == 3) {
+    // the usual window: all nine vectors requested before the first maximum (positions outside the image read -inf)
+    uint4 q[9];
+#pragma unroll
+    for (int dy = 0; dy < 3; ++dy) {
+      const int ih = oh * stride + dy - pad;
+#pragma unroll
+      for (int dx = 0; dx < 3; ++dx) {
+        const int iw = ow * stride + dx - pad;
+        const bool in = static_cast<unsigned>(ih) < static_cast<unsigned>(H) && static_cast<unsigned>(iw) < static_cast<unsigned>(W);
+        q[dy * 3 + dx] = in ? __ldg(img + (ih * W + iw) * cv + c8) : make_uint4(ninf, ninf, ninf, ninf);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 9; ++i) take(q[i]);
+  } else {
+    for (int dy = 0; dy < k; ++dy) {
+      const int ih = oh * stride + dy - pad;
+      if (ih < 0 || ih >= H) continue;
+      for (int dx = 0; dx < k; ++dx) {
+        const int iw = ow * stride + dx - pad;
+        if (iw < 0 || iw >= W) continue;
+        take(__ldg(img + (ih * W + iw) * cv + c8));
       }
     }
   }
@@ -419,15 +439,16 @@ extern "C" int dimq_max_pool_nhwc(const void* x, void* y, int dtype, int64_t bat
   if (total == 0) return DIMQ_OK;
   if (x == nullptr || y == nullptr) return DIMQ_ERR_NULL_POINTER;
   if (!aligned(x, 16) || !aligned(y, 16)) return DIMQ_ERR_ALIGNMENT;
-  const int64_t blocks = (total + kAuxThreads - 1) / kAuxThreads;
-  if (blocks > 0x7FFFFFFFll) return DIMQ_ERR_TOO_LARGE;
+  const int64_t per_image = oh * ow * (channels / 8);
+  if (per_image > 0x7FFFFFFFll - kAuxThreads || height * width * channels > 0x7FFFFFFFll || batch > 65535) return DIMQ_ERR_TOO_LARGE;
+  const dim3 blocks(static_cast<unsigned>((per_image + kAuxThreads - 1) / kAuxThreads), static_cast<unsigned>(batch));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == DIMQ_BF16)
-    max_pool_nhwc_kernel<__nv_bfloat16><<<(unsigned)blocks, kAuxThreads, 0, st>>>(
+    max_pool_nhwc_kernel<__nv_bfloat16><<<blocks, kAuxThreads, 0, st>>>(
         static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), (int)batch, (int)height, (int)width,
         (int)channels, (int)oh, (int)ow, kernel, stride, pad);
   else
-    max_pool_nhwc_kernel<__half><<<(unsigned)blocks, kAuxThreads, 0, st>>>(
+    max_pool_nhwc_kernel<__half><<<blocks, kAuxThreads, 0, st>>>(
         static_cast<const __half*>(x), static_cast<__half*>(y), (int)batch, (int)height, (int)width, (int)channels,
         (int)oh, (int)ow, kernel, stride, pad);
   return launch_status();

@@ -193,6 +193,10 @@ def test_im2col_and_max_pool_helpers(cuda_device):
     got = ops.max_pool_nhwc(xcl, 3, 2, 1)
     assert torch.equal(got, torch.nn.functional.max_pool2d(xcl, 3, 2, 1))
     assert got.is_contiguous(memory_format=torch.channels_last)
+    for dtype, (k, s, p) in ((torch.float16, (3, 2, 1)), (torch.bfloat16, (2, 2, 0)), (torch.float16, (5, 3, 2)),
+                             (torch.bfloat16, (3, 1, 1))):          # 3x3 takes the unrolled window, the rest the loop
+        xcl = torch.randn(3, 24, 17, 14, device="cuda").to(dtype).contiguous(memory_format=torch.channels_last)
+        assert torch.equal(ops.max_pool_nhwc(xcl, k, s, p), torch.nn.functional.max_pool2d(xcl, k, s, p)), (dtype, k, s, p)
 
 
 def test_resnet_layers_match_oracle_strictly(cuda_device):
