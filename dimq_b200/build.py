@@ -17,7 +17,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libdimq_b200.so"
-SOURCES = ["pack.cu", "lut_generic.cu", "lut_stream.cu", "lut_mma_stream.cu", "lut_gemm_tc.cu", "lut_expand_gemm.cu", "aux.cu", "conv_static.cu", "a4_tc.cu", "c_api.cu"]
+SOURCES = ["pack.cu", "lut_generic.cu", "lut_stream.cu", "lut_mma_stream.cu", "lut_mma_regs.cu", "lut_gemm_tc.cu", "lut_expand_gemm.cu", "aux.cu", "conv_static.cu", "a4_tc.cu", "c_api.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

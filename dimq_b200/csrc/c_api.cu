@@ -48,6 +48,13 @@ int launch_stem_conv(const void* x, int x_dtype, const dimq_wq_weight* w, const 
                      int64_t workspace_bytes, cudaStream_t st);
 int read_device_status(uint32_t* status);
 int read_ms_status(uint32_t* status);
+bool mma_regs_supported(const void* x, int x_dtype, const dimq_wq_weight* w, int64_t M, int64_t N, int64_t K);
+bool mma_regs_pays(const dimq_wq_weight* w, int64_t N, int64_t K);
+int64_t mma_regs_workspace_bytes(const dimq_wq_weight* w, int64_t M, int64_t N, int64_t K);
+int launch_linear_wq_mma_regs(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
+                              const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K,
+                              int epilogue, void* workspace, int64_t workspace_bytes, cudaStream_t st);
+int read_rg_status(uint32_t* status);
 int read_dense_status(uint32_t* status);
 int launch_bounded_wait_selftest(uint32_t polls, uint32_t* result, cudaStream_t st);
 }  // namespace dimq
@@ -59,6 +66,15 @@ namespace dimq { void diag_configure(int dbg, int rep, unsigned long long* prof,
 namespace dimq { void dense_diag_configure(int mode); void stem_diag_prof(unsigned long long* prof); }
 extern "C" __attribute__((visibility("default"))) int dimq_diag_stem_prof(void* prof) {
   stem_diag_prof(static_cast<unsigned long long*>(prof));
+  return DIMQ_OK;
+}
+namespace dimq { void set_mma_regs_slices(int ks); void set_mma_regs_trace(uint32_t* trace); }
+extern "C" __attribute__((visibility("default"))) int dimq_diag_mma_regs_trace(void* trace) {
+  set_mma_regs_trace(static_cast<uint32_t*>(trace));
+  return DIMQ_OK;
+}
+extern "C" __attribute__((visibility("default"))) int dimq_diag_mma_regs_slices(int ks) {
+  set_mma_regs_slices(ks);
   return DIMQ_OK;
 }
 extern "C" __attribute__((visibility("default"))) int dimq_diag_dense(int mode) {
@@ -97,14 +113,16 @@ extern "C" const char* dimq_status_string(int status) {
 
 extern "C" int dimq_last_device_status(uint32_t* status) {
   if (status == nullptr) return DIMQ_ERR_NULL_POINTER;
-  uint32_t tc = 0, ms = 0, dense = 0;
+  uint32_t tc = 0, ms = 0, dense = 0, rg = 0;
   int rc = read_device_status(&tc);
   if (rc != DIMQ_OK) return rc;
   rc = read_ms_status(&ms);
   if (rc != DIMQ_OK) return rc;
   rc = read_dense_status(&dense);
   if (rc != DIMQ_OK) return rc;
-  *status = tc | ms | dense;
+  rc = read_rg_status(&rg);
+  if (rc != DIMQ_OK) return rc;
+  *status = tc | ms | dense | rg;
   return DIMQ_OK;
 }
 
@@ -127,7 +145,10 @@ extern "C" int dimq_linear_wq(const void* x, int x_dtype, const dimq_wq_weight* 
   if (x == nullptr || y == nullptr) return DIMQ_ERR_NULL_POINTER;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (algo == DIMQ_ALGO_AUTO) {
-    if (mma_stream_supported(x, x_dtype, w, M, N, K)) algo = DIMQ_ALGO_MMA_STREAM;
+    if (mma_regs_supported(x, x_dtype, w, M, N, K) && mma_regs_pays(w, N, K) &&
+        mma_regs_workspace_bytes(w, M, N, K) == 0)
+      algo = DIMQ_ALGO_MMA_REGS;   // one k slice: no scratch needed
+    else if (mma_stream_supported(x, x_dtype, w, M, N, K)) algo = DIMQ_ALGO_MMA_STREAM;
     else if (stream_supported(w, M, N, K)) algo = DIMQ_ALGO_STREAM;
     else if (tc_supported(x, x_dtype, w, M, N, K)) algo = DIMQ_ALGO_TCGEN05;
     else algo = DIMQ_ALGO_GENERIC;
@@ -139,6 +160,9 @@ extern "C" int dimq_linear_wq(const void* x, int x_dtype, const dimq_wq_weight* 
       return launch_linear_wq_stream(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, st);
     case DIMQ_ALGO_MMA_STREAM:
       return launch_linear_wq_mma_stream(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, st);
+    case DIMQ_ALGO_MMA_REGS:
+      return launch_linear_wq_mma_regs(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, nullptr,
+                                       0, st);   // DIMQ_ERR_SCRATCH_TOO_SMALL where K has several slices
     case DIMQ_ALGO_TCGEN05:
       return launch_linear_wq_tc(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, 0, st);
 #ifdef DIMQ_B200_DIAG
@@ -150,12 +174,41 @@ extern "C" int dimq_linear_wq(const void* x, int x_dtype, const dimq_wq_weight* 
   }
 }
 
+extern "C" int dimq_linear_wq_regs_workspace_bytes(const void* x, int x_dtype, const dimq_wq_weight* w, int64_t M,
+                                                   int64_t N, int64_t K, int64_t* bytes) {
+  if (bytes == nullptr || w == nullptr) return DIMQ_ERR_NULL_POINTER;
+  *bytes = 0;
+  const int rc = check_wq_weight(w, N);
+  if (rc != DIMQ_OK) return rc;
+  if (!mma_regs_supported(x, x_dtype, w, M, N, K)) return DIMQ_ERR_UNSUPPORTED;
+  *bytes = mma_regs_workspace_bytes(w, M, N, K);
+  return DIMQ_OK;
+}
+
+extern "C" int dimq_linear_wq_regs(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
+                                   const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K,
+                                   int epilogue, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return DIMQ_ERR_BAD_SIZE;
+  if (!valid_dtype(x_dtype) || !valid_dtype(y_dtype)) return DIMQ_ERR_BAD_DTYPE;
+  if (bias != nullptr && !valid_dtype(bias_dtype)) return DIMQ_ERR_BAD_DTYPE;
+  if (epilogue < DIMQ_EPI_NONE || epilogue > DIMQ_EPI_ADD_RELU) return DIMQ_ERR_UNSUPPORTED;
+  const int rc = check_wq_weight(w, N);
+  if (rc != DIMQ_OK) return rc;
+  if (x == nullptr || y == nullptr) return DIMQ_ERR_NULL_POINTER;
+  return launch_linear_wq_mma_regs(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, workspace,
+                                   workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int dimq_linear_wq_workspace_bytes(const void* x, int x_dtype, const dimq_wq_weight* w, int64_t M, int64_t N,
                                               int64_t K, int64_t* bytes) {
   if (bytes == nullptr || w == nullptr) return DIMQ_ERR_NULL_POINTER;
   *bytes = 0;
   if (M <= 0 || N <= 0 || K <= 0) return DIMQ_OK;
   if (check_wq_weight(w, N) != DIMQ_OK) return DIMQ_OK;
+  if (mma_regs_supported(x, x_dtype, w, M, N, K) && mma_regs_pays(w, N, K)) {
+    *bytes = mma_regs_workspace_bytes(w, M, N, K);   // the k slices' partial sums (0 with one slice)
+    return DIMQ_OK;
+  }
   if (mma_stream_supported(x, x_dtype, w, M, N, K) || stream_supported(w, M, N, K)) return DIMQ_OK;
   // many activation rows: the expanded 16-bit weight (the output is taken to be as wide as it may get
   // - 16-bit - and aligned; dimq_linear_wq_ws checks the real one and falls back if it does not fit)
@@ -178,6 +231,9 @@ extern "C" int dimq_linear_wq_ws(const void* x, int x_dtype, const dimq_wq_weigh
       x != nullptr && y != nullptr &&
       dimq_linear_wq_workspace_bytes(x, x_dtype, w, M, N, K, &need) == DIMQ_OK && need > 0) {
     if (workspace_bytes < need) return DIMQ_ERR_SCRATCH_TOO_SMALL;
+    if (mma_regs_supported(x, x_dtype, w, M, N, K) && mma_regs_pays(w, N, K))
+      return launch_linear_wq_mma_regs(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue, workspace,
+                                       workspace_bytes, static_cast<cudaStream_t>(stream));
     if (dense_pays(M)) {
       if (dense_supported(x, x_dtype, w, y, y_dtype, residual, M, N, K))
         return launch_linear_wq_dense(x, x_dtype, w, bias, bias_dtype, residual, y, y_dtype, M, N, K, epilogue,

@@ -35,6 +35,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "mma_small.cuh"
 
 namespace dimq {
 int encode_plain_tensor_map(void* out, int elem_bytes, int rank, const void* base, const uint64_t* dims,
@@ -42,12 +43,12 @@ int encode_plain_tensor_map(void* out, int elem_bytes, int rank, const void* bas
 
 namespace {
 
+using namespace small_m;
+
 constexpr int kWarps = 16;
 constexpr int kWriteWarps = 2;  // warps that only add the partial sums and write y, off the compute warps' path
 constexpr int kThreads = (kWarps + kWriteWarps) * 32;
 constexpr int kChunkK = 128;
-constexpr uint32_t kSmemWindow = 227 * 1024;  // dynamic shared memory a CTA may ask for
-constexpr uint32_t kLowStart = 1024;          // the dynamic window starts at or below this shared address
 
 // Absolute shared-memory addresses.  The lookup table sits on a boundary of its own size so that a
 // lookup address is (index bits, masked in place) OR (table base | lane offset): no add.
@@ -58,10 +59,9 @@ template <int BITS>
 struct Cfg {
   static constexpr int kWords = BITS;  // 32 indices per lane, row and unit
   static constexpr uint32_t kUnitBytes = 16 * kChunkK * BITS / 8;  // one ring slot: [16 rows][128 k]
-  static constexpr int kTableEntries = BITS == 3 ? 64 : 256;
-  static constexpr int kEntryWords = BITS == 2 ? 2 : 1;
-  static constexpr uint32_t kTableBytes = kTableEntries * 32 * 4 * kEntryWords;
-  static constexpr uint32_t kTableAddr = BITS == 2 ? 65536u : 32768u;
+  static constexpr int kEntryWords = PairTable<BITS>::kEntryWords;
+  static constexpr uint32_t kTableBytes = PairTable<BITS>::kBytes;
+  static constexpr uint32_t kTableAddr = PairTable<BITS>::kAddr;
   static constexpr uint32_t kXAddr = kTableAddr + kTableBytes;
 };
 
@@ -101,49 +101,6 @@ struct MsParams {
 };
 
 static __device__ uint32_t g_ms_status;
-
-template <bool F16>
-__device__ __forceinline__ uint32_t to_operand(float c) {
-  if constexpr (F16) return __half_as_ushort(__float2half_rn(c));
-  else return __bfloat16_as_ushort(__float2bfloat16_rn(c));
-}
-
-template <bool F16>
-__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                          uint32_t b0, uint32_t b1) {
-  if constexpr (F16) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-  } else {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-  }
-}
-
-template <int BITS>
-__device__ __forceinline__ void load_row_words(const uint8_t* p, uint32_t (&w)[BITS]) {
-  if constexpr (BITS == 4) {
-    const uint4 q = __ldg(reinterpret_cast<const uint4*>(p));
-    w[0] = q.x; w[1] = q.y; w[2] = q.z; w[3] = q.w;
-  } else if constexpr (BITS == 2) {
-    const uint2 q = __ldg(reinterpret_cast<const uint2*>(p));
-    w[0] = q.x; w[1] = q.y;
-  } else {
-#pragma unroll
-    for (int i = 0; i < BITS; ++i) w[i] = __ldg(reinterpret_cast<const uint32_t*>(p) + i);
-  }
-}
-
-// compile-time loop: f(std::integral_constant<int, I>) for I in [0, N) - every index a constant
-template <int I, int N, typename F>
-__device__ __forceinline__ void static_for(F&& f) {
-  if constexpr (I < N) {
-    f(std::integral_constant<int, I>{});
-    static_for<I + 1, N>(f);
-  }
-}
 
 // One lane of a converged warp: TMA copies are issued under this predicate from warp-uniform control
 // flow (issued from a `lane == 0` branch the same instruction costs several times more issue time).
@@ -202,20 +159,6 @@ __device__ __forceinline__ void tma_load_unit(uint32_t dst, const CUtensorMap* m
       : "memory");
 }
 
-// Table lookups: their addresses depend on index words read after the slot's wait, so the compiler
-// cannot move them ahead of the data they need, and the table only changes between two barriers that
-// no lookup can cross for the same reason.  Not volatile: the scheduler is free to issue the lookups of
-// later MMA steps early.
-__device__ __forceinline__ uint32_t lookup_u32(uint32_t addr) {
-  uint32_t v;
-  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ uint2 lookup_u64(uint32_t addr) {
-  uint2 v;
-  asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-  return v;
-}
 __device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
   uint32_t v;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
@@ -438,26 +381,7 @@ linear_wq_mma_stream_kernel(const __grid_constant__ CUtensorMap wmap, const MsPa
       else cb_s[tid] = tid < p.entries ? load_as_float(p.codebooks, p.cb_dtype, group * p.entries + tid) : 0.0f;
     }
     __syncthreads();
-    // 16 bytes per store: four lanes' copies of an entry (two at 2 bits, where an entry is 8 bytes)
-    uint4* table4 = reinterpret_cast<uint4*>(table);
-    if constexpr (BITS == 2) {
-#pragma unroll 2
-      for (int wi = tid; wi < C::kTableEntries * 16; wi += kThreads) {
-        const int e = wi >> 4;
-        uint32_t h[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) h[j] = to_operand<F16>(cb_s[(e >> (2 * j)) & 3]);
-        const uint32_t a = h[0] | (h[1] << 16), b = h[2] | (h[3] << 16);
-        table4[wi] = make_uint4(a, b, a, b);
-      }
-    } else {
-#pragma unroll 2
-      for (int wi = tid; wi < C::kTableEntries * 8; wi += kThreads) {
-        const int e = wi >> 3;
-        const uint32_t v = to_operand<F16>(cb_s[e & ((1 << BITS) - 1)]) | (to_operand<F16>(cb_s[e >> BITS]) << 16);
-        table4[wi] = make_uint4(v, v, v, v);
-      }
-    }
+    fill_pair_table<BITS, F16>(reinterpret_cast<uint4*>(table), cb_s, tid, kThreads);
   };
   auto group_of_iteration = [&](int it) -> int64_t {
     return (static_cast<int64_t>(it) * p.G * 16) / p.group_rows;
@@ -607,39 +531,7 @@ linear_wq_mma_stream_kernel(const __grid_constant__ CUtensorMap wmap, const MsPa
     static_for<0, 8>([&](auto sc) {
       constexpr int s = decltype(sc)::value;
       uint32_t a0, a1, a2, a3;
-      if constexpr (BITS == 4) {
-        // byte b of the word, times 128 bytes per entry: (w >> (8 b - 7)) & 0x7F80
-        constexpr int word = s / 2, b = 2 * s % 4;
-        const uint32_t wg = buf[0][word], wh = buf[1][word];
-        const uint32_t g0 = b == 0 ? (wg << 7) : (wg >> (8 * b - 7));
-        const uint32_t h0 = b == 0 ? (wh << 7) : (wh >> (8 * b - 7));
-        a0 = lookup_u32((g0 & 0x7F80u) | tbl);
-        a2 = lookup_u32(((wg >> (8 * b + 1)) & 0x7F80u) | tbl);
-        a1 = lookup_u32((h0 & 0x7F80u) | tbl);
-        a3 = lookup_u32(((wh >> (8 * b + 1)) & 0x7F80u) | tbl);
-      } else if constexpr (BITS == 3) {
-        constexpr int bit = 12 * s, word = bit >> 5, sh = bit & 31;
-        uint32_t vg, vh;
-        if constexpr (sh + 12 > 32) {
-          vg = __funnelshift_r(buf[0][word], buf[0][word + 1], sh);
-          vh = __funnelshift_r(buf[1][word], buf[1][word + 1], sh);
-        } else {
-          vg = buf[0][word] >> sh;
-          vh = buf[1][word] >> sh;
-        }
-        a0 = lookup_u32(((vg << 7) & 0x1F80u) | tbl);
-        a2 = lookup_u32(((vg << 1) & 0x1F80u) | tbl);
-        a1 = lookup_u32(((vh << 7) & 0x1F80u) | tbl);
-        a3 = lookup_u32(((vh << 1) & 0x1F80u) | tbl);
-      } else {
-        // one byte -> four codewords (a0 and a2 of its row), 256 bytes per entry: the byte drops into
-        // byte 1 of the table address with one permute
-        constexpr int word = s / 4, b = s % 4;
-        constexpr uint32_t sel = 0x7604u | (b << 4);
-        const uint2 eg = lookup_u64(__byte_perm(buf[0][word], tbl, sel));
-        const uint2 eh = lookup_u64(__byte_perm(buf[1][word], tbl, sel));
-        a0 = eg.x; a2 = eg.y; a1 = eh.x; a3 = eh.y;
-      }
+      lookup_step<BITS, s>(buf[0], buf[1], tbl, a0, a1, a2, a3);
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb) {
         if constexpr (s % 2 == 0) bfrag[nb] = lds_u128(xrow[nb] + pr_j * xstep[nb] + 32 * s);  // steps s, s + 1

@@ -22,7 +22,7 @@ from ._lib import ALGO_AUTO, ALGO_GENERIC, ALGO_STREAM, ALGO_TCGEN05, EPI_GELU, 
 
 _EPILOGUES = {None: EPI_NONE, "none": EPI_NONE, "relu": EPI_RELU, "gelu": EPI_GELU, "add_relu": _lib.EPI_ADD_RELU}
 _ALGOS = {None: ALGO_AUTO, "auto": ALGO_AUTO, "generic": ALGO_GENERIC, "stream": ALGO_STREAM,
-          "tcgen05": ALGO_TCGEN05, "mma_stream": 4, "expand": 5}
+          "tcgen05": ALGO_TCGEN05, "mma_stream": 4, "expand": 5, "mma_regs": 6}
 
 
 def is_available() -> bool:
@@ -585,8 +585,28 @@ def dimq_linear_wq(x: torch.Tensor, packed_weight: torch.Tensor, codebooks: torc
         _lib.LAUNCH_COUNT[0] += 1  # the expansion and the GEMM
         del keep
         return y.view(*x.shape[:-1], out_features)
+    if algo == "mma_regs":
+        # the register-resident small-M kernel at any weight size; its k slices meet in scratch memory
+        need = C.c_int64(0)
+        st = _lib.lib().dimq_linear_wq_regs_workspace_bytes(
+            _lib.ptr(xc), _lib.dtype_code(xc, "x"), C.byref(w), C.c_int64(m), C.c_int64(out_features),
+            C.c_int64(in_features), C.byref(need))
+        if st != 0:
+            _lib.check(st, "linear_wq_regs_workspace_bytes")   # raises: a size query launches nothing
+        ws = torch.empty(max(need.value, 16), dtype=torch.uint8, device=xc.device)
+        with torch.cuda.device(xc.device):
+            st = _lib.lib().dimq_linear_wq_regs(_lib.ptr(xc), _lib.dtype_code(xc, "x"), C.byref(w), _lib.ptr(b), b_dt,
+                                                _lib.ptr(res), _lib.ptr(y), _lib.dtype_code(y, "y"), C.c_int64(m),
+                                                C.c_int64(out_features), C.c_int64(in_features), _EPILOGUES[epilogue],
+                                                _lib.ptr(ws), C.c_int64(ws.numel()), _lib.stream_ptr(xc.device))
+        _lib.check(st, "linear_wq_regs")
+        if need.value > 0:
+            _lib.LAUNCH_COUNT[0] += 1  # the kernel that adds the k slices
+        del keep
+        return y.view(*x.shape[:-1], out_features)
     if algo is None:
-        # Two shapes get scratch memory: many activation rows (the indices are expanded once to a
+        # Three shapes get scratch memory: a few activation rows against a large weight (the k slices of
+        # the small-M kernel meet there), many activation rows (the indices are expanded once to a
         # 16-bit weight and a dense tensor-core GEMM follows) and a few hundred rows against a long K
         # (the kernel splits K and sums partial tiles there).
         need = C.c_int64(0)

@@ -55,6 +55,9 @@ extern "C" {
 #define DIMQ_ALGO_TCGEN05 3   /* TMA + in-pipeline dequantisation + tcgen05 MMA (tensor-core regime) */
 #define DIMQ_ALGO_MMA_STREAM 4 /* small-M index-streaming kernel for 16-bit activations (M <= 32): pair-table
                                   lookups feeding warp-level MMAs; the HBM-bound regime */
+#define DIMQ_ALGO_MMA_REGS 6  /* small-M kernel for weights of 2 MB of indices and more (M <= 16, K a multiple of
+                                  2048): activations and indices in registers.  Through dimq_linear_wq only with
+                                  K = 2048 (one k slice); longer K needs scratch: dimq_linear_wq_ws / _regs */
 
 /* fused epilogues of the weight-only ops */
 #define DIMQ_EPI_NONE 0
@@ -202,7 +205,12 @@ DIMQ_API int dimq_conv2d_wq_static(const void* x, int x_dtype, const dimq_wq_wei
                                    int bias_dtype, const void* residual, void* y, int y_dtype,
                                    const dimq_conv_geom* geom, int epilogue, void* stream);
 
-/* dimq_linear_wq with caller-owned scratch memory, which two regimes use:
+/* dimq_linear_wq with caller-owned scratch memory, which three regimes use:
+ *  - a few activation rows (M <= 16, 16-bit x) against 2 MB of 2- to 4-bit indices or more, N a multiple
+ *    of 16 and K of 2048: the register-resident small-M kernel cuts K into slices of 2048 worked on by
+ *    different CTAs, each writes its partial sums to the workspace (slices * M * N * 4 bytes, at most 8
+ *    slices at a time) and a second small kernel adds them in a fixed order and applies bias / epilogue /
+ *    residual: no atomics, the same bits every run.
  *  - many activation rows (M >= 1024, 16-bit x, K a multiple of 64, 16-byte aligned y rows): the
  *    indices are expanded ONCE per call into a 16-bit weight matrix in the workspace (N*K*2 bytes; twice
  *    that when bf16 activations meet a codebook that is not stored in bf16 and every codeword is carried
@@ -247,6 +255,16 @@ DIMQ_API int dimq_conv2d_wq_expand(const void* x, int x_dtype, const dimq_wq_wei
                                    int bias_dtype, const void* residual, void* y, int y_dtype,
                                    const dimq_conv_geom* geom, int epilogue, void* workspace, int64_t workspace_bytes,
                                    void* stream);
+
+/* The register-resident small-M kernel requested explicitly, whatever the size of the weight
+ * (DIMQ_ERR_UNSUPPORTED outside M <= 16, 16-bit x, 2- to 4-bit indices, N % 16 == 0, K % 2048 == 0).
+ * dimq_linear_wq_regs_workspace_bytes gives the scratch it needs (0 when K = 2048).  Replaces the
+ * reference's per-call dequantisation (dimq_backend/reference.py:47-56) in the decode regime. */
+DIMQ_API int dimq_linear_wq_regs_workspace_bytes(const void* x, int x_dtype, const dimq_wq_weight* w, int64_t M,
+                                                 int64_t N, int64_t K, int64_t* bytes);
+DIMQ_API int dimq_linear_wq_regs(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,
+                                 const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K,
+                                 int epilogue, void* workspace, int64_t workspace_bytes, void* stream);
 
 /* ---- W4A4 product-table ops on the tensor cores ------------------------- */
 

@@ -359,6 +359,126 @@ def test_linear_wq_mma_stream_converts_bf16_activations_of_any_magnitude(ops):
         assert err <= 1e-3 * scale + (0.0 if scale > 0 else 1e-30), (row, err, scale)
 
 
+# ---- small-M kernel for large weights: activations and indices in registers, k split over a cluster ----
+
+# (m, k, n, group rows): 1 / 2 / 3 / 4 / 5 CTAs per cluster, several passes (k / 2048 = 11 is prime; 16384 = 2 x 4
+# slices), codebook groups, fewer row blocks than clusters
+MR_SHAPES = [(1, 2048, 64, None), (8, 4096, 256, 128), (9, 8192, 304, None), (3, 6144, 160, 16), (5, 10240, 48, None),
+             (16, 22528, 32, None), (2, 16384, 96, 32)]
+# enough row blocks that every cluster walks more of them than it keeps in flight (and crosses codebook groups)
+MR_LONG_SHAPES = [(16, 2048, 9616, 32), (4, 8192, 2400, 128), (7, 14336, 1360, 16), (2, 16384, 2384, None)]
+
+
+@pytest.mark.parametrize("mode", [0, 3])
+@pytest.mark.parametrize("bits", [2, 3, 4])
+@pytest.mark.parametrize("m,k,n,grp", MR_LONG_SHAPES)
+def test_linear_wq_mma_regs_many_row_blocks(ops, bits, m, k, n, grp, mode):
+    """~20 M weights per case: random index bytes against the exact fp32 kernel of this library (itself checked
+    against the oracle above), and one case against the oracle."""
+    x_dtype, _, cb_torch = MS_MODES[mode]
+    gen = torch.Generator(device="cuda").manual_seed(bits * 100 + m)
+    packed = torch.randint(0, 256, (n, k * bits // 8), dtype=torch.uint8, device="cuda", generator=gen)
+    groups = 1 if grp is None else -(-n // grp)
+    cb = (torch.randn(groups, 1 << bits, device="cuda", generator=gen) * 0.02).to(cb_torch)
+    x = torch.randn(m, k, device="cuda", generator=gen).to(x_dtype)
+    bias = torch.randn(n, device="cuda", generator=gen)
+    got = ops.dimq_linear_wq(x, packed, cb, bias, n, k, bits=bits, group_rows=grp, algo="mma_regs")
+    assert ops.last_device_status() == 0
+    cb_used = cb.to(x_dtype) if x_dtype == torch.float16 else cb      # fp16 MMAs round the codewords to fp16
+    want = ops.dimq_linear_wq(x, packed, cb_used, bias, n, k, bits=bits, group_rows=grp, algo="generic")
+    _assert_close(got, want.cpu().numpy(), f"mma_regs long bits={bits} {m}x{k}x{n} mode={mode}")
+    np.testing.assert_allclose(got.cpu().numpy(), want.cpu().numpy(), rtol=2e-4, atol=2e-4 * np.sqrt(k / 1024))
+    if (bits, mode, k) == (4, 3, 8192):
+        ref = o.linear_wq(x.float().cpu().numpy(), packed.cpu().numpy(), cb.float().cpu().numpy(), bits, n, k,
+                          bias.cpu().numpy(), grp)
+        _assert_close(got, ref, "mma_regs long against the oracle")
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2, 3])
+@pytest.mark.parametrize("bits", [2, 3, 4])
+@pytest.mark.parametrize("m,k,n,grp", MR_SHAPES)
+def test_linear_wq_mma_regs(ops, bits, m, k, n, grp, mode):
+    x_dtype, cb_np, cb_torch = MS_MODES[mode]
+    case = make_weight(n, k, bits, seed=bits * 5 + m, group_rows=grp, cb_dtype=cb_np)
+    rng = np.random.default_rng(m + k + n)
+    x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(x_dtype)
+    bias = rng.standard_normal(n).astype(np.float32)
+    cbs = case["codebooks"].astype(np.float16).astype(np.float32) if x_dtype == torch.float16 else case["codebooks"]
+    want = o.linear_wq(x.float().numpy(), case["packed"], cbs, bits, n, k, bias, case["group_rows"])
+    got = ops.dimq_linear_wq(x.cuda(), _cuda(case["packed"]), _cuda(case["codebooks"], cb_torch), _cuda(bias), n, k,
+                             bits=bits, group_rows=grp, algo="mma_regs")
+    assert ops.last_device_status() == 0
+    _assert_close(got, want, f"mma_regs bits={bits} {m}x{k}x{n} mode={mode}")
+    np.testing.assert_allclose(got.cpu().numpy(), want, rtol=2e-4, atol=2e-4 * np.sqrt(k / 1024))
+
+
+@pytest.mark.parametrize("y_dtype", [torch.float32, torch.bfloat16])
+def test_linear_wq_mma_regs_epilogues(ops, y_dtype):
+    m, k, n = 12, 4096, 208
+    case = make_weight(n, k, 4, seed=3, cb_dtype="bf16")
+    rng = np.random.default_rng(8)
+    x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(torch.bfloat16)
+    bias = rng.standard_normal(n).astype(np.float32)
+    res = torch.from_numpy(rng.standard_normal((m, n)).astype(np.float32)).to(y_dtype)
+    lin = o.linear_wq(x.float().numpy(), case["packed"], case["codebooks"], 4, n, k, bias)
+    args = (x.cuda(), _cuda(case["packed"]), _cuda(case["codebooks"], torch.bfloat16), _cuda(bias), n, k)
+    for epi, fn in (("relu", lambda v: np.maximum(v, 0)), ("gelu", None), (None, lambda v: v),
+                    ("add_relu", lambda v: np.maximum(v + res.float().numpy(), 0))):
+        want = torch.nn.functional.gelu(torch.from_numpy(lin)).numpy() if fn is None else fn(lin)
+        if epi != "add_relu":
+            want = want + res.float().numpy()
+        got = ops.dimq_linear_wq(*args, bits=4, out_dtype=y_dtype, epilogue=epi, residual=res.cuda(), algo="mma_regs")
+        assert got.dtype == y_dtype
+        max_abs, rel = o.parity_metrics(got.float().cpu().numpy(), want)
+        assert rel <= (5e-3 if y_dtype == torch.bfloat16 else 1e-4), (epi, max_abs, rel)
+
+
+def test_linear_wq_mma_regs_rejects_and_auto_dispatch(ops):
+    case = make_weight(64, 2048, 4, seed=1)
+    pw, cb = _cuda(case["packed"]), _cuda(case["codebooks"])
+    with pytest.raises(RuntimeError):  # fp32 activations
+        ops.dimq_linear_wq(torch.zeros(4, 2048, device="cuda"), pw, cb, None, 64, 2048, bits=4, algo="mma_regs")
+    with pytest.raises(RuntimeError):  # more than 16 rows
+        ops.dimq_linear_wq(torch.zeros(17, 2048, device="cuda", dtype=torch.float16), pw, cb, None, 64, 2048, bits=4,
+                           algo="mma_regs")
+    case = make_weight(64, 1024, 4, seed=1)
+    with pytest.raises(RuntimeError):  # k not a multiple of 2048
+        ops.dimq_linear_wq(torch.zeros(4, 1024, device="cuda", dtype=torch.float16), _cuda(case["packed"]),
+                           _cuda(case["codebooks"]), None, 64, 1024, bits=4, algo="mma_regs")
+    # 2 MB of indices and more: the automatic choice is this kernel (same bits as the forced call)
+    n, k = 4096, 4096
+    case = make_weight(n, k, 4, seed=9)
+    x = torch.from_numpy(np.random.default_rng(3).standard_normal((6, k)).astype(np.float32)).to(torch.bfloat16).cuda()
+    args = (x, _cuda(case["packed"]), _cuda(case["codebooks"], torch.float16), None, n, k)
+    assert torch.equal(ops.dimq_linear_wq(*args, bits=4), ops.dimq_linear_wq(*args, bits=4, algo="mma_regs"))
+    assert not torch.equal(ops.dimq_linear_wq(*args, bits=4), ops.dimq_linear_wq(*args, bits=4, algo="mma_stream"))
+
+
+def test_linear_wq_mma_regs_converts_bf16_activations_of_any_magnitude(ops):
+    """bf16 activations with an fp16 codebook run as fp16 MMAs; a (row, 128-k range) whose largest magnitude
+    lies outside the exactly convertible range is scaled by a power of two on the way in and its partial sums
+    back on the way out: huge, tiny, zero and mixed rows keep the weight-only tolerance."""
+    m, k, n = 7, 4096, 96
+    case = make_weight(n, k, 4, seed=5)                      # fp16-rounded codebook
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    x[1] *= 1.0e6            # beyond fp16's 65504
+    x[2] *= 1.0e-9           # below fp16's subnormals
+    x[3] = 0.0               # all zero
+    x[4, :5] *= 3.0e37       # a few huge values among ordinary ones
+    x[5] *= 1.0e-20
+    x[6] *= 3.0e30
+    x = bf16_round(x)
+    want = o.linear_wq(x, case["packed"], case["codebooks"], 4, n, k).astype(np.float64)
+    got = ops.dimq_linear_wq(_cuda(x, torch.bfloat16), _cuda(case["packed"]), _cuda(case["codebooks"], torch.float16),
+                             None, n, k, bits=4, algo="mma_regs").cpu().numpy().astype(np.float64)
+    assert ops.last_device_status() == 0 and np.isfinite(got).all()
+    for row in range(m):
+        scale = np.linalg.norm(want[row])
+        err = np.linalg.norm(got[row] - want[row])
+        assert err <= 1e-3 * scale + (0.0 if scale > 0 else 1e-30), (row, err, scale)
+
+
 TC_SHAPES = [(192, 64, 128), (200, 128, 130), (577, 768, 384), (64, 1024, 256), (16, 256, 128)]
 
 
@@ -478,14 +598,16 @@ def test_linear_wq_m_sweep_auto_dispatch(ops, bits, k, n, m):
     assert ops.last_device_status() == 0
     _assert_close(got, want, f"sweep bits={bits} m={m} {k}->{n}")
     if m <= 32:
-        # the index-streaming kernel is what the automatic choice runs here (fp16 codebook, bf16 activations:
-        # the reference export's default): the two results are the same bits
+        # what the automatic choice runs here (fp16 codebook, bf16 activations: the reference export's default)
+        # is a small-M kernel - the register-resident one from 2 MB of indices on when M <= 16 and K is a
+        # multiple of 2048, else the index-streaming one: the two results are the same bits
+        small = "mma_regs" if (m <= 16 and k % 2048 == 0 and n * k * bits // 8 >= 2 << 20) else "mma_stream"
         try:
             forced = ops.dimq_linear_wq(_cuda(x, torch.bfloat16), case["packed_cuda"], case["cb_cuda"], None, n, k,
-                                        bits=bits, algo="mma_stream")
+                                        bits=bits, algo=small)
         except RuntimeError as err:
             # 16 rows of 4096 activations do not fit beside the 64 KB table of the 2-bit form
-            assert (m, k, bits) == (16, 4096, 2) and "does not support" in str(err), err
+            assert (m, k, bits, small) == (16, 4096, 2, "mma_stream") and "does not support" in str(err), err
         else:
             assert torch.equal(got, forced)
 
