@@ -229,9 +229,10 @@ def run_micro(args) -> None:
 
 
 def small_m_micro(dev) -> dict:
-    """The index-streaming regime: M in {1, 4, 16} on the 1024 -> 4096 and 4096 -> 1024 shapes (4-bit,
-    bf16 activations, fp16 codebook as the reference's packed export stores it), the weight of every
-    call different and the ring of weights larger than the L2, one CUDA graph of back-to-back calls."""
+    """The index-streaming regime: M in {1, 4, 16} on the 1024 -> 4096, 4096 -> 1024 (2 MB of indices) and
+    8192 -> 8192 (32 MB) shapes (4-bit, bf16 activations, fp16 codebook as the reference's packed export
+    stores it), the weight of every call different and the ring of weights larger than the L2, one CUDA
+    graph of back-to-back calls."""
     import torch
 
     from dimq_b200 import ops
@@ -239,11 +240,13 @@ def small_m_micro(dev) -> dict:
     path = ROOT / "MEASURED_PEAKS.json"
     hbm_peak = float(json.loads(path.read_text()).get("hbm_gbs", FALLBACK_HBM_GBS)) if path.exists() else FALLBACK_HBM_GBS
     out = {"unit": "us per call", "index_gbs_peak": hbm_peak, "peak_source": "measured" if path.exists() else "fallback",
-           "weights": "4-bit, one fp16 codebook per layer; a ring of 136 distinct 2 MB index tensors (272 MB > L2), L2-cold",
+           "weights": "4-bit, one fp16 codebook per layer; rings of distinct index tensors larger than the L2 "
+                      "(136 x 2 MB, 6 x 32 MB), L2-cold",
            "cases": []}
-    copies, bits = 136, 4
-    for (k, n) in ((1024, 4096), (4096, 1024)):
+    bits = 4
+    for (k, n) in ((1024, 4096), (4096, 1024), (8192, 8192)):
         index_bytes = n * k * bits // 8
+        copies = 136 if index_bytes <= (2 << 20) else 6
         packed = [torch.randint(0, 256, (index_bytes,), dtype=torch.uint8, device=dev) for _ in range(copies)]
         cb = (torch.randn(1, 16, device=dev) * 0.02).sort(dim=1).values.to(torch.float16)
         for m in (1, 4, 16):
@@ -251,10 +254,12 @@ def small_m_micro(dev) -> dict:
             call = lambda pw: ops.dimq_linear_wq(x, pw, cb, None, n, k, bits=bits, out_dtype=torch.bfloat16)
             call(packed[0])
             torch.cuda.synchronize()
+            reps = max(1, 24 // copies)      # a graph of at least 24 calls
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                for pw in packed:
-                    call(pw)
+                for _ in range(reps):
+                    for pw in packed:
+                        call(pw)
             for _ in range(3):
                 graph.replay()
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -263,7 +268,7 @@ def small_m_micro(dev) -> dict:
                 graph.replay()
             end.record()
             torch.cuda.synchronize()
-            us = start.elapsed_time(end) * 1e3 / (5 * copies)
+            us = start.elapsed_time(end) * 1e3 / (5 * copies * reps)
             out["cases"].append({"m": m, "k": k, "n": n, "us": us, "index_gbs": index_bytes / us / 1e3,
                                  "index_gbs_frac": index_bytes / us / 1e3 / hbm_peak})
         del packed

@@ -9,10 +9,11 @@
 // rows - are loaded once; per unit it issues two (4-bit: 16-byte) index loads, kDepth units ahead, 32
 // lookups and 8 (16 at M > 8) MMAs.  No ring, no mbarrier, no activation reads.
 //
-// The price is a reduction over the k ranges.  A CTA's 16 compute warps cover 2048 consecutive k of the
-// same row block at the same time; each writes its 16 x M partial sums to a buffer of its own (double
-// buffered, handed over with named barriers that the compute warps only arrive at), two write-back warps
-// add the sixteen and keep the result in a per-CTA array `fin` for all row blocks of the CTA.  K / 2048
+// The price is a reduction over the k ranges.  A CTA's 16 warps cover 2048 consecutive k of the same row
+// blocks; each keeps the 16 x M partial sums of every unit in a buffer of its own in shared memory - as
+// many units as fit beside the table (a "chunk": all of a CTA's row blocks at the sizes this kernel is
+// chosen for), so the warps run freely, without a barrier per row block.  After a chunk one barrier, then
+// all threads add the sixteen tiles of every unit into a per-CTA array `fin`, and a second barrier.  K / 2048
 // CTAs (k slices) share a range of row blocks - several passes when K / 2048 has no divisor <= 8; each
 // writes its `fin` to a slice of the caller's workspace ([k slice][M][N] floats) and a second, tiny kernel
 // adds the slices and finishes the outputs (bias, epilogue, residual, store).  Nothing waits for another
@@ -35,10 +36,9 @@ namespace {
 
 using namespace small_m;
 
-constexpr int kKWarps = 16;   // warps of a CTA: one 128-k range each
-constexpr int kRgThreads = kKWarps * 32;
-constexpr int kCtaK = kKWarps * 128;
+constexpr int kCtaK = 2048;   // k of a CTA's warps together; a warp owns KR = 128 of them (16 warps) or 64 (32 warps)
 constexpr int kDepth = 3;     // units of indices in flight per warp
+constexpr uint32_t kLowPart = 2048;   // shared address where the partial tiles below the table start
 constexpr int kMaxSlices = 8;   // k slices worked on at a time (CTAs sharing a range of row blocks)
 struct RgParams {
   const void* x;
@@ -61,6 +61,9 @@ struct RgParams {
   int passes;    // K / (2048 ks)
   int ranges;    // ranges of row blocks (each worked on by ks CTAs)
   float* partial;  // ks > 1: [ks][M][N] sums of the k slices
+  int chunk;       // units a warp runs through between two reductions
+  int chunk_low;   // of which so many have their partial tiles below the table
+  uint32_t fin_bytes;  // size of `fin`: the partial tiles above the table start behind it
   uint32_t* status;
 #ifdef DIMQ_B200_DIAG
   uint32_t* trace;   // host-mapped clock samples, [CTA][32]
@@ -97,22 +100,22 @@ struct Tbl {
 };
 
 template <int BITS, bool F16>
-__device__ __forceinline__ void fill_table(uint4* table4, const float* cb, int tid) {
+__device__ __forceinline__ void fill_table(uint4* table4, const float* cb, int tid, int threads) {
   if constexpr (BITS == 4) {
 #pragma unroll 2
-    for (int wi = tid; wi < 256 * 8; wi += kRgThreads) {
+    for (int wi = tid; wi < 256 * 8; wi += threads) {
       const int e = wi >> 3;
       const uint32_t v = to_operand<F16>(cb[e & 15]) | (to_operand<F16>(cb[e >> 4]) << 16);
       table4[e * 16 + (wi & 7)] = make_uint4(v, v, v, v);
     }
   } else {
-    fill_pair_table<BITS, F16>(table4, cb, tid, kRgThreads);
+    fill_pair_table<BITS, F16>(table4, cb, tid, threads);
   }
 }
 
 // A fragments of MMA step S: the lane's indices 4 S .. 4 S + 3 of rows g (wg) and g + 8 (wh)
-template <int BITS, int S>
-__device__ __forceinline__ void lookup_a(const uint32_t (&wg)[BITS], const uint32_t (&wh)[BITS], uint32_t tbl,
+template <int BITS, int WL, int S>
+__device__ __forceinline__ void lookup_a(const uint32_t (&wg)[WL], const uint32_t (&wh)[WL], uint32_t tbl,
                                          uint32_t& a0, uint32_t& a1, uint32_t& a2, uint32_t& a3) {
   if constexpr (BITS == 4) {
     constexpr int word = S / 2, b = 2 * S % 4;
@@ -121,8 +124,15 @@ __device__ __forceinline__ void lookup_a(const uint32_t (&wg)[BITS], const uint3
     a2 = lookup_u32(__byte_perm(wg[word], tbl, sel1));
     a1 = lookup_u32(__byte_perm(wh[word], tbl, sel0));
     a3 = lookup_u32(__byte_perm(wh[word], tbl, sel1));
+  } else if constexpr (BITS == 2) {
+    // one byte -> four codewords (a0 and a2 of its row)
+    constexpr int word = S / 4, b = S % 4;
+    constexpr uint32_t sel = 0x7604u | (b << 4);
+    const uint2 eg = lookup_u64(__byte_perm(wg[word], tbl, sel));
+    const uint2 eh = lookup_u64(__byte_perm(wh[word], tbl, sel));
+    a0 = eg.x; a2 = eg.y; a1 = eh.x; a3 = eh.y;
   } else {
-    lookup_step<BITS, S>(wg, wh, tbl, a0, a1, a2, a3);
+    lookup_step<BITS, S>(wg, wh, tbl, a0, a1, a2, a3);   // 3 bits: WL == 3
   }
 }
 
@@ -141,13 +151,36 @@ __device__ __forceinline__ void mma_16816_first(float (&d)[4], uint32_t a0, uint
   }
 }
 
-template <int BITS, int NB, bool F16>
-__global__ void __launch_bounds__(kRgThreads, 1) linear_wq_mma_regs_kernel(const RgParams p) {
+// the lane's indices of one row of a unit: KR / 4 of them, WL words
+template <int WL>
+__device__ __forceinline__ void load_lane_words(const uint8_t* p, uint32_t (&w)[WL]) {
+  if constexpr (WL == 4) {
+    const uint4 q = __ldg(reinterpret_cast<const uint4*>(p));
+    w[0] = q.x; w[1] = q.y; w[2] = q.z; w[3] = q.w;
+  } else if constexpr (WL == 2) {
+    const uint2 q = __ldg(reinterpret_cast<const uint2*>(p));
+    w[0] = q.x; w[1] = q.y;
+  } else {
+#pragma unroll
+    for (int i = 0; i < WL; ++i) w[i] = __ldg(reinterpret_cast<const uint32_t*>(p) + i);
+  }
+}
+
+// KR: k of one warp.  128 (16 warps of up to 128 registers) is what runs.  64 (32 warps of 64 registers,
+// diagnostic builds only) was 30 % slower at 8192 x 8192: the kernel is not short of warps to hide latency
+// behind, it is bound by the load / store pipe - per unit 32 lookups, 16 wavefronts of index loads (a
+// warp's 16-byte pieces lie in eight different rows), the partial tile - and halving a warp's k doubles
+// the loads and tiles per k.
+template <int BITS, int NB, bool F16, int KR>
+__global__ void __launch_bounds__(kCtaK / KR * 32, 1) linear_wq_mma_regs_kernel(const RgParams p) {
   using T = Tbl<BITS>;
-  constexpr int W = BITS;
+  constexpr int kKWarps = kCtaK / KR;
+  constexpr int TH = kKWarps * 32;
+  constexpr int W = KR / 4 * BITS / 32;   // words of a lane's indices of one row of a unit
+  constexpr int kSteps = KR / 16;         // MMA steps of a unit
+  constexpr int XW = KR / 8;              // registers of a lane's activations of one row
   constexpr int MR = 8 * NB;          // columns of the MMA tiles (activation rows, M rounded up)
   constexpr int kTile = 16 * MR;      // floats of one row block's sums
-  constexpr int kAdders = kTile / 32; // warps that add an iteration's partial tiles (one sum per lane)
   extern __shared__ __align__(16) unsigned char smem[];
   const uint32_t s0 = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
   if (s0 > kLowStart) {  // same for every CTA of the grid: the fixed layout below would not fit, do nothing
@@ -157,9 +190,15 @@ __global__ void __launch_bounds__(kRgThreads, 1) linear_wq_mma_regs_kernel(const
   unsigned char* const abs0 = smem - s0;  // generic address of shared address 0
   float* cb_s = reinterpret_cast<float*>(abs0 + kLowStart);
   uint4* table4 = reinterpret_cast<uint4*>(abs0 + T::kAddr);
-  float* part = reinterpret_cast<float*>(abs0 + T::kEnd);        // [2][warp][16 rows][MR]
-  constexpr uint32_t kFinAddr = T::kEnd + 2 * kKWarps * kTile * 4;
-  float* fin = reinterpret_cast<float*>(abs0 + kFinAddr);        // [row block of this CTA][16 rows][MR]
+  // [kLowPart, table): partial tiles of the first chunk_low units of a chunk, [unit][warp][16 rows][MR];
+  // [table end, +fin_bytes): fin, [row block of this CTA][16 rows][MR]; behind it the other units' tiles
+  constexpr uint32_t kUnitBytes = kKWarps * kTile * 4;
+  constexpr uint32_t kFinAddr = T::kEnd;
+  float* fin = reinterpret_cast<float*>(abs0 + kFinAddr);
+  const uint32_t part_high = kFinAddr + p.fin_bytes;
+  auto part_addr = [&](int slot) -> uint32_t {   // shared address of the sixteen tiles of unit `slot` of a chunk
+    return slot < p.chunk_low ? kLowPart + slot * kUnitBytes : part_high + (slot - p.chunk_low) * kUnitBytes;
+  };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -184,12 +223,12 @@ __global__ void __launch_bounds__(kRgThreads, 1) linear_wq_mma_regs_kernel(const
   const uint32_t it_stride = 16u * row_bytes, half_stride = 8u * row_bytes;
   auto unit_off = [&](int pass) -> uint32_t {
     const int kr = (pass * p.ks + rank) * kKWarps + warp;
-    return (static_cast<uint32_t>(rb0) * 16u + g) * row_bytes + kr * (16 * BITS) + t * (4 * BITS);
+    return (static_cast<uint32_t>(rb0) * 16u + g) * row_bytes + kr * (KR * BITS / 8) + t * (4 * W);
   };
   uint32_t buf[kDepth][2][W];
   auto load_unit = [&](uint32_t (&b)[2][W], uint32_t off) {
-    load_row_words<BITS>(p.packed + off, b[0]);
-    load_row_words<BITS>(p.packed + off + half_stride, b[1]);
+    load_lane_words<W>(p.packed + off, b[0]);
+    load_lane_words<W>(p.packed + off + half_stride, b[1]);
   };
   uint32_t off0 = unit_off(0);
   static_for<0, kDepth>([&](auto dc) {
@@ -203,7 +242,7 @@ __global__ void __launch_bounds__(kRgThreads, 1) linear_wq_mma_regs_kernel(const
       else cb_s[tid] = tid < p.entries ? load_as_float(p.codebooks, p.cb_dtype, static_cast<int64_t>(cur_group) * p.entries + tid) : 0.0f;
     }
     __syncthreads();
-    fill_table<BITS, F16>(table4, cb_s, tid);
+    fill_table<BITS, F16>(table4, cb_s, tid, TH);
     __syncthreads();
   };
   build_table(true);
@@ -230,24 +269,24 @@ __global__ void __launch_bounds__(kRgThreads, 1) linear_wq_mma_regs_kernel(const
       group_end = (cur_group + 1) * p.group_rbs - rb0;
     }
     // ---- B fragments of this warp's k range: x[m = nb * 8 + g][32 t .. 32 t + 31], kept for all row blocks ----
-    uint32_t xb[NB][16];
+    uint32_t xb[NB][XW];
     float inv[NB][2];   // what the sums of columns 2 t, 2 t + 1 are multiplied by (converting mode)
     const int kr = (pass * p.ks + rank) * kKWarps + warp;
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
       const int m = nb * 8 + g;
-      uint4 q[4];
+      uint4 q[XW / 4];
       if (m < p.M) {
         const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.x) +
-                                                          static_cast<int64_t>(m) * p.K + kr * 128 + 32 * t);
+                                                          static_cast<int64_t>(m) * p.K + kr * KR + (KR / 4) * t);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) q[j] = __ldg(src + j);
+        for (int j = 0; j < XW / 4; ++j) q[j] = __ldg(src + j);
       } else {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) q[j] = make_uint4(0u, 0u, 0u, 0u);
+        for (int j = 0; j < XW / 4; ++j) q[j] = make_uint4(0u, 0u, 0u, 0u);
       }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < XW / 4; ++j) {
         xb[nb][4 * j] = q[j].x; xb[nb][4 * j + 1] = q[j].y; xb[nb][4 * j + 2] = q[j].z; xb[nb][4 * j + 3] = q[j].w;
       }
       float back = 1.0f;
@@ -255,7 +294,7 @@ __global__ void __launch_bounds__(kRgThreads, 1) linear_wq_mma_regs_kernel(const
         if (p.cvt) {
           float a = 0.0f;   // largest finite magnitude of the row within this k range
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
+          for (int j = 0; j < XW; ++j) {
             const float2 xy = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xb[nb][j]));
             if (fabsf(xy.x) < 3.0e38f) a = fmaxf(a, fabsf(xy.x));
             if (fabsf(xy.y) < 3.0e38f) a = fmaxf(a, fabsf(xy.y));
@@ -271,7 +310,7 @@ __global__ void __launch_bounds__(kRgThreads, 1) linear_wq_mma_regs_kernel(const
             back = ldexpf(1.0f, e - 15);
           }
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
+          for (int j = 0; j < XW; ++j) {
             float2 xy = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xb[nb][j]));
             xy.x *= f; xy.y *= f;
             const __half2 h = __float22half2_rn(xy);
@@ -285,6 +324,7 @@ __global__ void __launch_bounds__(kRgThreads, 1) linear_wq_mma_regs_kernel(const
     }
     if (pass == 0) RG_MARK(3);
 
+    int c0 = 0, c_end = min(n_it, p.chunk);   // the chunk being worked on: units [c0, c_end)
     for (int it0 = 0; it0 < n_it; it0 += kDepth) {
       static_for<0, kDepth>([&](auto dc) {
         constexpr int d = decltype(dc)::value;
@@ -311,10 +351,10 @@ __global__ void __launch_bounds__(kRgThreads, 1) linear_wq_mma_regs_kernel(const
           // MMAs; at M > 8 the two column tiles already are two chains
           constexpr int E = NB == 1 ? 2 : 1;
           float acc[E][NB][4];
-          static_for<0, 8>([&](auto sc) {
+          static_for<0, kSteps>([&](auto sc) {
             constexpr int s = decltype(sc)::value;
             uint32_t a0, a1, a2, a3;
-            lookup_a<BITS, s>(cur[0], cur[1], tbl_it, a0, a1, a2, a3);
+            lookup_a<BITS, W, s>(cur[0], cur[1], tbl_it, a0, a1, a2, a3);
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb) {
               if constexpr (s < E) mma_16816_first<F16>(acc[s % E][nb], a0, a1, a2, a3, xb[nb][2 * s], xb[nb][2 * s + 1]);
@@ -322,9 +362,8 @@ __global__ void __launch_bounds__(kRgThreads, 1) linear_wq_mma_regs_kernel(const
             }
           });
 
-          // the warp's partial tile; the buffer of this parity was last read before the barrier of the
-          // iteration before this one
-          const uint32_t dst = T::kEnd + static_cast<uint32_t>(((seq & 1) * kKWarps + warp) * kTile) * 4u;
+          // the warp's partial tile of this unit
+          const uint32_t dst = part_addr(it - c0) + static_cast<uint32_t>(warp * kTile) * 4u;
 #pragma unroll
           for (int nb = 0; nb < NB; ++nb) {
             float c[4];
@@ -334,16 +373,22 @@ __global__ void __launch_bounds__(kRgThreads, 1) linear_wq_mma_regs_kernel(const
             st_shared_f2(dst + (g * MR + m) * 4, c[0] * inv[nb][0], c[1] * inv[nb][1]);
             st_shared_f2(dst + ((g + 8) * MR + m) * 4, c[2] * inv[nb][0], c[3] * inv[nb][1]);
           }
-          __syncthreads();
-          // kAdders warps (another set every iteration) add the sixteen tiles, one sum per lane, into `fin`
-          const int aw = (warp - seq * kAdders) & (kKWarps - 1);
-          if (aw < kAdders) {
-            const float* src = part + static_cast<size_t>(seq & 1) * kKWarps * kTile + aw * 32 + lane;
-            float sum = src[0];
+          if (it + 1 == c_end) {
+            // end of a chunk: all threads add the sixteen tiles of each of its units into `fin`
+            __syncthreads();
+            const int outs = (c_end - c0) * kTile;
+            for (int o = tid; o < outs; o += TH) {
+              const int slot = o / kTile, e = o - slot * kTile;   // consecutive lanes: consecutive words
+              const float* src = reinterpret_cast<const float*>(abs0 + part_addr(slot)) + e;
+              float sum = src[0];
 #pragma unroll
-            for (int wi = 1; wi < kKWarps; ++wi) sum += src[wi * kTile];
-            float* f = fin + static_cast<size_t>(it) * kTile + aw * 32 + lane;
-            *f = pass > 0 ? *f + sum : sum;
+              for (int wi = 1; wi < kKWarps; ++wi) sum += src[wi * kTile];
+              float* f = fin + static_cast<size_t>(c0 + slot) * kTile + e;
+              *f = pass > 0 ? *f + sum : sum;
+            }
+            __syncthreads();
+            c0 = c_end;
+            c_end = min(n_it, c0 + p.chunk);
           }
           if (seq == 0) RG_MARK(4);
           ++seq;
@@ -361,12 +406,12 @@ __global__ void __launch_bounds__(kRgThreads, 1) linear_wq_mma_regs_kernel(const
   const int64_t n0 = static_cast<int64_t>(rb0) * 16;
   if (p.ks > 1) {
     float* dst = p.partial + static_cast<int64_t>(rank) * p.M * p.N + n0;
-    for (int o = tid; o < total_out; o += kRgThreads) {
+    for (int o = tid; o < total_out; o += TH) {
       const int m = o / n_rows, nl = o - m * n_rows;   // consecutive threads: consecutive output columns
       dst[static_cast<int64_t>(m) * p.N + nl] = fin[nl * MR + m];
     }
   } else {
-    for (int o = tid; o < total_out; o += kRgThreads) {
+    for (int o = tid; o < total_out; o += TH) {
       const int m = o / n_rows, nl = o - m * n_rows;
       const int64_t n = n0 + nl;
       const float vb = fin[nl * MR + m] + (p.bias != nullptr ? load_as_float(p.bias, p.bias_dtype, n) : 0.0f);
@@ -405,12 +450,14 @@ __global__ void __launch_bounds__(kFinishThreads) mma_regs_finish_kernel(const R
 }
 
 struct RgPlan {
-  int nb, ks, passes, ranges;
+  int nb, kr, ks, passes, ranges, chunk, chunk_low;
+  uint32_t fin_bytes;
   size_t smem;
 };
 
 #ifdef DIMQ_B200_DIAG
 int g_force_ks = 0;   // k slices at a time, when it divides K / 2048
+int g_force_kr = 0;   // k per warp (64 or 128)
 uint32_t* g_trace = nullptr;
 #endif
 
@@ -419,6 +466,10 @@ bool make_rg_plan(int64_t M, int64_t N, int64_t K, RgPlan* out) {
   using T = Tbl<BITS>;
   RgPlan pl{};
   pl.nb = M <= 8 ? 1 : 2;
+  pl.kr = 128;
+#ifdef DIMQ_B200_DIAG
+  if (g_force_kr == 64 && BITS != 3 && pl.nb == 1) pl.kr = 64;   // 32 warps of 64 k: measured 30 % slower
+#endif
   const int slices = static_cast<int>(K / kCtaK);
   // k slices at a time: the largest divisor of the slice count up to 4, else up to 8, else passes
   int ks = 1;
@@ -433,10 +484,17 @@ bool make_rg_plan(int64_t M, int64_t N, int64_t K, RgPlan* out) {
   const int64_t cl = kNumSMs / ks;
   pl.ranges = static_cast<int>(nrb < cl ? nrb : cl);
   const int64_t max_it = (nrb + pl.ranges - 1) / pl.ranges;
-  const size_t fin_addr = T::kEnd + 2 * kKWarps * 16 * 8 * pl.nb * sizeof(float);
-  const size_t end = fin_addr + static_cast<size_t>(max_it) * 16 * 8 * pl.nb * sizeof(float);
-  if (end > kSmemWindow) return false;
-  pl.smem = end;   // counted from shared address 0: the window starts at or below kLowStart
+  // shared memory: fin behind the table, the units' partial tiles below the table and behind fin
+  const size_t unit = static_cast<size_t>(kCtaK / pl.kr) * 16 * 8 * pl.nb * sizeof(float);
+  const size_t fin_bytes = static_cast<size_t>(max_it) * 16 * 8 * pl.nb * sizeof(float);
+  if (T::kEnd + fin_bytes > kSmemWindow) return false;
+  const int64_t low = (T::kAddr - kLowPart) / unit;
+  const int64_t high = (kSmemWindow - T::kEnd - fin_bytes) / unit;
+  if (low + high < 1) return false;
+  pl.chunk = static_cast<int>(low + high < max_it ? low + high : max_it);
+  pl.chunk_low = static_cast<int>(low < pl.chunk ? low : pl.chunk);
+  pl.fin_bytes = static_cast<uint32_t>(fin_bytes);
+  pl.smem = T::kEnd + fin_bytes + static_cast<size_t>(pl.chunk - pl.chunk_low) * unit;   // counted from shared address 0
   *out = pl;
   return true;
 }
@@ -450,9 +508,9 @@ bool rg_plan_for(int bits, int64_t M, int64_t N, int64_t K, RgPlan* plan) {
   }
 }
 
-template <int BITS, int NB, bool F16>
+template <int BITS, int NB, bool F16, int KR>
 int launch_rg(RgParams& p, const RgPlan& plan, cudaStream_t st) {
-  auto kern = linear_wq_mma_regs_kernel<BITS, NB, F16>;
+  auto kern = linear_wq_mma_regs_kernel<BITS, NB, F16, KR>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemWindow);
   if (e != cudaSuccess) return static_cast<int>(e);
   void* status = nullptr;
@@ -464,7 +522,7 @@ int launch_rg(RgParams& p, const RgPlan& plan, cudaStream_t st) {
 #endif
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(plan.ranges * plan.ks));   // no CTA waits for another: any order will do
-  cfg.blockDim = dim3(kRgThreads);
+  cfg.blockDim = dim3(kCtaK / KR * 32);
   cfg.dynamicSmemBytes = plan.smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -489,14 +547,20 @@ int launch_rg(RgParams& p, const RgPlan& plan, cudaStream_t st) {
 
 template <int BITS>
 int launch_rg_bits(RgParams& p, const RgPlan& plan, bool f16, cudaStream_t st) {
-  if (plan.nb == 1) return f16 ? launch_rg<BITS, 1, true>(p, plan, st) : launch_rg<BITS, 1, false>(p, plan, st);
-  return f16 ? launch_rg<BITS, 2, true>(p, plan, st) : launch_rg<BITS, 2, false>(p, plan, st);
+#ifdef DIMQ_B200_DIAG
+  if constexpr (BITS != 3) {
+    if (plan.nb == 1 && plan.kr == 64)
+      return f16 ? launch_rg<BITS, 1, true, 64>(p, plan, st) : launch_rg<BITS, 1, false, 64>(p, plan, st);
+  }
+#endif
+  if (plan.nb == 1) return f16 ? launch_rg<BITS, 1, true, 128>(p, plan, st) : launch_rg<BITS, 1, false, 128>(p, plan, st);
+  return f16 ? launch_rg<BITS, 2, true, 128>(p, plan, st) : launch_rg<BITS, 2, false, 128>(p, plan, st);
 }
 
 }  // namespace
 
 #ifdef DIMQ_B200_DIAG
-void set_mma_regs_slices(int ks) { g_force_ks = ks; }
+void set_mma_regs_slices(int ks) { g_force_ks = ks & 0xFF; g_force_kr = ks >> 8; }   // slices | k per warp << 8
 void set_mma_regs_trace(uint32_t* trace) { g_trace = trace; }
 #endif
 
@@ -544,6 +608,7 @@ int launch_linear_wq_mma_regs(const void* x, int x_dtype, const dimq_wq_weight* 
   p.cvt = (x_dtype == DIMQ_BF16 && w->cb_dtype != DIMQ_BF16) ? 1 : 0;
   p.nrb = static_cast<int>(N / 16); p.ks = plan.ks; p.passes = plan.passes; p.ranges = plan.ranges;
   p.partial = static_cast<float*>(workspace);
+  p.chunk = plan.chunk; p.chunk_low = plan.chunk_low; p.fin_bytes = plan.fin_bytes;
   const bool f16 = x_dtype == DIMQ_F16 || p.cvt != 0;
   switch (w->bits) {
     case 2: return launch_rg_bits<2>(p, plan, f16, st);
