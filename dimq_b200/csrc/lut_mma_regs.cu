@@ -171,15 +171,19 @@ __device__ __forceinline__ void load_lane_words(const uint8_t* p, uint32_t (&w)[
 // behind, it is bound by the load / store pipe - per unit 32 lookups, 16 wavefronts of index loads (a
 // warp's 16-byte pieces lie in eight different rows), the partial tile - and halving a warp's k doubles
 // the loads and tiles per k.
-template <int BITS, int NB, bool F16, int KR>
+// MR: columns kept of a unit's 16 x 8 (M > 8: 16 x 16) accumulator tile - M rounded up to 2, 4, 8 or 16.
+// The MMAs always compute eight (sixteen) columns; only the lanes that hold one of the first MR columns
+// store their part of the partial tile, so the tile costs one shared-memory wavefront per store instead
+// of two at M <= 4, and its reduction shrinks with it.
+template <int BITS, int MR, bool F16, int KR>
 __global__ void __launch_bounds__(kCtaK / KR * 32, 1) linear_wq_mma_regs_kernel(const RgParams p) {
+  constexpr int NB = MR == 16 ? 2 : 1;   // 8-column MMA tiles
   using T = Tbl<BITS>;
   constexpr int kKWarps = kCtaK / KR;
   constexpr int TH = kKWarps * 32;
   constexpr int W = KR / 4 * BITS / 32;   // words of a lane's indices of one row of a unit
   constexpr int kSteps = KR / 16;         // MMA steps of a unit
   constexpr int XW = KR / 8;              // registers of a lane's activations of one row
-  constexpr int MR = 8 * NB;          // columns of the MMA tiles (activation rows, M rounded up)
   constexpr int kTile = 16 * MR;      // floats of one row block's sums
   extern __shared__ __align__(16) unsigned char smem[];
   const uint32_t s0 = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
@@ -370,8 +374,10 @@ __global__ void __launch_bounds__(kCtaK / KR * 32, 1) linear_wq_mma_regs_kernel(
 #pragma unroll
             for (int j = 0; j < 4; ++j) c[j] = E == 2 ? acc[0][nb][j] + acc[E - 1][nb][j] : acc[0][nb][j];
             const int m = nb * 8 + 2 * t;
-            st_shared_f2(dst + (g * MR + m) * 4, c[0] * inv[nb][0], c[1] * inv[nb][1]);
-            st_shared_f2(dst + ((g + 8) * MR + m) * 4, c[2] * inv[nb][0], c[3] * inv[nb][1]);
+            if (MR >= 8 || m < MR) {   // only the lanes that hold a kept column
+              st_shared_f2(dst + (g * MR + m) * 4, c[0] * inv[nb][0], c[1] * inv[nb][1]);
+              st_shared_f2(dst + ((g + 8) * MR + m) * 4, c[2] * inv[nb][0], c[3] * inv[nb][1]);
+            }
           }
           if (it + 1 == c_end) {
             // end of a chunk: all threads add the sixteen tiles of each of its units into `fin`
@@ -450,7 +456,7 @@ __global__ void __launch_bounds__(kFinishThreads) mma_regs_finish_kernel(const R
 }
 
 struct RgPlan {
-  int nb, kr, ks, passes, ranges, chunk, chunk_low;
+  int mr, kr, ks, passes, ranges, chunk, chunk_low;
   uint32_t fin_bytes;
   size_t smem;
 };
@@ -465,10 +471,10 @@ template <int BITS>
 bool make_rg_plan(int64_t M, int64_t N, int64_t K, RgPlan* out) {
   using T = Tbl<BITS>;
   RgPlan pl{};
-  pl.nb = M <= 8 ? 1 : 2;
+  pl.mr = M <= 2 ? 2 : (M <= 4 ? 4 : (M <= 8 ? 8 : 16));   // columns kept of the accumulator tiles
   pl.kr = 128;
 #ifdef DIMQ_B200_DIAG
-  if (g_force_kr == 64 && BITS != 3 && pl.nb == 1) pl.kr = 64;   // 32 warps of 64 k: measured 30 % slower
+  if (g_force_kr == 64 && BITS != 3 && pl.mr == 8) pl.kr = 64;   // 32 warps of 64 k: measured 30 % slower
 #endif
   const int slices = static_cast<int>(K / kCtaK);
   // k slices at a time: the largest divisor of the slice count up to 4, else up to 8, else passes
@@ -485,8 +491,8 @@ bool make_rg_plan(int64_t M, int64_t N, int64_t K, RgPlan* out) {
   pl.ranges = static_cast<int>(nrb < cl ? nrb : cl);
   const int64_t max_it = (nrb + pl.ranges - 1) / pl.ranges;
   // shared memory: fin behind the table, the units' partial tiles below the table and behind fin
-  const size_t unit = static_cast<size_t>(kCtaK / pl.kr) * 16 * 8 * pl.nb * sizeof(float);
-  const size_t fin_bytes = static_cast<size_t>(max_it) * 16 * 8 * pl.nb * sizeof(float);
+  const size_t unit = static_cast<size_t>(kCtaK / pl.kr) * 16 * pl.mr * sizeof(float);
+  const size_t fin_bytes = static_cast<size_t>(max_it) * 16 * pl.mr * sizeof(float);
   if (T::kEnd + fin_bytes > kSmemWindow) return false;
   const int64_t low = (T::kAddr - kLowPart) / unit;
   const int64_t high = (kSmemWindow - T::kEnd - fin_bytes) / unit;
@@ -508,9 +514,9 @@ bool rg_plan_for(int bits, int64_t M, int64_t N, int64_t K, RgPlan* plan) {
   }
 }
 
-template <int BITS, int NB, bool F16, int KR>
+template <int BITS, int MR, bool F16, int KR>
 int launch_rg(RgParams& p, const RgPlan& plan, cudaStream_t st) {
-  auto kern = linear_wq_mma_regs_kernel<BITS, NB, F16, KR>;
+  auto kern = linear_wq_mma_regs_kernel<BITS, MR, F16, KR>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemWindow);
   if (e != cudaSuccess) return static_cast<int>(e);
   void* status = nullptr;
@@ -545,16 +551,24 @@ int launch_rg(RgParams& p, const RgPlan& plan, cudaStream_t st) {
   return launch_status();
 }
 
-template <int BITS>
-int launch_rg_bits(RgParams& p, const RgPlan& plan, bool f16, cudaStream_t st) {
+template <int BITS, bool F16>
+int launch_rg_cols(RgParams& p, const RgPlan& plan, cudaStream_t st) {
 #ifdef DIMQ_B200_DIAG
   if constexpr (BITS != 3) {
-    if (plan.nb == 1 && plan.kr == 64)
-      return f16 ? launch_rg<BITS, 1, true, 64>(p, plan, st) : launch_rg<BITS, 1, false, 64>(p, plan, st);
+    if (plan.mr == 8 && plan.kr == 64) return launch_rg<BITS, 8, F16, 64>(p, plan, st);
   }
 #endif
-  if (plan.nb == 1) return f16 ? launch_rg<BITS, 1, true, 128>(p, plan, st) : launch_rg<BITS, 1, false, 128>(p, plan, st);
-  return f16 ? launch_rg<BITS, 2, true, 128>(p, plan, st) : launch_rg<BITS, 2, false, 128>(p, plan, st);
+  switch (plan.mr) {
+    case 2: return launch_rg<BITS, 2, F16, 128>(p, plan, st);
+    case 4: return launch_rg<BITS, 4, F16, 128>(p, plan, st);
+    case 8: return launch_rg<BITS, 8, F16, 128>(p, plan, st);
+    default: return launch_rg<BITS, 16, F16, 128>(p, plan, st);
+  }
+}
+
+template <int BITS>
+int launch_rg_bits(RgParams& p, const RgPlan& plan, bool f16, cudaStream_t st) {
+  return f16 ? launch_rg_cols<BITS, true>(p, plan, st) : launch_rg_cols<BITS, false>(p, plan, st);
 }
 
 }  // namespace
