@@ -187,6 +187,9 @@ def run_micro(args) -> None:
     parts = args.micro.split(",")
     m, k, n, bits = (int(v) for v in parts[:4])
     algo = parts[4] if len(parts) > 4 and parts[4] not in ("", "auto") else None
+    tiled = algo is not None and algo.endswith("_tiled")      # the small-M kernel over prepacked (tiled) indices
+    if tiled:
+        algo = algo[:-len("_tiled")]
     index_bytes = n * k * bits // 8
     copies = int(parts[5]) if len(parts) > 5 else max(1, min(64, (192 << 20) // max(index_bytes, 1) + 1))
     dev = torch.device("cuda", 0)
@@ -196,7 +199,8 @@ def run_micro(args) -> None:
     groups = n // 128 if bits == 3 and n % 128 == 0 else 1
     cb = (torch.randn(groups, 1 << bits, device=dev) * 0.02).sort(dim=1).values.to(torch.bfloat16)
     kw = dict(bits=bits, group_rows=128 if groups > 1 else None, out_dtype=torch.bfloat16, algo=algo)
-    call = lambda pw: ops.dimq_linear_wq(x, pw, cb, None, n, k, **kw)
+    tiles = {id(pw): ops.linear_prepack(pw, n, k, bits) for pw in packed} if tiled else {}
+    call = lambda pw: ops.dimq_linear_wq(x, pw, cb, None, n, k, packed_tiled=tiles.get(id(pw)), **kw)
     for pw in packed[:2]:
         call(pw)
     torch.cuda.synchronize()
@@ -220,7 +224,8 @@ def run_micro(args) -> None:
     hbm_peak = float(json.loads(path.read_text()).get("hbm_gbs", FALLBACK_HBM_GBS)) if path.exists() else FALLBACK_HBM_GBS
     print(json.dumps({
         "metric": "linear_wq_us_per_call", "value": us, "unit": "us", "higher_is_better": False,
-        "config": {"workload": f"lut_gemm_m{m}_k{k}_n{n}_w{bits}", "algo": algo or "auto", "weight_copies": copies,
+        "config": {"workload": f"lut_gemm_m{m}_k{k}_n{n}_w{bits}", "algo": (algo or "auto") + ("_tiled" if tiled else ""),
+                   "weight_copies": copies,
                    "l2": "weights rotated over more than 126 MB" if copies * index_bytes > (126 << 20) else "weights fit L2"},
         "tflops": 2.0 * m * n * k / us / 1e6, "tflops_frac": 2.0 * m * n * k / us / 1e6 / tc_peak,
         "index_gbs": index_bytes / us / 1e3, "index_gbs_frac": index_bytes / us / 1e3 / hbm_peak,
@@ -249,9 +254,15 @@ def small_m_micro(dev) -> dict:
         copies = 136 if index_bytes <= (2 << 20) else 6
         packed = [torch.randint(0, 256, (index_bytes,), dtype=torch.uint8, device=dev) for _ in range(copies)]
         cb = (torch.randn(1, 16, device=dev) * 0.02).sort(dim=1).values.to(torch.float16)
+        # what a DIMQLinear module does on its own: a tiled copy of the indices where the small-M kernel takes
+        # the weight (K a multiple of 2048, 2 MB of indices and more); the calls read that copy, not the other
+        tiles = {}
+        if k % 2048 == 0 and index_bytes >= (2 << 20):
+            tiles = {id(pw): ops.linear_prepack(pw, n, k, bits) for pw in packed}
         for m in (1, 4, 16):
             x = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
-            call = lambda pw: ops.dimq_linear_wq(x, pw, cb, None, n, k, bits=bits, out_dtype=torch.bfloat16)
+            call = lambda pw: ops.dimq_linear_wq(x, pw, cb, None, n, k, bits=bits, out_dtype=torch.bfloat16,
+                                                 packed_tiled=tiles.get(id(pw)))
             call(packed[0])
             torch.cuda.synchronize()
             reps = max(1, 24 // copies)      # a graph of at least 24 calls
@@ -271,7 +282,7 @@ def small_m_micro(dev) -> dict:
             us = start.elapsed_time(end) * 1e3 / (5 * copies * reps)
             out["cases"].append({"m": m, "k": k, "n": n, "us": us, "index_gbs": index_bytes / us / 1e3,
                                  "index_gbs_frac": index_bytes / us / 1e3 / hbm_peak})
-        del packed
+        del packed, tiles
     return out
 
 

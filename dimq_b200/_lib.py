@@ -29,7 +29,7 @@ EXPORTED_SYMBOLS = (
     "dimq_last_device_status", "dimq_add_layer_norm", "dimq_conv_prepack", "dimq_conv2d_wq_static", "dimq_im2col", "dimq_max_pool_nhwc", "dimq_images_to_nhwc",
     "dimq_a4_workspace_bytes", "dimq_linear_lut_tc", "dimq_conv2d_lut_tc",
     "dimq_linear_wq_workspace_bytes", "dimq_linear_wq_ws", "dimq_expand_workspace_bytes", "dimq_linear_wq_expand",
-    "dimq_linear_wq_regs_workspace_bytes", "dimq_linear_wq_regs",
+    "dimq_linear_wq_regs_workspace_bytes", "dimq_linear_wq_regs", "dimq_linear_prepack",
     "dimq_conv2d_wq_workspace_bytes", "dimq_conv2d_wq_ws", "dimq_conv2d_wq_expand", "dimq_selftest_bounded_wait", "dimq_fake_quantize_ste", "dimq_centre_quantize_u4",
 )
 

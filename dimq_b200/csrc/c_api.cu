@@ -55,6 +55,7 @@ int launch_linear_wq_mma_regs(const void* x, int x_dtype, const dimq_wq_weight* 
                               const void* residual, void* y, int y_dtype, int64_t M, int64_t N, int64_t K,
                               int epilogue, void* workspace, int64_t workspace_bytes, cudaStream_t st);
 int read_rg_status(uint32_t* status);
+int launch_linear_prepack(const uint8_t* packed, int bits, int64_t N, int64_t K, uint8_t* out, cudaStream_t st);
 int read_dense_status(uint32_t* status);
 int launch_bounded_wait_selftest(uint32_t polls, uint32_t* result, cudaStream_t st);
 }  // namespace dimq
@@ -172,6 +173,13 @@ extern "C" int dimq_linear_wq(const void* x, int x_dtype, const dimq_wq_weight* 
     default:
       return DIMQ_ERR_UNSUPPORTED;
   }
+}
+
+extern "C" int dimq_linear_prepack(const uint8_t* packed, int32_t bits, int64_t N, int64_t K, uint8_t* packed_tiled,
+                                   void* stream) {
+  if (packed == nullptr || packed_tiled == nullptr) return DIMQ_ERR_NULL_POINTER;
+  if (N <= 0 || K <= 0) return DIMQ_ERR_BAD_SIZE;
+  return launch_linear_prepack(packed, bits, N, K, packed_tiled, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int dimq_linear_wq_regs_workspace_bytes(const void* x, int x_dtype, const dimq_wq_weight* w, int64_t M,

@@ -54,6 +54,7 @@ struct RgParams {
   int M;
   int64_t N, K;
   int64_t row_bytes;  // of the packed index matrix
+  int tiled;          // 1: `packed` is the output of dimq_linear_prepack ([row block][128-k range][16 rows][16 * bits bytes])
   int epilogue;
   int cvt;       // 1: x is bf16 and is converted to fp16 in registers
   int nrb;       // row blocks (N / 16)
@@ -224,10 +225,15 @@ __global__ void __launch_bounds__(kCtaK / KR * 32, 1) linear_wq_mma_regs_kernel(
 
   // byte offsets into the packed matrix fit 32 bits (checked on the host)
   const uint32_t row_bytes = static_cast<uint32_t>(p.row_bytes);
-  const uint32_t it_stride = 16u * row_bytes, half_stride = 8u * row_bytes;
+  // canonical layout: the lane's pieces of rows g and g + 8 lie 8 rows apart and a warp's load touches eight
+  // rows; tiled layout: the 16 row pieces of a unit are contiguous, a warp's load is one run of 512 bytes
+  constexpr uint32_t kPiece = KR * BITS / 8;   // bytes of one row of a unit
+  const uint32_t it_stride = 16u * row_bytes;  // the same unit of the next row block (either layout)
+  const uint32_t half_stride = p.tiled ? 8u * kPiece : 8u * row_bytes;
   auto unit_off = [&](int pass) -> uint32_t {
     const int kr = (pass * p.ks + rank) * kKWarps + warp;
-    return (static_cast<uint32_t>(rb0) * 16u + g) * row_bytes + kr * (KR * BITS / 8) + t * (4 * W);
+    if (p.tiled) return static_cast<uint32_t>(rb0) * it_stride + (kr * 16u + g) * kPiece + t * (4 * W);
+    return (static_cast<uint32_t>(rb0) * 16u + g) * row_bytes + kr * kPiece + t * (4 * W);
   };
   uint32_t buf[kDepth][2][W];
   auto load_unit = [&](uint32_t (&b)[2][W], uint32_t off) {
@@ -455,6 +461,20 @@ __global__ void __launch_bounds__(kFinishThreads) mma_regs_finish_kernel(const R
   }
 }
 
+// canonical [N][K] index stream -> tiles of 16 rows x 128 k, [row block][128-k range][row][16 * bits bytes]:
+// one 32-bit word per thread
+__global__ void linear_prepack_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ dst, int bits,
+                                      int64_t row_words, int64_t ranges, int64_t total_words) {
+  const int64_t wo = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (wo >= total_words) return;
+  const int piece = 4 * bits;                  // words of one row of a unit
+  const int64_t tile = wo / (16 * piece);
+  const int within = static_cast<int>(wo - tile * (16 * piece));
+  const int r = within / piece, cw = within - r * piece;
+  const int64_t rb = tile / ranges, kr = tile - rb * ranges;
+  dst[wo] = src[(rb * 16 + r) * row_words + kr * piece + cw];
+}
+
 struct RgPlan {
   int mr, kr, ks, passes, ranges, chunk, chunk_low;
   uint32_t fin_bytes;
@@ -614,7 +634,13 @@ int launch_linear_wq_mma_regs(const void* x, int x_dtype, const dimq_wq_weight* 
   if (need > 0 && (workspace == nullptr || workspace_bytes < need)) return DIMQ_ERR_SCRATCH_TOO_SMALL;
   if (need > 0 && !aligned(workspace, 16)) return DIMQ_ERR_ALIGNMENT;
   RgParams p{};
-  p.x = x; p.packed = w->packed; p.codebooks = w->codebooks; p.cb_dtype = w->cb_dtype; p.entries = w->entries;
+  p.x = x; p.codebooks = w->codebooks;
+  p.tiled = (w->packed_khwc != nullptr && aligned(w->packed_khwc, 16)) ? 1 : 0;   // the output of dimq_linear_prepack
+  p.packed = p.tiled ? w->packed_khwc : w->packed;
+#ifdef DIMQ_B200_DIAG
+  if (plan.kr != 128) { p.tiled = 0; p.packed = w->packed; }   // the tiles are cut for 128 k per warp
+#endif
+  p.cb_dtype = w->cb_dtype; p.entries = w->entries;
   p.group_rbs = w->groups > 1 ? static_cast<int>(w->group_rows / 16) : static_cast<int>(N / 16) + 1;
   p.bias = bias; p.bias_dtype = bias_dtype; p.residual = residual; p.y = y; p.y_dtype = y_dtype;
   p.M = static_cast<int>(M); p.N = N; p.K = K; p.epilogue = epilogue;
@@ -629,6 +655,21 @@ int launch_linear_wq_mma_regs(const void* x, int x_dtype, const dimq_wq_weight* 
     case 3: return launch_rg_bits<3>(p, plan, f16, st);
     default: return launch_rg_bits<4>(p, plan, f16, st);
   }
+}
+
+// Index stream of a Linear weight re-ordered for this kernel: every unit (16 rows x 128 k) contiguous, so
+// that a warp's index load is one run of 512 bytes (4-bit) instead of sixteen 16-byte pieces in eight rows.
+int launch_linear_prepack(const uint8_t* packed, int bits, int64_t N, int64_t K, uint8_t* out, cudaStream_t st) {
+  if (bits != 2 && bits != 3 && bits != 4) return DIMQ_ERR_UNSUPPORTED;
+  if (N < 16 || N % 16 != 0 || K < 128 || K % 128 != 0) return DIMQ_ERR_UNSUPPORTED;
+  if (!aligned(packed, 4) || !aligned(out, 16)) return DIMQ_ERR_ALIGNMENT;
+  const int64_t total_words = N * K * bits / 32;
+  if (total_words > 0x7FFFFFFFll * 64) return DIMQ_ERR_TOO_LARGE;
+  const int threads = 256;
+  linear_prepack_kernel<<<static_cast<unsigned>((total_words + threads - 1) / threads), threads, 0, st>>>(
+      reinterpret_cast<const uint32_t*>(packed), reinterpret_cast<uint32_t*>(out), bits, K * bits / 32, K / 128,
+      total_words);
+  return launch_status();
 }
 
 // Status word of this kernel (non-zero: the shared-memory window did not start where the fixed layout

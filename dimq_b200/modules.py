@@ -78,13 +78,32 @@ class DIMQLinear(_PackedBase):
                           group_rows, out_dtype, epilogue)
         self.out_features = int(out_features)
         self.in_features = int(in_features)
+        # indices re-ordered for the small-M kernel: built the first time a call with at most 16 activation
+        # rows meets a weight that kernel takes (a second copy of the indices), rebuilt whenever the
+        # packed_weight buffer is replaced, moved or written in place
+        self._tiled = None
+        self._tiled_key = None
+
+    def _prepacked(self, rows: int, x: torch.Tensor) -> torch.Tensor | None:
+        if (rows > 16 or self.bits not in (2, 3, 4) or self.out_features % 16 != 0 or self.in_features % 2048 != 0
+                or x.dtype not in (torch.float16, torch.bfloat16)
+                or self.out_features * self.in_features * self.bits < (1 << 24)):
+            return None
+        pw = self.packed_weight
+        key = (pw.data_ptr(), pw._version, pw.device)
+        if self._tiled is None or self._tiled_key != key:
+            self._tiled = ops.linear_prepack(pw, self.out_features, self.in_features, self.bits)
+            self._tiled_key = key
+        return self._tiled
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
         self._check_input(x)
         if self.act_scale is None:
+            tiled = self._prepacked(x.numel() // self.in_features, x)
             return ops.dimq_linear_wq(x, self.packed_weight, self.codebook, self.bias, self.out_features,
                                       self.in_features, bits=self.bits, group_rows=self.group_rows,
-                                      out_dtype=self.out_dtype, epilogue=self.epilogue, residual=residual)
+                                      out_dtype=self.out_dtype, epilogue=self.epilogue, residual=residual,
+                                      packed_tiled=tiled)
         rows = x.numel() // self.in_features
         if rows >= ops.A4_TC_MIN_ROWS and self.in_features % 64 == 0:
             # many rows: centred activation codes (exact in bf16) times the scaled codebook through the

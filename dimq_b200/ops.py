@@ -542,11 +542,13 @@ def dimq_linear_wq(x: torch.Tensor, packed_weight: torch.Tensor, codebooks: torc
                    bias: torch.Tensor | None, out_features: int, in_features: int, *, bits: int = 4,
                    group_rows: int | None = None, out_dtype: torch.dtype | None = None,
                    epilogue: str | None = None, residual: torch.Tensor | None = None,
-                   algo: str | None = None) -> torch.Tensor:
+                   algo: str | None = None, packed_tiled: torch.Tensor | None = None) -> torch.Tensor:
     """Weight-only LUT linear: ``x @ codebook[idx].T + bias`` with fp32 accumulation.
 
     The result the reference gets from ``dequantize_packed_weight`` + ``F.linear``
-    (dimq_backend/reference.py:47-56), without materialising the weight.
+    (dimq_backend/reference.py:47-56), without materialising the weight.  ``packed_tiled`` (the indices
+    re-ordered by :func:`linear_prepack`) speeds up the small-M kernel for large weights; the result is the
+    same bits with and without it.
     """
     require_extension()
     _require_cuda(x, "linear_wq")
@@ -558,7 +560,8 @@ def dimq_linear_wq(x: torch.Tensor, packed_weight: torch.Tensor, codebooks: torc
     if x.dim() == 0 or x.size(-1) != in_features:
         raise RuntimeError("input last dimension must equal in_features")
     xc = x.contiguous()
-    w, keep = _wq_weight(packed_weight, codebooks, int(bits), out_features, out_features * in_features, group_rows)
+    w, keep = _wq_weight(packed_weight, codebooks, int(bits), out_features, out_features * in_features, group_rows,
+                         packed_tiled)
     b, b_dt = _bias_arg(bias, out_features, xc.device, "out_features")
     out_dtype = out_dtype or torch.float32
     m = xc.numel() // in_features
@@ -699,6 +702,23 @@ def dimq_conv2d_wq(x: torch.Tensor, packed_weight: torch.Tensor, codebooks: torc
     _lib.check(st, "conv2d_wq")
     del keep
     return y
+
+
+def linear_prepack(packed_weight: torch.Tensor, out_features: int, in_features: int, bits: int = 4) -> torch.Tensor:
+    """Indices of an ``[N, K]`` weight re-ordered into tiles of 16 rows x 128 k (same bit width and size): what
+    ``dimq_linear_wq(..., packed_tiled=...)`` takes.  2-, 3- or 4-bit, N a multiple of 16, K of 128."""
+    require_extension()
+    _require_cuda(packed_weight, "linear_prepack")
+    nbytes = out_features * in_features * bits // 8
+    src = packed_weight.contiguous().view(-1)
+    if src.dtype != torch.uint8 or src.numel() < nbytes:
+        raise RuntimeError("packed_weight is too small for the weight shape")
+    dst = torch.empty((nbytes,), dtype=torch.uint8, device=src.device)
+    with torch.cuda.device(src.device):
+        st = _lib.lib().dimq_linear_prepack(_lib.ptr(src), C.c_int(bits), C.c_int64(out_features),
+                                            C.c_int64(in_features), _lib.ptr(dst), _lib.stream_ptr(src.device))
+    _lib.check(st, "linear_prepack")
+    return dst
 
 
 def conv_prepack(packed_weight: torch.Tensor, weight_shape: Sequence[int], bits: int = 4) -> torch.Tensor:

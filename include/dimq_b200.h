@@ -163,8 +163,11 @@ typedef struct dimq_wq_weight {
   int32_t entries;           /* <= 2^bits */
   int64_t groups;
   int64_t group_rows;        /* output rows (channels) per codebook */
-  const uint8_t* packed_khwc; /* optional, convolution only: the same indices re-ordered to
-                                [OC][KH][KW][ICg] by dimq_conv_prepack; enables the tensor-core conv */
+  const uint8_t* packed_khwc; /* optional second copy of the indices in the order a fast kernel reads them.
+                                Convolutions: [OC][KH][KW][ICg], written by dimq_conv_prepack; enables the
+                                tensor-core conv.  Linear layers: tiles of 16 rows x 128 k, written by
+                                dimq_linear_prepack; read by the register-resident small-M kernel only (its index
+                                loads become contiguous), every other kernel reads `packed` */
 } dimq_wq_weight;
 
 /* y[m][n] = sum_k x[m][k] * codebooks[n / group_rows][idx(n, k)] + bias[n], then
@@ -260,6 +263,10 @@ DIMQ_API int dimq_conv2d_wq_expand(const void* x, int x_dtype, const dimq_wq_wei
  * (DIMQ_ERR_UNSUPPORTED outside M <= 16, 16-bit x, 2- to 4-bit indices, N % 16 == 0, K % 2048 == 0).
  * dimq_linear_wq_regs_workspace_bytes gives the scratch it needs (0 when K = 2048).  Replaces the
  * reference's per-call dequantisation (dimq_backend/reference.py:47-56) in the decode regime. */
+/* packed_tiled = the [N, K] index stream re-ordered into tiles of 16 rows x 128 k ([row block][128-k range][row]
+ * [16 * bits bytes]); same size as the input.  2-, 3- or 4-bit, N a multiple of 16, K of 128; once per layer. */
+DIMQ_API int dimq_linear_prepack(const uint8_t* packed, int32_t bits, int64_t N, int64_t K, uint8_t* packed_tiled,
+                                 void* stream);
 DIMQ_API int dimq_linear_wq_regs_workspace_bytes(const void* x, int x_dtype, const dimq_wq_weight* w, int64_t M,
                                                  int64_t N, int64_t K, int64_t* bytes);
 DIMQ_API int dimq_linear_wq_regs(const void* x, int x_dtype, const dimq_wq_weight* w, const void* bias, int bias_dtype,

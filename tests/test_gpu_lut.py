@@ -454,6 +454,41 @@ def test_linear_wq_mma_regs_rejects_and_auto_dispatch(ops):
     assert not torch.equal(ops.dimq_linear_wq(*args, bits=4), ops.dimq_linear_wq(*args, bits=4, algo="mma_stream"))
 
 
+@pytest.mark.parametrize("bits", [2, 3, 4])
+def test_linear_prepack_and_tiled_small_m_kernel(ops, bits):
+    """dimq_linear_prepack is the byte permutation it says it is, and the small-M kernel gives the same bits
+    from the tiled indices as from the canonical ones (same arithmetic, another load pattern)."""
+    n, k = 1040, 4096     # 65 row blocks over 74 ranges x 2 slices
+    gen = torch.Generator(device="cuda").manual_seed(bits)
+    packed = torch.randint(0, 256, (n, k * bits // 8), dtype=torch.uint8, device="cuda", generator=gen)
+    tiled = ops.linear_prepack(packed, n, k, bits)
+    piece = 16 * bits     # bytes of one row of a 128-k range
+    want = packed.view(n // 16, 16, k // 128, piece).permute(0, 2, 1, 3).contiguous().view(-1)
+    assert torch.equal(tiled, want)
+    cb = (torch.randn(n // 16, 1 << bits, device="cuda", generator=gen) * 0.02).to(torch.float16)
+    bias = torch.randn(n, device="cuda", generator=gen)
+    for m, x_dtype in ((1, torch.bfloat16), (5, torch.float16), (16, torch.bfloat16)):
+        x = torch.randn(m, k, device="cuda", generator=gen).to(x_dtype)
+        args = (x, packed, cb, bias, n, k)
+        plain = ops.dimq_linear_wq(*args, bits=bits, group_rows=16, algo="mma_regs")
+        fast = ops.dimq_linear_wq(*args, bits=bits, group_rows=16, algo="mma_regs", packed_tiled=tiled)
+        assert ops.last_device_status() == 0
+        assert torch.equal(plain, fast), (bits, m)
+        auto = ops.dimq_linear_wq(*args, bits=bits, group_rows=16, packed_tiled=tiled)   # 2 MB of indices and more at 4 bits
+        exact = ops.dimq_linear_wq(*args, bits=bits, group_rows=16, algo="generic")
+        _assert_close(auto, exact.cpu().numpy(), f"tiled auto bits={bits} m={m}")
+    with pytest.raises(RuntimeError):
+        ops.linear_prepack(packed, n + 8, k, bits)      # N not a multiple of 16 (and a short buffer)
+    # the module builds the tiled copy by itself the first time a small batch meets a large enough weight
+    from dimq_b200.modules import DIMQLinear
+    layer = DIMQLinear(packed, cb, None, None, n, k, bias, bits=bits, group_rows=16)
+    x = torch.randn(3, k, device="cuda", generator=gen).to(torch.bfloat16)
+    y = layer(x)
+    assert (layer._tiled is not None) == (n * k * bits >= 1 << 24)
+    assert torch.equal(y, ops.dimq_linear_wq(x, packed, cb, bias, n, k, bits=bits, group_rows=16))
+    layer(torch.randn(64, k, device="cuda", generator=gen).to(torch.bfloat16))    # many rows: other kernels, same module
+
+
 def test_linear_wq_mma_regs_converts_bf16_activations_of_any_magnitude(ops):
     """bf16 activations with an fp16 codebook run as fp16 MMAs; a (row, 128-k range) whose largest magnitude
     lies outside the exactly convertible range is scaled by a power of two on the way in and its partial sums
