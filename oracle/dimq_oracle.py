@@ -324,3 +324,16 @@ def quantile_codebook(w: np.ndarray, k: int) -> np.ndarray:
             fixed[i] = fixed[i - 1] + min_gap
     fixed = fixed - (fixed.mean(dtype=F32) - centers.mean(dtype=F32))
     return np.sort(fixed).astype(F32)
+
+
+def linear_prepack(packed_w, out_features, in_features, bits):
+    """Byte order of ``dimq_linear_prepack``: the canonical ``[N][K * bits / 8]`` index stream cut into tiles of
+    16 rows x 128 k, stored ``[row block][128-k range][row][16 * bits bytes]``.  No counterpart in the
+    reference (its kernels read the canonical stream, csrc/dimq_gemm_lut.cu:45-49); the layout is this
+    library's own and the oracle states it so that the kernel can be checked against something."""
+    piece = 16 * bits
+    rows = np.asarray(packed_w, dtype=np.uint8).reshape(out_features, in_features * bits // 8)
+    assert out_features % 16 == 0 and in_features % 128 == 0
+    tiles = rows.reshape(out_features // 16, 16, in_features // 128, piece)
+    return np.ascontiguousarray(tiles.transpose(0, 2, 1, 3)).reshape(-1)
+

@@ -465,6 +465,7 @@ def test_linear_prepack_and_tiled_small_m_kernel(ops, bits):
     piece = 16 * bits     # bytes of one row of a 128-k range
     want = packed.view(n // 16, 16, k // 128, piece).permute(0, 2, 1, 3).contiguous().view(-1)
     assert torch.equal(tiled, want)
+    assert np.array_equal(tiled.cpu().numpy(), o.linear_prepack(packed.cpu().numpy(), n, k, bits))
     cb = (torch.randn(n // 16, 1 << bits, device="cuda", generator=gen) * 0.02).to(torch.float16)
     bias = torch.randn(n, device="cuda", generator=gen)
     for m, x_dtype in ((1, torch.bfloat16), (5, torch.float16), (16, torch.bfloat16)):

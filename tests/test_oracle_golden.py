@@ -171,3 +171,21 @@ def test_c_oracle_matches_reference_vectors(golden):
     np.testing.assert_allclose(y, golden["convg_y_deq"], rtol=1e-5, atol=1e-5)
     y = c.linear_wq(golden["wq_lin_x"], golden["wq_lin_packed"], 4, golden["wq_lin_cb"], 48, 96, golden["wq_lin_bias"])
     np.testing.assert_allclose(y, golden["wq_lin_y"], rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4])
+def test_linear_prepack_order_by_hand(bits):
+    """The tiled index order: unit (row block rb, 128-k range kr) is contiguous, its rows in order, and the
+    dequantised weight read back through the tiles is the one read from the canonical stream."""
+    n, k = 48, 384
+    rng = np.random.default_rng(bits)
+    idx = rng.integers(0, 1 << bits, size=(n, k)).astype(np.uint8)
+    packed = o.pack_bits(idx.reshape(-1), bits)
+    tiled = o.linear_prepack(packed, n, k, bits)
+    assert tiled.shape == packed.shape and sorted(tiled.tolist()) == sorted(packed.tolist())
+    piece = 16 * bits
+    for rb, kr, r in ((0, 0, 0), (1, 2, 5), (2, 1, 15)):
+        at = ((rb * (k // 128) + kr) * 16 + r) * piece
+        want = o.pack_bits(idx[rb * 16 + r, kr * 128:(kr + 1) * 128], bits)
+        assert np.array_equal(tiled[at:at + piece], want)
+
