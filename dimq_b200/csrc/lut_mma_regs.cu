@@ -277,7 +277,7 @@ __global__ void __launch_bounds__(kCtaK / KR * 32, 1) linear_wq_mma_regs_kernel(
         constexpr int d = decltype(dc)::value;
         if (d < n_it) load_unit(buf[d], off0 + d * it_stride);
       });
-          if (cur_group != rb0 / p.group_rbs) {   // back to the first row block's codebook
+      if (cur_group != rb0 / p.group_rbs) {   // back to the first row block's codebook
         cur_group = rb0 / p.group_rbs;
         __syncthreads();
         build_table(false);
