@@ -255,9 +255,9 @@ def small_m_micro(dev) -> dict:
         packed = [torch.randint(0, 256, (index_bytes,), dtype=torch.uint8, device=dev) for _ in range(copies)]
         cb = (torch.randn(1, 16, device=dev) * 0.02).sort(dim=1).values.to(torch.float16)
         # what a DIMQLinear module does on its own: a tiled copy of the indices where the small-M kernel takes
-        # the weight (K a multiple of 2048, 2 MB of indices and more); the calls read that copy, not the other
+        # the weight (K a multiple of 128 and at least 2048, 2 MB of indices and more); the calls read that copy
         tiles = {}
-        if k % 2048 == 0 and index_bytes >= (2 << 20):
+        if k % 128 == 0 and k >= 2048 and index_bytes >= (2 << 20):
             tiles = {id(pw): ops.linear_prepack(pw, n, k, bits) for pw in packed}
         for m in (1, 4, 16):
             x = torch.randn(m, k, device=dev, dtype=torch.bfloat16)

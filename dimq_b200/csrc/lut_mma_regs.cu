@@ -65,7 +65,8 @@ struct RgParams {
   int cvt;       // 1: x is bf16 and is converted to fp16 in registers
   int nrb;       // row blocks (N / 16)
   int ks;        // k slices of 2048 worked on at a time = CTAs per range of row blocks
-  int passes;    // K / (2048 ks)
+  int passes;    // slices / ks
+  int nk;        // 128-k ranges of the weight (K / 128): warps of the last slice beyond it have nothing to do
   int ranges;    // ranges of row blocks (each worked on by ks CTAs)
   float* partial;  // ks > 1: [ks][M][N] sums of the k slices
   int chunk;       // units a warp runs through between two reductions
@@ -241,8 +242,13 @@ __global__ void __launch_bounds__(kCtaK / KR * 32, 1) linear_wq_mma_regs_kernel(
     if (p.tiled) return static_cast<uint32_t>(rb0) * it_stride + (kr * 16u + g) * kPiece + t * (4 * W);
     return (static_cast<uint32_t>(rb0) * 16u + g) * row_bytes + kr * kPiece + t * (4 * W);
   };
-  uint32_t buf[kDepth][2][W];
+  // K need not fill the last slice: a warp whose range lies beyond K loads nothing, keeps zero activations and
+  // so contributes tiles of zeros (its lookups read the table at whatever its zeroed index words say)
+  auto live = [&](int pass) -> bool { return (pass * p.ks + rank) * kKWarps + warp < p.nk; };
+  bool live_now = live(0);
+  uint32_t buf[kDepth][2][W] = {};
   auto load_unit = [&](uint32_t (&b)[2][W], uint32_t off) {
+    if (!live_now) return;   // uniform over the warp
     load_lane_words<W>(p.packed + off, b[0]);
     load_lane_words<W>(p.packed + off + half_stride, b[1]);
   };
@@ -272,6 +278,7 @@ __global__ void __launch_bounds__(kCtaK / KR * 32, 1) linear_wq_mma_regs_kernel(
   int seq = 0;
   for (int pass = 0; pass < p.passes; ++pass) {
     if (pass > 0) {
+      live_now = live(pass);
       off0 = unit_off(pass);
       static_for<0, kDepth>([&](auto dc) {
         constexpr int d = decltype(dc)::value;
@@ -292,7 +299,7 @@ __global__ void __launch_bounds__(kCtaK / KR * 32, 1) linear_wq_mma_regs_kernel(
     for (int nb = 0; nb < NB; ++nb) {
       const int m = nb * 8 + g;
       uint4 q[XW / 4];
-      if (m < p.M) {
+      if (m < p.M && live_now) {
         const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.x) +
                                                           static_cast<int64_t>(m) * p.K + kr * KR + (KR / 4) * t);
 #pragma unroll
@@ -502,7 +509,7 @@ bool make_rg_plan(int64_t M, int64_t N, int64_t K, RgPlan* out) {
 #ifdef DIMQ_B200_DIAG
   if (g_force_kr == 64 && BITS != 3 && pl.mr == 8) pl.kr = 64;   // 32 warps of 64 k: measured 30 % slower
 #endif
-  const int slices = static_cast<int>(K / kCtaK);
+  const int slices = static_cast<int>((K + kCtaK - 1) / kCtaK);   // the last one may be partly empty
   // k slices at a time: the largest divisor of the slice count up to 4, else up to 8, else passes
   int ks = 1;
   for (int d = 1; d <= 4; ++d) if (slices % d == 0) ks = d;
@@ -604,11 +611,11 @@ void set_mma_regs_slices(int ks) { g_force_ks = ks & 0xFF; g_force_kr = ks >> 8;
 void set_mma_regs_trace(uint32_t* trace) { g_trace = trace; }
 #endif
 
-// 16-bit activations, M <= 16, N a multiple of 16, K a multiple of 2048, 2-, 3- or 4-bit indices; the
+// 16-bit activations, M <= 16, N a multiple of 16, K a multiple of 128 and at least 2048, 2-, 3- or 4-bit indices; the
 // sums of one CTA's row blocks must fit its shared memory beside the table.
 bool mma_regs_supported(const void* x, int x_dtype, const dimq_wq_weight* w, int64_t M, int64_t N, int64_t K) {
   if (x_dtype != DIMQ_F16 && x_dtype != DIMQ_BF16) return false;
-  if (M < 1 || M > 16 || N < 16 || N % 16 != 0 || K < kCtaK || K % kCtaK != 0) return false;
+  if (M < 1 || M > 16 || N < 16 || N % 16 != 0 || K < kCtaK || K % 128 != 0) return false;
   if (w->bits != 2 && w->bits != 3 && w->bits != 4) return false;
   if (w->groups > 1 && w->group_rows % 16 != 0) return false;
   if (!aligned(x, 16) || !aligned(w->packed, 16)) return false;
@@ -653,6 +660,7 @@ int launch_linear_wq_mma_regs(const void* x, int x_dtype, const dimq_wq_weight* 
   p.row_bytes = K * w->bits / 8;
   p.cvt = (x_dtype == DIMQ_BF16 && w->cb_dtype != DIMQ_BF16) ? 1 : 0;
   p.nrb = static_cast<int>(N / 16); p.ks = plan.ks; p.passes = plan.passes; p.ranges = plan.ranges;
+  p.nk = static_cast<int>(K / 128);
   p.partial = static_cast<float*>(workspace);
   p.chunk = plan.chunk; p.chunk_low = plan.chunk_low; p.fin_bytes = plan.fin_bytes;
   const bool f16 = x_dtype == DIMQ_F16 || p.cvt != 0;

@@ -85,7 +85,8 @@ class DIMQLinear(_PackedBase):
         self._tiled_key = None
 
     def _prepacked(self, rows: int, x: torch.Tensor) -> torch.Tensor | None:
-        if (rows > 16 or self.bits not in (2, 3, 4) or self.out_features % 16 != 0 or self.in_features % 2048 != 0
+        if (rows > 16 or self.bits not in (2, 3, 4) or self.out_features % 16 != 0 or self.in_features % 128 != 0
+                or self.in_features < 2048
                 or x.dtype not in (torch.float16, torch.bfloat16)
                 or self.out_features * self.in_features * self.bits < (1 << 24)):
             return None

@@ -56,8 +56,9 @@ extern "C" {
 #define DIMQ_ALGO_MMA_STREAM 4 /* small-M index-streaming kernel for 16-bit activations (M <= 32): pair-table
                                   lookups feeding warp-level MMAs; the HBM-bound regime */
 #define DIMQ_ALGO_MMA_REGS 6  /* small-M kernel for weights of 2 MB of indices and more (M <= 16, K a multiple of
-                                  2048): activations and indices in registers.  Through dimq_linear_wq only with
-                                  K = 2048 (one k slice); longer K needs scratch: dimq_linear_wq_ws / _regs */
+                                  128, at least 2048): activations and indices in registers.  Through
+                                  dimq_linear_wq only with K = 2048 (one k slice); longer K needs scratch:
+                                  dimq_linear_wq_ws / _regs */
 
 /* fused epilogues of the weight-only ops */
 #define DIMQ_EPI_NONE 0
@@ -210,7 +211,7 @@ DIMQ_API int dimq_conv2d_wq_static(const void* x, int x_dtype, const dimq_wq_wei
 
 /* dimq_linear_wq with caller-owned scratch memory, which three regimes use:
  *  - a few activation rows (M <= 16, 16-bit x) against 2 MB of 2- to 4-bit indices or more, N a multiple
- *    of 16 and K of 2048: the register-resident small-M kernel cuts K into slices of 2048 worked on by
+ *    of 16 and K of 128, K >= 2048: the register-resident small-M kernel cuts K into slices of 2048 worked on by
  *    different CTAs, each writes its partial sums to the workspace (slices * M * N * 4 bytes, at most 8
  *    slices at a time) and a second small kernel adds them in a fixed order and applies bias / epilogue /
  *    residual: no atomics, the same bits every run.
@@ -260,7 +261,7 @@ DIMQ_API int dimq_conv2d_wq_expand(const void* x, int x_dtype, const dimq_wq_wei
                                    void* stream);
 
 /* The register-resident small-M kernel requested explicitly, whatever the size of the weight
- * (DIMQ_ERR_UNSUPPORTED outside M <= 16, 16-bit x, 2- to 4-bit indices, N % 16 == 0, K % 2048 == 0).
+ * (DIMQ_ERR_UNSUPPORTED outside M <= 16, 16-bit x, 2- to 4-bit indices, N % 16 == 0, K % 128 == 0, K >= 2048).
  * dimq_linear_wq_regs_workspace_bytes gives the scratch it needs (0 when K = 2048).  Replaces the
  * reference's per-call dequantisation (dimq_backend/reference.py:47-56) in the decode regime. */
 /* packed_tiled = the [N, K] index stream re-ordered into tiles of 16 rows x 128 k ([row block][128-k range][row]

@@ -364,7 +364,9 @@ def test_linear_wq_mma_stream_converts_bf16_activations_of_any_magnitude(ops):
 # (m, k, n, group rows): 1 / 2 / 3 / 4 / 5 CTAs per cluster, several passes (k / 2048 = 11 is prime; 16384 = 2 x 4
 # slices), codebook groups, fewer row blocks than clusters
 MR_SHAPES = [(1, 2048, 64, None), (8, 4096, 256, 128), (9, 8192, 304, None), (3, 6144, 160, 16), (5, 10240, 48, None),
-             (16, 22528, 32, None), (2, 16384, 96, 32)]
+             (16, 22528, 32, None), (2, 16384, 96, 32),
+             # K that does not fill its last 2048-k slice: 17, 24 and 86 ranges of 128
+             (3, 2176, 64, None), (7, 3072, 320, 16), (16, 11008, 48, None)]
 # enough row blocks that every cluster walks more of them than it keeps in flight (and crosses codebook groups)
 MR_LONG_SHAPES = [(16, 2048, 9616, 32), (4, 8192, 2400, 128), (7, 14336, 1360, 16), (2, 16384, 2384, None)]
 
@@ -442,7 +444,7 @@ def test_linear_wq_mma_regs_rejects_and_auto_dispatch(ops):
         ops.dimq_linear_wq(torch.zeros(17, 2048, device="cuda", dtype=torch.float16), pw, cb, None, 64, 2048, bits=4,
                            algo="mma_regs")
     case = make_weight(64, 1024, 4, seed=1)
-    with pytest.raises(RuntimeError):  # k not a multiple of 2048
+    with pytest.raises(RuntimeError):  # k below 2048
         ops.dimq_linear_wq(torch.zeros(4, 1024, device="cuda", dtype=torch.float16), _cuda(case["packed"]),
                            _cuda(case["codebooks"]), None, 64, 1024, bits=4, algo="mma_regs")
     # 2 MB of indices and more: the automatic choice is this kernel (same bits as the forced call)
@@ -458,7 +460,7 @@ def test_linear_wq_mma_regs_rejects_and_auto_dispatch(ops):
 def test_linear_prepack_and_tiled_small_m_kernel(ops, bits):
     """dimq_linear_prepack is the byte permutation it says it is, and the small-M kernel gives the same bits
     from the tiled indices as from the canonical ones (same arithmetic, another load pattern)."""
-    n, k = 1040, 4096     # 65 row blocks over 74 ranges x 2 slices
+    n, k = 1040, 4224     # 65 row blocks; 33 ranges of 128 k: three slices, the last with one live warp
     gen = torch.Generator(device="cuda").manual_seed(bits)
     packed = torch.randint(0, 256, (n, k * bits // 8), dtype=torch.uint8, device="cuda", generator=gen)
     tiled = ops.linear_prepack(packed, n, k, bits)
@@ -636,8 +638,8 @@ def test_linear_wq_m_sweep_auto_dispatch(ops, bits, k, n, m):
     if m <= 32:
         # what the automatic choice runs here (fp16 codebook, bf16 activations: the reference export's default)
         # is a small-M kernel - the register-resident one from 2 MB of indices on when M <= 16 and K is a
-        # multiple of 2048, else the index-streaming one: the two results are the same bits
-        small = "mma_regs" if (m <= 16 and k % 2048 == 0 and n * k * bits // 8 >= 2 << 20) else "mma_stream"
+        # multiple of 128 and at least 2048, else the index-streaming one: the two results are the same bits
+        small = "mma_regs" if (m <= 16 and k >= 2048 and k % 128 == 0 and n * k * bits // 8 >= 2 << 20) else "mma_stream"
         try:
             forced = ops.dimq_linear_wq(_cuda(x, torch.bfloat16), case["packed_cuda"], case["cb_cuda"], None, n, k,
                                         bits=bits, algo=small)
