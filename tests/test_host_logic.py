@@ -54,6 +54,33 @@ def test_argument_errors_are_reported_without_a_gpu(lib):
                                C.c_int64(4), null) == -2
 
 
+def test_linear_module_builds_tiled_indices_only_where_the_small_m_kernel_takes_them():
+    """DIMQLinear's lazy second copy of the indices: no copy for many rows, a short K, a small weight or fp32
+    activations; where one is due, building it needs the GPU (no CPU fallback: it raises)."""
+    from dimq_b200.modules import DIMQLinear
+
+    def layer(n, k, bits=4):
+        return DIMQLinear(torch.zeros(n * k * bits // 8, dtype=torch.uint8), torch.zeros(1 << bits), None, None, n, k,
+                          bits=bits)
+
+    big = layer(1024, 4096)                                  # 2 MB of indices
+    x16 = torch.zeros(4, 4096, dtype=torch.bfloat16)
+    assert big._prepacked(64, x16) is None                   # more than 16 rows
+    assert big._prepacked(4, x16.float()) is None            # fp32 activations
+    assert layer(4096, 1024)._prepacked(4, x16[:, :1024]) is None   # K below 2048
+    assert layer(256, 4096)._prepacked(4, x16) is None       # 0.5 MB of indices
+    assert layer(1024, 4096, bits=8)._prepacked(4, x16) is None
+    with pytest.raises(RuntimeError):
+        big._prepacked(4, x16)                               # due, but these are CPU tensors
+
+
+def test_linear_prepack_argument_errors(lib):
+    buf = (C.c_uint8 * 64)()
+    assert lib.dimq_linear_prepack(None, 4, C.c_int64(16), C.c_int64(128), buf, None) == -1   # null pointer
+    for bits, n, k in ((8, 16, 128), (4, 24, 128), (4, 16, 192), (4, 0, 128)):
+        assert lib.dimq_linear_prepack(buf, bits, C.c_int64(n), C.c_int64(k), buf, None) < 0, (bits, n, k)
+
+
 def test_conv_geometry(lib):
     from dimq_b200._lib import ConvGeom
 
