@@ -81,6 +81,36 @@ def test_linear_prepack_argument_errors(lib):
         assert lib.dimq_linear_prepack(buf, bits, C.c_int64(n), C.c_int64(k), buf, None) < 0, (bits, n, k)
 
 
+def test_small_m_kernel_plan_through_the_workspace_queries(lib):
+    """How the register-resident small-M kernel cuts K into slices of 2048, read off the scratch it asks for
+    (slices worked on at a time x M x N floats; nothing with one slice).  Host logic only: no launch."""
+    from dimq_b200 import _lib
+
+    fake = 1 << 20                                   # an aligned address that is never dereferenced
+    need = C.c_int64(-1)
+
+    def query(fn, m, n, k, bits=4, x_dtype=_lib.BF16, x=fake):
+        w = _lib.WqWeight(fake, bits, fake, _lib.F16, 1 << bits, 1, n, None)
+        rc = fn(C.c_void_p(x), x_dtype, C.byref(w), C.c_int64(m), C.c_int64(n), C.c_int64(k), C.byref(need))
+        return rc, need.value
+
+    forced = lib.dimq_linear_wq_regs_workspace_bytes
+    assert query(forced, 8, 4096, 8192) == (0, 4 * 8 * 4096 * 4)        # four slices at a time
+    assert query(forced, 1, 4096, 4096) == (0, 2 * 1 * 4096 * 4)
+    assert query(forced, 16, 4096, 2048) == (0, 0)                      # one slice: no scratch
+    assert query(forced, 3, 4096, 11008) == (0, 3 * 3 * 4096 * 4)       # 5.4 -> 6 slices, three at a time, two passes
+    assert query(forced, 3, 64, 22528) == (0, 0)                        # 11 slices: a prime, one at a time
+    assert query(forced, 3, 64, 16384) == (0, 4 * 3 * 64 * 4)           # 8 slices: four at a time, two passes
+    for m, n, k, kw in ((17, 64, 2048, {}), (4, 72, 2048, {}), (4, 64, 1024, {}), (4, 64, 2112, {}),
+                        (4, 64, 2048, {"bits": 8}), (4, 64, 2048, {"x_dtype": _lib.F32}), (4, 64, 2048, {"x": fake + 8})):
+        assert query(forced, m, n, k, **kw)[0] < 0, (m, n, k, kw)       # rows, N % 16, K, bits, dtype, alignment
+    # the automatic choice takes it from 2 MB of indices on; below that the call needs no scratch
+    auto = lib.dimq_linear_wq_workspace_bytes
+    assert query(auto, 4, 1024, 4096) == (0, 2 * 4 * 1024 * 4)
+    assert query(auto, 4, 512, 4096) == (0, 0)
+    assert query(auto, 4, 4096, 1024) == (0, 0)                         # K below 2048: the index-streaming kernel
+
+
 def test_conv_geometry(lib):
     from dimq_b200._lib import ConvGeom
 
